@@ -1,0 +1,142 @@
+/*
+ * nacho_b200 — C ABI of the B200 (sm_100a) sparse-kernel library.
+ *
+ * Drop-in boundary for the GPU hot path of the nacho sparse tensor algebra compiler: each
+ * entry point below stands where one of nacho's emitted host drivers
+ * `<kernel>::<kernel>_gpu_i32_f32(a, b[, c], num_blocks, threads_per_block)` stands today
+ * (emitter: src/backend/stitch_and_generate_gpu.cpp:142-185, signature
+ * src/backend/stitch_and_generate.cpp:278-290), and is what the emitted nanobind wrappers
+ * `gpu_<kernel>_f32` (src/backend/generate_bindings.cpp:288-331) would call instead.
+ *
+ * Conventions shared by every entry point
+ *   - All indices are int32 and all values float32 (src/backend/stitch_and_generate.cpp:235-236).
+ *   - Every array pointer is a DEVICE pointer on the current CUDA device, 4-byte aligned,
+ *     contiguous. Operands are borrowed and never written (runtime/nacho_nb.h:73-78).
+ *   - Operands must hold sorted, duplicate-free columns / coordinates, as nacho requires.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, which is
+ *     what nacho's drivers use, src/backend/stitch_and_generate_gpu.cpp:163-167).
+ *   - Every call returns an nb200_status; 0 is success. Nothing throws and nothing aborts.
+ *   - The calls block the host until the result lengths are known (one small device-to-host
+ *     read), like nacho's drivers do; on return the result is complete in stream order.
+ *   - num_blocks / threads_per_block are accepted for signature compatibility
+ *     (src/backend/generate_bindings.cpp:317-327); the kernels size their own grids, so the
+ *     two values are ignored.
+ *
+ * Two flavours per operator
+ *   nb200_<op>_f32       allocates each result array separately with cudaMallocAsync on
+ *                        `stream`, so that each can be released independently with
+ *                        nb200_free_async (= cudaFreeAsync), the ownership nacho's adopt_gpu
+ *                        capsules expect (runtime/nacho_nb.h:50-58,
+ *                        runtime/cuda_utils/cuda_utils.cu:7-11). A zero-length array is
+ *                        returned as NULL (runtime/nacho_nb.h:37-45).
+ *   nb200_<op>_f32_into  writes into caller-owned arrays of a stated capacity (for callers
+ *                        whose framework owns device memory, e.g. torch tensors) and reports
+ *                        the used lengths. If a capacity is too small the call returns
+ *                        NB200_E_CAPACITY with the needed lengths filled in and the value /
+ *                        index arrays untouched.
+ */
+#ifndef NACHO_B200_H
+#define NACHO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB200_VERSION 100
+
+typedef enum nb200_status {
+    NB200_OK = 0,
+    NB200_E_BADARG = 1,     /* null pointer, negative size, mismatched shapes */
+    NB200_E_CUDA = 2,       /* a CUDA runtime call failed; see nb200_last_cuda_error() */
+    NB200_E_OVERFLOW = 3,   /* a result length or work count does not fit int32 */
+    NB200_E_CAPACITY = 4,   /* caller-provided result arrays are too small */
+    NB200_E_TIMEOUT = 5,    /* a bounded device-side wait gave up (no hang, context intact) */
+    NB200_E_NOMEM = 6,      /* device allocation failed */
+    NB200_E_UNSUPPORTED = 7 /* size beyond a documented limit of the entry point */
+} nb200_status;
+
+/* CSR matrix: the field set of nacho's emitted CSR structs
+ * {dim_i_size, dim_j_size, dim_j_offsets, dim_j_length, dim_j_indices, values, nnz}
+ * (src/backend/tensor.cpp:13-61, include/backend/tensor.h:78-81). */
+typedef struct nb200_csr {
+    int32_t rows;     /* dim_i_size */
+    int32_t cols;     /* dim_j_size */
+    int32_t nnz;      /* dim_j_length */
+    int32_t *row_ptr; /* dim_j_offsets, rows + 1 entries */
+    int32_t *col;     /* dim_j_indices, nnz entries */
+    float *val;       /* values, nnz entries */
+} nb200_csr;
+
+/* COO3 tensor: three parallel coordinate arrays + values
+ * (src/backend/tensor.cpp:13-61 for the Compressed_non_unique, Singleton, Singleton levels of
+ * compiler.cpp:60-64). */
+typedef struct nb200_coo3 {
+    int32_t dims[3];
+    int32_t nnz;
+    int32_t *i, *j, *k; /* dim_{i,j,k}_indices, nnz entries each */
+    float *val;
+} nb200_coo3;
+
+/* CSF3 tensor: three compressed levels (compiler.cpp:44-48); the outermost level has no
+ * offsets array (src/backend/tensor.cpp:35-39). */
+typedef struct nb200_csf3 {
+    int32_t dims[3];
+    int32_t n_i, n_j, n_k; /* dim_{i,j,k}_length */
+    int32_t *i_idx;        /* dim_i_indices, n_i */
+    int32_t *j_ptr;        /* dim_j_offsets, n_i + 1 */
+    int32_t *j_idx;        /* dim_j_indices, n_j */
+    int32_t *k_ptr;        /* dim_k_offsets, n_j + 1 */
+    int32_t *k_idx;        /* dim_k_indices, n_k */
+    float *val;            /* values, n_k */
+} nb200_csf3;
+
+/* ---- library -------------------------------------------------------------------------- */
+
+int nb200_version(void);
+const char *nb200_strerror(int status);
+/* Text of the last CUDA error seen by the calling thread's most recent failing call. */
+const char *nb200_last_cuda_error(void);
+/* Release a result array of an allocating entry point: cudaFreeAsync(p, stream); NULL is
+ * ignored. Replaces cudaFreeWrapper (runtime/cuda_utils/cuda_utils.cu:7-11). */
+int nb200_free_async(void *p, void *stream);
+/* Release the per-device scratch pools the library keeps between calls. */
+int nb200_release_workspaces(void);
+/* Number of kernels this library has launched in this process so far. */
+uint64_t nb200_launch_count(void);
+
+/* Per-kernel device timing. While enabled, every kernel launch of the library is bracketed
+ * by CUDA events on its stream. nb200_profile_read synchronises those events and reports,
+ * for the kernel called `name`, the launches and their summed duration since the last
+ * nb200_profile_reset; nb200_profile_names writes a comma-separated list of kernel names. */
+int nb200_profile_enable(int on);
+int nb200_profile_reset(void);
+int nb200_profile_read(const char *name, int64_t *launches, double *total_ms);
+int nb200_profile_names(char *buf, size_t buf_len);
+
+/* ---- CSR element-wise ------------------------------------------------------------------- */
+
+/* Z = A + B, sorted union per row; a position present in both holds a + b, explicit zeros
+ * are kept. Replaces csr_add::csr_add_gpu_i32_f32 (kernel declared at compiler.cpp:112;
+ * partition src/backend/partition.cpp:813-993, count/fill src/backend/compute.cpp:152-411).
+ * Result: row_ptr rows+1, col/val nnz. Capacity that always suffices: nnz(A) + nnz(B). */
+int nb200_csr_add_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
+                      int32_t num_blocks, int32_t threads_per_block, void *stream);
+int nb200_csr_add_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
+                           int64_t capacity, void *stream);
+
+/* Z = A .* B, sorted intersection per row, value a * b. Replaces
+ * csr_mul::csr_mul_gpu_i32_f32 (compiler.cpp:116; src/backend/compute.cpp:434-440). An empty
+ * result has an all-zero row_ptr (src/backend/stitch_and_generate.cpp:168-220).
+ * Capacity that always suffices: min(nnz(A), nnz(B)). */
+int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
+                      int32_t num_blocks, int32_t threads_per_block, void *stream);
+int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
+                           int64_t capacity, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NACHO_B200_H */

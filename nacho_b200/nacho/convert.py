@@ -1,0 +1,95 @@
+"""torch tensors -> nacho tensor classes: same names, arguments and buffer order as the
+reference's converters (python/nacho/convert.py:23-118). Only CUDA targets exist here; asking
+for ``device="cpu"`` raises, because this package has no CPU kernels.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import nacho_ext as _ext
+
+__all__ = ["to_csr", "to_dcsr", "to_coo", "to_coo3", "to_csf3"]
+
+
+def _gpu_only(device) -> torch.device:
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise ValueError("nacho_b200 provides the GPU tensor classes only (device must be CUDA)")
+    return dev
+
+
+def _shape(*sizes) -> torch.Tensor:
+    return torch.tensor(list(sizes), dtype=torch.int32)
+
+
+def to_csr(csr, device="cuda"):
+    """torch CSR -> CSR_gpu (python/nacho/convert.py:23-31)."""
+    dev = _gpu_only(device)
+    return _ext.CSR_gpu(
+        csr.crow_indices().to(dtype=torch.int32, device=dev),
+        csr.col_indices().to(dtype=torch.int32, device=dev),
+        csr.values().to(dtype=torch.float32, device=dev),
+        _shape(csr.shape[0], csr.shape[1]),
+    )
+
+
+def to_dcsr(csr, device="cuda"):
+    """DCSR is outside the kernels this package implements (python/nacho/convert.py:34-56)."""
+    raise NotImplementedError("DCSR tensors are not part of the nacho_b200 hot path")
+
+
+def to_coo(coo, device="cuda"):
+    """2-D COO is outside the kernels this package implements (python/nacho/convert.py:58-67)."""
+    raise NotImplementedError("2-D COO tensors are not part of the nacho_b200 hot path")
+
+
+def _tensor(array, dtype, dev):
+    return torch.from_numpy(np.ascontiguousarray(array)).to(dtype=dtype, device=dev)
+
+
+def to_coo3(coordinates, values, shape, device="cuda"):
+    """Sorted, deduplicated (i, j, k) rows -> COO3_gpu (python/nacho/convert.py:70-87)."""
+    dev = _gpu_only(device)
+    return _ext.COO3_gpu(
+        _tensor(coordinates[:, 0], torch.int32, dev),
+        _tensor(coordinates[:, 1], torch.int32, dev),
+        _tensor(coordinates[:, 2], torch.int32, dev),
+        _tensor(values, torch.float32, dev),
+        torch.tensor(list(shape), dtype=torch.int32),
+    )
+
+
+def csf3_levels(coordinates):
+    """Level arrays of the CSF3 tree over sorted unique (i, j, k) rows: (i_idx, j_ptr, j_idx,
+    k_ptr, k_idx) as numpy arrays. Runs are found by comparing neighbours, which equals the
+    reference's np.unique-based run detection (python/nacho/convert.py:97-108) on sorted input."""
+    c = np.asarray(coordinates)
+    n = c.shape[0]
+    if n == 0:
+        z = np.zeros(0, np.int64)
+        return z, np.zeros(1, np.int64), z, np.zeros(1, np.int64), z
+    new_ij = np.ones(n, bool)
+    new_ij[1:] = (c[1:, 0] != c[:-1, 0]) | (c[1:, 1] != c[:-1, 1])
+    ij_starts = np.flatnonzero(new_ij)
+    ij_i = c[ij_starts, 0]
+    new_i = np.ones(len(ij_starts), bool)
+    new_i[1:] = ij_i[1:] != ij_i[:-1]
+    i_starts = np.flatnonzero(new_i)
+    return (ij_i[i_starts], np.append(i_starts, len(ij_starts)), c[ij_starts, 1],
+            np.append(ij_starts, n), c[:, 2])
+
+
+def to_csf3(coordinates, values, shape, device="cuda"):
+    """Sorted, deduplicated (i, j, k) rows -> CSF3_gpu (python/nacho/convert.py:90-118)."""
+    dev = _gpu_only(device)
+    i_idx, j_ptr, j_idx, k_ptr, k_idx = csf3_levels(coordinates)
+    return _ext.CSF3_gpu(
+        _tensor(i_idx, torch.int32, dev),
+        _tensor(j_ptr, torch.int32, dev),
+        _tensor(j_idx, torch.int32, dev),
+        _tensor(k_ptr, torch.int32, dev),
+        _tensor(k_idx, torch.int32, dev),
+        _tensor(values, torch.float32, dev),
+        torch.tensor(list(shape), dtype=torch.int32),
+    )

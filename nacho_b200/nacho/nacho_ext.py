@@ -1,0 +1,117 @@
+"""Host-side mirror of the reference's generated extension module ``nacho_ext``: the GPU tensor
+classes and the ``gpu_<kernel>_f32`` operators, with the names, argument order, defaults and
+read-only attributes the reference's binding generator emits
+(src/backend/generate_bindings.cpp:84-154 classes, :288-331 operators, :317-327 keyword names
+and the 256 x 256 default grid). Every operator forwards to the C ABI in ``libnacho_b200.so``;
+nothing is computed in Python or torch.
+
+Tensors are 1-D contiguous CUDA torch tensors (int32 indices, float32 values) and ``shape`` is
+a host int32 tensor, as in runtime/nacho_nb.h:22-31. Operands are borrowed; results are fresh
+torch tensors owned by the returned object.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _capi
+from .._capi import CsrStruct, lib
+
+__all__ = ["CSR_gpu", "gpu_csr_add_f32", "gpu_csr_mul_f32"]
+
+
+def _dev_array(t, dtype, name):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name}: expected a torch tensor")
+    if not t.is_cuda or t.dtype != dtype or t.dim() != 1 or not t.is_contiguous():
+        raise TypeError(f"{name}: expected a 1-D contiguous CUDA tensor of dtype {dtype}")
+    return t
+
+
+def _shape_array(t, rank, name="shape"):
+    if not isinstance(t, torch.Tensor):
+        t = torch.tensor(list(t), dtype=torch.int32)
+    if t.is_cuda or t.dtype != torch.int32 or t.dim() != 1 or t.numel() != rank:
+        raise TypeError(f"{name}: expected a host int32 tensor of {rank} entries")
+    return t.contiguous()
+
+
+def _stream_for(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class CSR_gpu:
+    """CSR matrix on the GPU: ``CSR_gpu(dim_j_offsets, dim_j_indices, values, shape)``
+    (attribute names as emitted by src/backend/generate_bindings.cpp:84-154)."""
+
+    __slots__ = ("_offsets", "_indices", "_values", "_shape")
+
+    def __init__(self, dim_j_offsets, dim_j_indices, values, shape):
+        self._offsets = _dev_array(dim_j_offsets, torch.int32, "dim_j_offsets")
+        self._indices = _dev_array(dim_j_indices, torch.int32, "dim_j_indices")
+        self._values = _dev_array(values, torch.float32, "values")
+        self._shape = _shape_array(shape, 2)
+        if self._indices.numel() != self._values.numel():
+            raise ValueError("dim_j_indices and values differ in length")
+        if self._offsets.numel() != int(self._shape[0]) + 1:
+            raise ValueError("dim_j_offsets must hold rows + 1 entries")
+        if not (self._offsets.device == self._indices.device == self._values.device):
+            raise ValueError("all buffers of a tensor must live on one device")
+
+    dim_j_offsets = property(lambda self: self._offsets)
+    dim_j_indices = property(lambda self: self._indices)
+    values = property(lambda self: self._values)
+    shape = property(lambda self: self._shape)
+
+    @property
+    def device(self):
+        return self._values.device
+
+    def _struct(self) -> CsrStruct:
+        return CsrStruct(int(self._shape[0]), int(self._shape[1]), self._values.numel(),
+                         self._offsets.data_ptr(), self._indices.data_ptr(), self._values.data_ptr())
+
+    def __repr__(self):
+        return f"CSR_gpu(shape=({int(self._shape[0])}, {int(self._shape[1])}), nnz={self._values.numel()})"
+
+
+def _same_device(*tensors):
+    dev = tensors[0].device
+    for t in tensors[1:]:
+        if t.device != dev:
+            raise ValueError("operands live on different devices")
+    return dev
+
+
+def _csr_result(rows, cols, dev):
+    return torch.empty(rows + 1, dtype=torch.int32, device=dev)
+
+
+def _csr_binary(entry, where, a: CSR_gpu, b: CSR_gpu, capacity: int) -> CSR_gpu:
+    if not isinstance(a, CSR_gpu) or not isinstance(b, CSR_gpu):
+        raise TypeError(f"{where}: operands must be CSR_gpu")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    with torch.cuda.device(dev):
+        row_ptr = _csr_result(sa.rows, sa.cols, dev)
+        col = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+        val = torch.empty(max(capacity, 1), dtype=torch.float32, device=dev)
+        sz = CsrStruct(sa.rows, sa.cols, 0, row_ptr.data_ptr(), col.data_ptr(), val.data_ptr())
+        status = entry(C.byref(sa), C.byref(sb), C.byref(sz), capacity, _stream_for(row_ptr))
+    _capi.check(status, where)
+    n = int(sz.nnz)
+    return CSR_gpu(row_ptr, col[:n], val[:n], torch.tensor([sz.rows, sz.cols], dtype=torch.int32))
+
+
+def gpu_csr_add_f32(a: CSR_gpu, b: CSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSR_gpu:
+    """Z = A + B (sorted union per row; explicit zeros kept). ``num_blocks`` and
+    ``threads_per_block`` are accepted for compatibility and ignored."""
+    return _csr_binary(lib.nb200_csr_add_f32_into, "gpu_csr_add_f32", a, b,
+                       a.values.numel() + b.values.numel())
+
+
+def gpu_csr_mul_f32(a: CSR_gpu, b: CSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSR_gpu:
+    """Z = A .* B (sorted intersection per row)."""
+    return _csr_binary(lib.nb200_csr_mul_f32_into, "gpu_csr_mul_f32", a, b,
+                       min(a.values.numel(), b.values.numel()))
