@@ -209,12 +209,15 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c3_csr_add_sigma0", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-rows-scale", type=float, default=0.125,
                     help="fraction of the workload's rows in the CPU-baseline sample")
+    ap.add_argument("--rows-scale", type=float, default=1.0,
+                    help="shrink the workload's rows and entries by this factor (profiling captures only; "
+                         "a line printed with a factor other than 1 is not a benchmark result)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -240,7 +243,7 @@ def main():
 
     spec = WORKLOADS[args.workload]
     op_fn = {"csr_add": nacho.gpu_csr_add_f32, "csr_mul": nacho.gpu_csr_mul_f32}[spec["op"]]
-    ops = make_operands(args.workload, rank, dev)
+    ops = make_operands(args.workload, rank, dev, rows_scale=args.rows_scale)
     tensors = [nacho.CSR_gpu(rp, col, val, torch.tensor([rows, cols], dtype=torch.int32))
                for rows, cols, rp, col, val in ops]
     rows = ops[0][0]
@@ -284,7 +287,7 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- per-kernel timing of the dominant kernel, same workload, events on the launching stream
-    fill_name = spec["op"] + "_fill"
+    fill_name = spec["op"] + "_fused"
     _capi.profile_reset()
     _capi.profile_enable(True)
     for _ in range(max(3, min(args.steps, 10))):
@@ -356,7 +359,7 @@ def main():
             "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "rows_per_gpu": rows, "operand_nnz_per_gpu": nnz_in,
+            "config": {"workload": args.workload, "rows_scale": args.rows_scale, "rows_per_gpu": rows, "operand_nnz_per_gpu": nnz_in,
                        "result_nnz_per_gpu": nnz_out, "algorithmic_bytes_per_gpu": nbytes,
                        "l2_policy": "inputs_larger_than_L2" if nbytes > 2 * 126e6 else "inputs fit L2 (latency-bound case)",
                        "parallelism": f"row blocks x{world}, all-gather of (rows, nnz) per step"},

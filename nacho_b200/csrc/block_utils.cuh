@@ -118,4 +118,68 @@ __device__ __forceinline__ int64_t warp_count_true(int64_t lo, int64_t hi, Pred 
     return lo;
 }
 
+// ---- bounded decoupled look-back ----------------------------------------------------------
+
+// Chained scan across CTAs in one pass: every tile publishes its own count ("aggregate") as
+// soon as it knows it, then walks back over its predecessors' words, 32 at a time, adding
+// aggregates until it meets a tile that already knows its inclusive prefix. A word carries a
+// 2-bit state and a 62-bit value and is written with one 8-byte store, so no fence is needed
+// between the two. Tiles must be numbered in the order their CTAs start (take the number from
+// an atomic ticket) so that a tile only ever waits on CTAs that are already running.
+//
+// Every wait is bounded: after LOOKBACK_POLL_LIMIT polls of one word the walk gives up,
+// records the tile in `status` and returns -1; the caller then skips its writes. The tile
+// still publishes a prefix so that its successors do not wait on it in turn.
+constexpr uint64_t LB_AGGREGATE = 1ull << 62;
+constexpr uint64_t LB_PREFIX = 2ull << 62;
+constexpr uint64_t LB_VALUE_MASK = (1ull << 62) - 1;
+constexpr int LOOKBACK_POLL_LIMIT = 1 << 22;
+constexpr int ERR_LOOKBACK_TIMEOUT = 1;
+
+// Called by all 32 lanes of one warp. Returns the sum of the aggregates of tiles [0, t).
+__device__ __forceinline__ int64_t lookback_exclusive(volatile uint64_t *state, int t, int64_t aggregate,
+                                                      DeviceStatus *status) {
+    if (lane_id() == 0) state[t] = (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)aggregate;
+    if (t == 0) return 0;
+    int64_t exclusive = 0;
+    bool failed = false;
+    for (int pos = t - 1;; pos -= 32) {
+        const int idx = pos - lane_id();
+        uint64_t s = LB_PREFIX;  // lanes that fall before tile 0 stand for an empty prefix
+        bool timed_out = false;
+        if (idx >= 0) {
+            int polls = 0;
+            s = state[idx];
+            while ((s >> 62) == 0) {
+                if (++polls >= LOOKBACK_POLL_LIMIT) {
+                    timed_out = true;
+                    break;
+                }
+                __nanosleep(64);
+                s = state[idx];
+            }
+        }
+        if (__any_sync(FULL_MASK, timed_out)) {
+            failed = true;
+            break;
+        }
+        const unsigned prefix_lanes = __ballot_sync(FULL_MASK, (s >> 62) == 2);
+        const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 32;
+        long long v = lane_id() <= first ? (long long)(s & LB_VALUE_MASK) : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
+        exclusive += v;
+        if (prefix_lanes) break;
+    }
+    if (failed) {
+        if (lane_id() == 0) {
+            if (atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
+            state[t] = LB_PREFIX;  // unblock successors; the call reports the failure
+        }
+        return -1;
+    }
+    if (lane_id() == 0) state[t] = LB_PREFIX | (uint64_t)(exclusive + aggregate);
+    return exclusive;
+}
+
 }  // namespace nb200

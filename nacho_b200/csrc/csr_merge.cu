@@ -16,18 +16,22 @@
 // :273-411, value expressions :426-440, empty-result path
 // src/backend/stitch_and_generate.cpp:168-220.
 #include <algorithm>
+#include <cstring>
 
 #include "block_utils.cuh"
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace nb200 {
 
 namespace {
 
 constexpr int NT = 256;
+#ifndef CSR2_MIN_CTAS
+#define CSR2_MIN_CTAS 4
+#endif
 
 enum SetOp { OP_UNION = 0, OP_INTERSECT = 1 };
-enum Pass { PASS_COUNT = 0, PASS_FILL = 1 };
 
 struct CsrIn {
     const int32_t *rp;
@@ -118,78 +122,103 @@ struct KeyTraits<uint64_t> {
     __device__ static __forceinline__ uint64_t make(uint32_t row, uint32_t col, int) { return ((uint64_t)row << 32) | col; }
 };
 
-// Writes `value` into out_rp[first .. last] (inclusive), the whole warp cooperating.
-__device__ __forceinline__ void warp_fill_rows(int32_t *out_rp, int64_t first, int64_t last, int32_t value) {
-    for (int64_t r = first + lane_id(); r <= last; r += 32) out_rp[r] = value;
-}
+// What one launch of the tile kernel does.
+//   MODE_COUNT  count the tile's result entries (first pass of the two-pass scheme)
+//   MODE_FILL   write the result; the tile's output base comes from the scanned counts
+//   MODE_FUSED  single pass: count, obtain the base by look-back over earlier tiles, write
+enum Mode { MODE_COUNT = 0, MODE_FILL = 1, MODE_FUSED = 2 };
 
-template <typename KeyT, int VT, int OP, int PASS>
-__device__ __forceinline__ void csr2_tile_body(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits,
-                                               int32_t *tile_count, const CsrOut &Z, unsigned char *smem_raw,
-                                               int *scan_tmp) {
+// Device-side control block of a fused launch.
+struct FusedCtl {
+    int ticket;           // next tile number to hand out
+    DeviceStatus status;  // bounded-wait failures
+    long long total;      // result entries, written by the last tile
+};
+
+// Generic tile body: any key width, plain loads and stores. Used for the tiles whose rows do not
+// fit a 32-bit composite key; the common case takes csr2_tile_fast below.
+template <typename KeyT, int VT, int OP, int MODE>
+__device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits,
+                                               const int t, int32_t *tile_count, volatile uint64_t *tile_state,
+                                               FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
+                                               int *scan_tmp, int *thread_rank, unsigned *thread_emit) {
     using KT = KeyTraits<KeyT>;
     constexpr int CAP = NT * VT;  // most merged entries a tile can hold
+    constexpr bool WRITES = MODE != MODE_COUNT;
     const int tid = threadIdx.x;
-    const int t = blockIdx.x;
     const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
     const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
     const int n = na + nb;
 
-    KeyT *keys = reinterpret_cast<KeyT *>(smem_raw);  // [0, na) from A, [na, n) from B
-    float *vals = reinterpret_cast<float *>(smem_raw + sizeof(KeyT) * (CAP + 2));
+    // Shared layout: keys of A, a sentinel, keys of B, a sentinel, then VT words of slack so
+    // that the merge may read a little past the end; values mirror the same positions.
+    constexpr int KEY_SLOTS = CAP + 2 + VT;
+    KeyT *kx = reinterpret_cast<KeyT *>(smem_raw);
+    KeyT *ky = kx + na + 1;
+    float *vx = reinterpret_cast<float *>(smem_raw + sizeof(KeyT) * KEY_SLOTS);
+    float *vy = vx + na + 1;
 
     // ---- stage columns (and values) in shared memory, coalesced
-    for (int i = tid; i < na; i += NT) keys[i] = (KeyT)(uint32_t)ld_nc(A.col + a0 + i);
-    for (int i = tid; i < nb; i += NT) keys[na + i] = (KeyT)(uint32_t)ld_nc(B.col + b0 + i);
-    if (PASS == PASS_FILL) {
-        for (int i = tid; i < na; i += NT) vals[i] = ld_nc(A.val + a0 + i);
-        for (int i = tid; i < nb; i += NT) vals[na + i] = ld_nc(B.val + b0 + i);
+    for (int i = tid; i < na; i += NT) kx[i] = (KeyT)(uint32_t)ld_nc(A.col + a0 + i);
+    for (int i = tid; i < nb; i += NT) ky[i] = (KeyT)(uint32_t)ld_nc(B.col + b0 + i);
+    if (WRITES) {
+        for (int i = tid; i < na; i += NT) vx[i] = ld_nc(A.val + a0 + i);
+        for (int i = tid; i < nb; i += NT) vy[i] = ld_nc(B.val + b0 + i);
+    }
+    // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over
+    // the threads); kept in registers for the row-offset pass at the end
+    const int64_t my_row = (int64_t)i0 + 1 + tid;
+    int32_t my_sa = 0, my_sb = 0;
+    if (my_row <= i1) {
+        my_sa = ld_nc(A.rp + my_row) - a0;
+        my_sb = ld_nc(B.rp + my_row) - b0;
     }
     __syncthreads();
 
     // ---- mark the first entry of every row that starts inside the tile with its row number
     // relative to i0 (max wins where empty rows share a start), then spread it forward with a
     // running maximum so that every entry carries its row in the high bits of its key.
-    for (int64_t r = (int64_t)i0 + 1 + tid; r <= i1; r += NT) {
+    for (int64_t r = my_row; r <= i1; r += NT) {
         const uint32_t rr = (uint32_t)(r - i0);
-        const int64_t sa = (int64_t)ld_nc(A.rp + r) - a0;
-        if (sa >= 0 && sa < na) {
-            if (sizeof(KeyT) == 4) atomicMax(reinterpret_cast<unsigned *>(keys) + sa, (rr << cbits) | (unsigned)keys[sa] & ((1u << cbits) - 1u));
-            else atomicMax(reinterpret_cast<unsigned *>(keys) + 2 * sa + 1, rr);
+        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
+        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
+        if (sa < na) {
+            if (sizeof(KeyT) == 4) atomicMax(reinterpret_cast<unsigned *>(kx) + sa, (rr << cbits) | ((unsigned)kx[sa] & ((1u << cbits) - 1u)));
+            else atomicMax(reinterpret_cast<unsigned *>(kx) + 2 * sa + 1, rr);
         }
-        const int64_t sb = (int64_t)ld_nc(B.rp + r) - b0;
-        if (sb >= 0 && sb < nb) {
-            if (sizeof(KeyT) == 4) atomicMax(reinterpret_cast<unsigned *>(keys) + na + sb, (rr << cbits) | (unsigned)keys[na + sb] & ((1u << cbits) - 1u));
-            else atomicMax(reinterpret_cast<unsigned *>(keys) + 2 * (na + sb) + 1, rr);
+        if (sb < nb) {
+            if (sizeof(KeyT) == 4) atomicMax(reinterpret_cast<unsigned *>(ky) + sb, (rr << cbits) | ((unsigned)ky[sb] & ((1u << cbits) - 1u)));
+            else atomicMax(reinterpret_cast<unsigned *>(ky) + 2 * sb + 1, rr);
         }
     }
     __syncthreads();
     {
+        // thread tid owns merged-array slots [tid*VT, tid*VT+VT): first the A part, then B
         const int lo = tid * VT, hi = min(lo + VT, n);
         unsigned ma = 0, mb = 0;
         for (int i = lo; i < hi; ++i) {
-            const unsigned rr = KT::row_of(keys[i], cbits);
-            if (i < na) ma = max(ma, rr); else mb = max(mb, rr);
+            if (i < na) ma = max(ma, KT::row_of(kx[i], cbits)); else mb = max(mb, KT::row_of(ky[i - na], cbits));
         }
         unsigned ea, eb;
         block_excl_max2<NT>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
         for (int i = lo; i < hi; ++i) {
-            const KeyT k = keys[i];
-            const unsigned rr = KT::row_of(k, cbits);
             if (i < na) {
-                ea = max(ea, rr);
-                keys[i] = KT::make(ea, KT::col_of(k, cbits), cbits);
+                const KeyT k = kx[i];
+                ea = max(ea, KT::row_of(k, cbits));
+                kx[i] = KT::make(ea, KT::col_of(k, cbits), cbits);
             } else {
-                eb = max(eb, rr);
-                keys[i] = KT::make(eb, KT::col_of(k, cbits), cbits);
+                const KeyT k = ky[i - na];
+                eb = max(eb, KT::row_of(k, cbits));
+                ky[i - na] = KT::make(eb, KT::col_of(k, cbits), cbits);
             }
         }
+        if (tid < VT + 1) ky[nb + tid] = KT::INF;
+        if (tid == 0) kx[na] = KT::INF;
     }
     __syncthreads();
 
     // ---- split the tile among threads: merge-path diagonal tid * VT, ties take A first
-    const KeyT *kx = keys, *ky = keys + na;
     const int diag = min(tid * VT, n);
     int x, y;
     {
@@ -201,126 +230,413 @@ __device__ __forceinline__ void csr2_tile_body(const CsrIn &A, const CsrIn &B, c
         x = lo;
         y = diag - lo;
     }
+    const int x0 = x, y0 = y;
 
-    // ---- merge VT entries in registers
+    // ---- merge VT entries; straight-line code, no divergent branches. Bit i of `from_a` says
+    // entry i came from A, of `twin` that the same column is in B too, of `emit` that the
+    // entry goes to the result.
     KeyT key[VT];
-    float val[VT];
-    unsigned emit = 0;
-    KeyT prev_any = KT::INF;  // key of the merged entry just before this thread's first
+    unsigned from_a = 0, twin = 0, emit = 0;
     {
-        KeyT hx = x < na ? kx[x] : KT::INF;
-        KeyT hy = y < nb ? ky[y] : KT::INF;
+        const int valid = min(VT, n - diag);
+        KeyT hx = kx[x], hy = ky[y];
         KeyT last_x = x > 0 ? kx[x - 1] : KT::INF;
-        const KeyT last_y = y > 0 ? ky[y - 1] : KT::INF;
-        if (x > 0 && y > 0) prev_any = max(last_x, last_y);
-        else if (x > 0) prev_any = last_x;
-        else if (y > 0) prev_any = last_y;
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
-            const bool valid = diag + i < n;
-            const bool take_x = hx <= hy;
-            if (take_x) {
-                const bool both = hx == hy;
-                key[i] = hx;
-                if (PASS == PASS_FILL && valid) {
-                    const float va = vals[x];
-                    if (OP == OP_UNION) val[i] = both ? va + vals[na + y] : va;
-                    else val[i] = both ? va * vals[na + y] : 0.f;
-                }
-                if (valid && (OP == OP_UNION || both)) emit |= 1u << i;
-                last_x = hx;
-                ++x;
-                hx = x < na ? kx[x] : KT::INF;
-            } else {
-                key[i] = hy;
-                if (PASS == PASS_FILL && valid) val[i] = vals[na + y];
-                if (valid && OP == OP_UNION && hy != last_x) emit |= 1u << i;
-                ++y;
-                hy = y < nb ? ky[y] : KT::INF;
-            }
+            const bool ok = i < valid;
+            const bool tx = hx <= hy;
+            const bool both = hx == hy;
+            key[i] = tx ? hx : hy;
+            const bool out = OP == OP_UNION ? (tx || hy != last_x) : (tx && both);
+            from_a |= (unsigned)tx << i;
+            twin |= (unsigned)(tx && both) << i;
+            emit |= (unsigned)(ok && out) << i;
+            last_x = tx ? hx : last_x;
+            x += tx;
+            y += !tx;
+            hx = kx[x];
+            hy = ky[y];
         }
     }
 
-    // ---- rank the survivors
+    // ---- rank the survivors inside the tile
     int total;
     const int mine = __popc(emit);
-    int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // syncs: all reads of keys/vals are done
-    if (PASS == PASS_COUNT) {
+    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // syncs: key reads are done
+    if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
         return;
     }
 
-    const int32_t base = tile_count[t];  // exclusive prefix over tiles, made between the passes
-
-    // ---- row offsets: an entry that opens a new row closes every row before it
-    {
-        uint32_t prev_row = prev_any == KT::INF ? 0u : KT::row_of(prev_any, cbits);
-        int r = rank;
-#pragma unroll
-        for (int i = 0; i < VT; ++i) {
-            const bool valid = diag + i < n;
-            const uint32_t row = valid ? KT::row_of(key[i], cbits) : prev_row;
-            const uint32_t gap = row - prev_row;
-            if (gap > 0 && gap <= 32) {
-                for (uint32_t g = 1; g <= gap; ++g) Z.rp[(int64_t)i0 + prev_row + g] = base + r;
-            }
-            unsigned big = __ballot_sync(FULL_MASK, gap > 32);
-            while (big) {
-                const int src = __ffs(big) - 1;
-                big &= big - 1;
-                const uint32_t p = __shfl_sync(FULL_MASK, prev_row, src);
-                const uint32_t q = __shfl_sync(FULL_MASK, row, src);
-                const int v = __shfl_sync(FULL_MASK, r, src);
-                warp_fill_rows(Z.rp, (int64_t)i0 + p + 1, (int64_t)i0 + q, base + v);
-            }
-            prev_row = row;
-            r += (emit >> i) & 1u;
+    // ---- output base of the tile
+    long long base;
+    if (MODE == MODE_FILL) {
+        base = tile_count[t];  // exclusive prefix over tiles, made between the two passes
+    } else {
+        __shared__ long long s_base;
+        if (warp_id() == 0) {
+            const int64_t b = lookback_exclusive(tile_state, t, total, &ctl->status);
+            if (lane_id() == 0) s_base = b;
         }
-        // the thread holding the tile's last entry closes the rows up to the next tile's first
-        const bool owns_last = diag < n && diag + VT >= n;
-        const uint32_t end_row = (uint32_t)(i1 - i0);
-        unsigned tail = __ballot_sync(FULL_MASK, owns_last && end_row > prev_row);
-        if (tail) {
-            const int src = __ffs(tail) - 1;
-            const uint32_t p = __shfl_sync(FULL_MASK, prev_row, src);
-            warp_fill_rows(Z.rp, (int64_t)i0 + p + 1, (int64_t)i0 + end_row, base + total);
-        }
-        if (t == 0 && tid == 0) Z.rp[0] = 0;
+        thread_rank[tid] = rank;
+        thread_emit[tid] = emit;
+        __syncthreads();
+        base = s_base;
+        if (base < 0) return;  // a bounded wait gave up; the host reports it
+        if (t == (int)gridDim.x - 1 && tid == 0) ctl->total = base + total;
+    }
+    if (MODE == MODE_FILL) {
+        thread_rank[tid] = rank;
+        thread_emit[tid] = emit;
+        __syncthreads();
     }
 
-    // ---- compact through shared memory (the staging area reuses the key/value arrays; the
-    // scan above already separated the last read from the first write) and store coalesced
+    // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
+    // tile those are the survivors among the first d = (A entries before row r) + (B entries
+    // before row r) merged entries, read off the per-thread ranks. The tile owns rows
+    // i0+1 .. i1 (the next tile's first row).
+    for (int64_t r = my_row; r <= i1; r += NT) {
+        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
+        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
+        const int d = sa + sb;
+        const int owner = d / VT, off = d - owner * VT;
+        const int before = owner >= NT ? total : thread_rank[owner] + __popc(thread_emit[owner] & ((1u << off) - 1u));
+        Z.rp[r] = (int32_t)(base + before);
+    }
+    if (t == 0 && tid == 0) Z.rp[0] = 0;
+
+    // ---- fetch values, compact through shared memory (the staging area reuses the key
+    // arrays; the syncs above separate the last key read from the first write), store coalesced
     int32_t *out_col = reinterpret_cast<int32_t *>(smem_raw);
-    float *out_val = reinterpret_cast<float *>(smem_raw) + (CAP + 2);
+    // 64-bit keys leave room for both staging arrays inside the key area; 32-bit keys need a
+    // third array after the values. Either way the footprint is 12 bytes per slot.
+    float *out_val = sizeof(KeyT) == 8 ? reinterpret_cast<float *>(smem_raw) + KEY_SLOTS
+                                       : reinterpret_cast<float *>(smem_raw) + 2 * KEY_SLOTS;
     {
-        int r = rank;
+        int r = rank, xi = x0, yi = y0;
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
+            const bool tx = (from_a >> i) & 1u;
+            const bool both = (twin >> i) & 1u;
+            const float va = vx[xi], vb = vy[yi];  // always inside the slack-padded arrays
+            float v = tx ? va : vb;
+            v = both ? (OP == OP_UNION ? va + vb : va * vb) : v;
             if ((emit >> i) & 1u) {
                 out_col[r] = (int32_t)KT::col_of(key[i], cbits);
-                out_val[r] = val[i];
-                ++r;
+                out_val[r] = v;
             }
+            r += (emit >> i) & 1u;
+            xi += tx;
+            yi += !tx;
         }
     }
     __syncthreads();
     for (int i = tid; i < total; i += NT) {
-        Z.col[(int64_t)base + i] = out_col[i];
-        Z.val[(int64_t)base + i] = out_val[i];
+        Z.col[base + i] = out_col[i];
+        Z.val[base + i] = out_val[i];
     }
 }
 
-template <int VT, int OP, int PASS>
-__global__ void __launch_bounds__(NT) k_csr2_tile(CsrIn A, CsrIn B, Cuts cuts, int cbits, int32_t *tile_count, CsrOut Z) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+// Shared-memory plan of the fast tile body, in 4-byte words. Keys and values use the same
+// word positions: A's entry e sits at word oa + e and B's at word obv + e, where oa and obv
+// are chosen so that a global address on a 16-byte boundary lands on a 16-byte boundary in
+// shared memory too (what a bulk copy needs). The two output staging arrays follow.
+template <int VT>
+struct FastPlan {
+    static constexpr int CAP = NT * VT;
+    static constexpr int CH = (VT + 1 + 3) & ~3;                   // words each thread scans
+    static constexpr int SLOTS = NT * CH + ((VT + 4 + 3) & ~3);    // key words = value words
+    static constexpr int OUT = CAP + 8;                            // staging words per array
+    static constexpr size_t BYTES = 4 * (size_t)(2 * SLOTS + 2 * OUT);
+    static_assert(NT * CH >= CAP + 12, "scan range must cover the padded tile");
+};
+
+constexpr int MBAR_POLL_LIMIT = 1 << 24;
+constexpr int ERR_COPY_TIMEOUT = 2;
+
+// Number of 4-byte elements from `p` up to the next 16-byte boundary (0..3).
+__device__ __forceinline__ int head_elems(const void *p) {
+    return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
+}
+
+// Fast tile body: 32-bit composite keys; operands staged with bulk copies, result written with
+// bulk stores, so that neither costs per-entry instructions.
+template <int VT, int OP, int MODE>
+__device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits,
+                                               const int t, int32_t *tile_count, volatile uint64_t *tile_state,
+                                               FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
+                                               int *scan_tmp, int *thread_rank, unsigned *thread_emit,
+                                               uint64_t *mbar) {
+    using P = FastPlan<VT>;
+    constexpr bool WRITES = MODE != MODE_COUNT;
+    constexpr uint32_t INF = 0xffffffffu;
+    const int tid = threadIdx.x;
+    const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
+    const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
+    const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
+    const int n = na + nb;
+    const uint32_t cmask = (1u << cbits) - 1u;
+
+    uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw);
+    float *vals = reinterpret_cast<float *>(keys + P::SLOTS);
+    int32_t *out_col = reinterpret_cast<int32_t *>(vals + P::SLOTS);
+    float *out_val = reinterpret_cast<float *>(out_col + P::OUT);
+
+    const int32_t *ga_col = A.col + a0, *gb_col = B.col + b0;
+    const float *ga_val = A.val + a0, *gb_val = B.val + b0;
+    const int ha = head_elems(ga_col), hb = head_elems(gb_col);
+    const int oa = (4 - ha) & 3;                 // word of A's entry 0
+    const int ob = (oa + na + 1 + 3) & ~3;       // first word of B's region (A's sentinel before it)
+    const int obv = ob + ((4 - hb) & 3);         // word of B's entry 0
+    const int scan_end = (obv + nb + 3) & ~3;
+    uint32_t *kx = keys + oa, *ky = keys + obv;
+    const float *vx = vals + oa, *vy = vals + obv;
+
+    // ---- stage the tile. Thread 0 hands the 16-byte-aligned interior of each array to the copy
+    // engine; a few other threads load the ragged ends (at most 3 entries each side).
+    // Value arrays whose alignment differs from their column arrays' take plain loads.
+    const bool va_bulk = !WRITES || head_elems(ga_val) == ha, vb_bulk = !WRITES || head_elems(gb_val) == hb;
+    const int head_a = min(na, ha), head_b = min(nb, hb);
+    const int nva = (na - head_a) >> 2, nvb = (nb - head_b) >> 2;  // 16-byte vectors in the interior
+    if (tid == 0) {
+        uint32_t bytes = 16u * (uint32_t)(nva + nvb);
+        if (WRITES) bytes += (va_bulk ? 16u * nva : 0u) + (vb_bulk ? 16u * nvb : 0u);
+        mbar_arrive_expect_tx(mbar, bytes);
+        if (nva) bulk_load(kx + head_a, ga_col + head_a, 16u * nva, mbar);
+        if (nvb) bulk_load(ky + head_b, gb_col + head_b, 16u * nvb, mbar);
+        if (WRITES && va_bulk && nva) bulk_load(vals + oa + head_a, ga_val + head_a, 16u * nva, mbar);
+        if (WRITES && vb_bulk && nvb) bulk_load(vals + obv + head_b, gb_val + head_b, 16u * nvb, mbar);
+    }
+    if (tid >= 32 && tid < 32 + 12) {  // ragged ends: 3 head + 3 tail slots for A, then for B
+        const int k = tid - 32;
+        const bool is_b = k >= 6;
+        const int e = is_b ? k - 6 : k;
+        const int count = is_b ? nb : na, head = is_b ? head_b : head_a, nv = is_b ? nvb : nva;
+        const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
+        const bool live = e < 3 ? e < head : idx < count;
+        if (live) {
+            const int w = (is_b ? obv : oa) + idx;
+            keys[w] = (uint32_t)ld_nc((is_b ? gb_col : ga_col) + idx);
+            if (WRITES && (is_b ? vb_bulk : va_bulk)) vals[w] = ld_nc((is_b ? gb_val : ga_val) + idx);
+        }
+    }
+    if (WRITES && !va_bulk) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
+    if (WRITES && !vb_bulk) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
+    // padding words that precede live keys must read as "no row mark"; the end-of-list
+    // sentinels are all-ones, which the row spreading below leaves intact
+    if (tid >= 64 && tid < 64 + 3) { if (tid - 64 < oa) keys[tid - 64] = 0u; }
+    if (tid >= 68 && tid < 68 + 3) { if (ob + (tid - 68) < obv) keys[ob + (tid - 68)] = 0u; }
+    if (tid == 72) keys[oa + na] = INF;
+    if (tid >= 96 && tid < 96 + VT + 1) keys[obv + nb + (tid - 96)] = INF;
+
+    // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over the
+    // threads); kept in registers for the row-offset pass at the end
+    const int64_t my_row = (int64_t)i0 + 1 + tid;
+    int32_t my_sa = 0, my_sb = 0;
+    if (my_row <= i1) {
+        my_sa = ld_nc(A.rp + my_row) - a0;
+        my_sb = ld_nc(B.rp + my_row) - b0;
+    }
+    const bool landed = mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);
+    if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
+        if (tid == 0) {
+            if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
+            if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;  // successors must not wait on this tile
+            mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
+        }
+        return;
+    }
+
+    // ---- mark the first entry of every row that starts inside the tile with its row number
+    // relative to i0, in the bits above the column (max wins where empty rows share a start)
+    for (int64_t r = my_row; r <= i1; r += NT) {
+        const uint32_t rr = (uint32_t)(r - i0);
+        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
+        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
+        if (sa < na) atomicMax(kx + sa, (rr << cbits) | (kx[sa] & cmask));
+        if (sb < nb) atomicMax(ky + sb, (rr << cbits) | (ky[sb] & cmask));
+    }
+    __syncthreads();
+
+    // ---- spread the marks forward (running maximum) so that every key carries its row.
+    // Each thread owns CH consecutive words; A's region and B's region run separately.
+    {
+        constexpr int NV = P::CH / 4;
+        const int w_base = tid * P::CH;
+        uint4 q[NV];
+        unsigned ma = 0, mb = 0;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int w = w_base + 4 * j;
+            q[j] = w < scan_end ? *reinterpret_cast<const uint4 *>(keys + w) : make_uint4(0, 0, 0, 0);
+            const unsigned m = max(max(q[j].x & ~cmask, q[j].y & ~cmask), max(q[j].z & ~cmask, q[j].w & ~cmask));
+            if (w < ob) ma = max(ma, m); else mb = max(mb, m);
+        }
+        unsigned ea, eb;
+        block_excl_max2<NT>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int w = w_base + 4 * j;
+            const bool in_a = w < ob;
+            unsigned run = in_a ? ea : eb;
+            uint4 v = q[j];
+            run = max(run, v.x & ~cmask); v.x = run | (v.x & cmask);
+            run = max(run, v.y & ~cmask); v.y = run | (v.y & cmask);
+            run = max(run, v.z & ~cmask); v.z = run | (v.z & cmask);
+            run = max(run, v.w & ~cmask); v.w = run | (v.w & cmask);
+            if (in_a) ea = run; else eb = run;
+            if (w < scan_end) *reinterpret_cast<uint4 *>(keys + w) = v;
+        }
+    }
+    __syncthreads();
+
+    // ---- split the tile among threads: merge-path diagonal tid * VT, ties take A first
+    const int diag = min(tid * VT, n);
+    int x, y;
+    {
+        int lo = max(0, diag - nb), hi = min(diag, na);
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (kx[mid] <= ky[diag - 1 - mid]) lo = mid + 1; else hi = mid;
+        }
+        x = lo;
+        y = diag - lo;
+    }
+    const int x0 = x, y0 = y;
+
+    // ---- merge VT entries; straight-line code. Bit i of `from_a`: entry i came from A; of
+    // `twin`: the same (row, column) is in B too; of `emit`: the entry goes to the result.
+    unsigned from_a = 0, twin = 0, emit = 0;
+    {
+        const int valid = min(VT, n - diag);
+        uint32_t hx = kx[x], hy = ky[y];
+        uint32_t last_x = x > 0 ? kx[x - 1] : INF;
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = hx <= hy;
+            const bool both = hx == hy;
+            const bool out = OP == OP_UNION ? (tx || hy != last_x) : both;
+            from_a |= (unsigned)tx << i;
+            twin |= (unsigned)both << i;
+            emit |= (unsigned)(out && i < valid) << i;
+            last_x = tx ? hx : last_x;
+            x += tx;
+            y += !tx;
+            hx = kx[x];
+            hy = ky[y];
+        }
+    }
+
+    // ---- rank the survivors inside the tile
+    int total;
+    const int mine = __popc(emit);
+    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);
+    if (MODE == MODE_COUNT) {
+        if (tid == 0) tile_count[t] = total;
+        return;
+    }
+
+    // ---- output base of the tile
+    __shared__ long long s_base;
+    thread_rank[tid] = rank;
+    thread_emit[tid] = emit;
+    if (MODE == MODE_FUSED && warp_id() == 0) {
+        const int64_t b = lookback_exclusive(tile_state, t, total, &ctl->status);
+        if (lane_id() == 0) s_base = b;
+    }
+    __syncthreads();
+    const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
+    if (base < 0) return;  // a bounded wait gave up; the host reports it
+    if (MODE == MODE_FUSED && t == (int)gridDim.x - 1 && tid == 0) ctl->total = base + total;
+
+    // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
+    // tile those are the survivors among the first d = (A entries before row r) + (B entries
+    // before row r) merged entries, read off the per-thread ranks. The tile owns rows
+    // i0+1 .. i1 (the next tile's first row).
+    for (int64_t r = my_row; r <= i1; r += NT) {
+        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
+        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
+        const int d = sa + sb;
+        const int owner = d / VT, off = d - owner * VT;
+        const int before = owner >= NT ? total : thread_rank[owner] + __popc(thread_emit[owner] & ((1u << off) - 1u));
+        Z.rp[r] = (int32_t)(base + before);
+    }
+    if (t == 0 && tid == 0) Z.rp[0] = 0;
+
+    // ---- gather columns and values of the survivors into the staging arrays, shifted so that
+    // 16-byte boundaries of the result arrays fall on 16-byte boundaries of shared memory
+    int32_t *gz_col = Z.col + base;
+    float *gz_val = Z.val + base;
+    const int sc = (4 - head_elems(gz_col)) & 3, sv = (4 - head_elems(gz_val)) & 3;
+    {
+        int r = rank, xi = x0, yi = y0;
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = (from_a >> i) & 1u;
+            const bool both = (twin >> i) & 1u;
+            const bool out = (emit >> i) & 1u;
+            const int w = tx ? oa + xi : obv + yi;
+            const float v1 = vals[w], v2 = vy[yi];  // both reads stay inside the padded arrays
+            const float v = both ? (OP == OP_UNION ? v1 + v2 : v1 * v2) : v1;
+            if (out) {
+                out_col[sc + r] = (int32_t)(keys[w] & cmask);
+                out_val[sv + r] = v;
+            }
+            r += out;
+            xi += tx;
+            yi += !tx;
+        }
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    // ---- store: aligned interior by bulk store, ragged ends by a few threads
+    const int hc = min(total, (4 - sc) & 3), hv = min(total, (4 - sv) & 3);
+    const int nvc = (total - hc) >> 2, nvv = (total - hv) >> 2;
+    if (tid == 0) {
+        if (nvc) bulk_store(gz_col + hc, out_col + sc + hc, 16u * nvc);
+        if (nvv) bulk_store(gz_val + hv, out_val + sv + hv, 16u * nvv);
+        bulk_commit();
+    }
+    if (tid >= 32 && tid < 32 + 12) {
+        const int k = tid - 32;
+        const bool is_val = k >= 6;
+        const int e = is_val ? k - 6 : k;
+        const int head = is_val ? hv : hc, nv = is_val ? nvv : nvc;
+        const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
+        const bool live = e < 3 ? e < head : idx < total;
+        if (live) {
+            if (is_val) gz_val[idx] = out_val[sv + idx];
+            else gz_col[idx] = out_col[sc + idx];
+        }
+    }
+    if (tid == 0) bulk_wait_read_all();  // shared memory must outlive the engine's reads
+}
+
+template <int VT, int OP, int MODE>
+__global__ void __launch_bounds__(NT, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, CsrIn B, Cuts cuts, int cbits, int32_t *tile_count,
+                                                  uint64_t *tile_state, FusedCtl *ctl, CsrOut Z) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
-    const int t = blockIdx.x;
+    __shared__ int thread_rank[NT];
+    __shared__ unsigned thread_emit[NT];
+    __shared__ __align__(8) uint64_t mbar;
+    __shared__ int s_tile;
+    int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        // number tiles in the order CTAs start, so a tile only waits on running CTAs
+        if (MODE == MODE_FUSED) s_tile = atomicAdd(&ctl->ticket, 1);
+        mbar_init(&mbar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (MODE == MODE_FUSED) t = s_tile;
     // 32-bit composite keys hold (row in tile << cbits | column) when that fits; tiles that
     // span too many rows for that (long runs of empty rows) fall back to 64-bit keys.
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
     const bool narrow = cbits < 32 && (nr << cbits) < 0xffffffffull;
-    if (narrow) csr2_tile_body<uint32_t, VT, OP, PASS>(A, B, cuts, cbits, tile_count, Z, smem_raw, scan_tmp);
-    else csr2_tile_body<uint64_t, VT, OP, PASS>(A, B, cuts, 32, tile_count, Z, smem_raw, scan_tmp);
+    if (narrow) csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar);
+    else csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit);
 }
 
 // Exclusive prefix of the per-tile counts, in place, by one CTA; the grand total goes to
@@ -369,7 +685,7 @@ constexpr int VT_CSR2 = 11;
 
 template <int VT>
 constexpr size_t csr2_smem_bytes() {
-    return (sizeof(uint64_t) + sizeof(float)) * (size_t)(NT * VT + 2);
+    return std::max<size_t>(FastPlan<VT>::BYTES, 12 * (size_t)(NT * VT + 2 + VT));
 }
 
 int col_bits(int32_t cols) {
@@ -384,11 +700,11 @@ int check_csr(const nb200_csr *m, bool need_arrays) {
     return NB200_OK;
 }
 
-template <int OP, int PASS>
+template <int OP, int MODE>
 cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits, int32_t *tile_count,
-                        const CsrOut &Z, int num_tiles, cudaStream_t stream) {
+                        uint64_t *tile_state, FusedCtl *ctl, const CsrOut &Z, int num_tiles, cudaStream_t stream) {
     constexpr size_t smem = csr2_smem_bytes<VT_CSR2>();
-    auto kernel = k_csr2_tile<VT_CSR2, OP, PASS>;
+    auto kernel = k_csr2_tile<VT_CSR2, OP, MODE>;
     static bool configured[64] = {};  // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -397,15 +713,19 @@ cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cb
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    LaunchScope scope(PASS == PASS_COUNT ? (OP == OP_UNION ? "csr_add_count" : "csr_mul_count")
-                                         : (OP == OP_UNION ? "csr_add_fill" : "csr_mul_fill"),
-                      stream);
-    kernel<<<num_tiles, NT, smem, stream>>>(A, B, cuts, cbits, tile_count, Z);
+    static const char *const names[2][3] = {{"csr_add_count", "csr_add_fill", "csr_add_fused"},
+                                            {"csr_mul_count", "csr_mul_fill", "csr_mul_fused"}};
+    LaunchScope scope(names[OP][MODE], stream);
+    kernel<<<num_tiles, NT, smem, stream>>>(A, B, cuts, cbits, tile_count, tile_state, ctl, Z);
     return cudaGetLastError();
 }
 
 // Shared driver of add and multiply. When `alloc` is set the result arrays are allocated
 // here (one cudaMallocAsync each); otherwise z's arrays are the caller's, `capacity` entries.
+//
+// With room for the largest possible result (every operand entry for a union, the smaller
+// operand for an intersection) the single-pass kernel runs. A caller-provided capacity below
+// that bound takes the two-pass route, which knows the exact length before it writes.
 template <int OP>
 int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, int64_t capacity, void *stream_v) {
     int st;
@@ -419,6 +739,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     const int64_t tiles64 = (total + tile_step - 1) / tile_step;
     if (tiles64 > INT32_MAX - 1) return NB200_E_OVERFLOW;
     const int num_tiles = (int)tiles64;
+    const int64_t bound = OP == OP_UNION ? total : std::min<int64_t>(a->nnz, b->nnz);
 
     z->rows = rows;
     z->cols = a->cols;
@@ -451,6 +772,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     sizes.take<int32_t>((size_t)num_tiles + 1);
     sizes.take<int32_t>((size_t)num_tiles + 1);
     sizes.take<int64_t>(1);
+    sizes.take<uint64_t>((size_t)num_tiles + 8);
     Workspace *ws = nullptr;
     if ((st = acquire_workspace(stream, sizes.used(), &ws))) return fail(st);
     Carver carve(ws->dev);
@@ -460,10 +782,25 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     cuts.b = carve.take<int32_t>((size_t)num_tiles + 1);
     int32_t *tile_count = carve.take<int32_t>((size_t)num_tiles + 1);
     int64_t *d_total = carve.take<int64_t>(1);
+    // control block and tile words of the single-pass kernel, contiguous for one memset
+    uint64_t *fused_block = carve.take<uint64_t>((size_t)num_tiles + 8);
+    static_assert(sizeof(FusedCtl) <= 4 * sizeof(uint64_t), "control block must fit its slot");
+    FusedCtl *ctl = reinterpret_cast<FusedCtl *>(fused_block);
+    uint64_t *tile_state = fused_block + 4;
 
     const CsrIn A{a->row_ptr, a->col, a->val, a->nnz}, B{b->row_ptr, b->col, b->val, b->nnz};
     const int cbits = col_bits(a->cols);
+    const bool fused = alloc || capacity >= bound;
     cudaError_t e;
+    if (fused) {
+        e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
+        if (alloc && bound > 0) {
+            e = cudaMallocAsync(reinterpret_cast<void **>(&z->col), sizeof(int32_t) * (size_t)bound, stream);
+            if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&z->val), sizeof(float) * (size_t)bound, stream);
+            if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMallocAsync"));
+        }
+    }
     {
         LaunchScope scope("csr2_partition", stream);
         const int warps = num_tiles + 1;
@@ -472,7 +809,28 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_partition"));
-    e = launch_tile<OP, PASS_COUNT>(A, B, cuts, cbits, tile_count, CsrOut{nullptr, nullptr, nullptr}, num_tiles, stream);
+
+    if (fused) {
+        e = launch_tile<OP, MODE_FUSED>(A, B, cuts, cbits, nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fused>"));
+        e = cudaMemcpyAsync(ws->host, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "read result length"));
+        FusedCtl h;
+        std::memcpy(&h, ws->host, sizeof(h));
+        if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+        if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
+        z->nnz = (int32_t)h.total;
+        if (alloc && h.total == 0) {  // zero-length arrays are handed over as NULL
+            if (z->col) cudaFreeAsync(z->col, stream);
+            if (z->val) cudaFreeAsync(z->val, stream);
+            z->col = nullptr;
+            z->val = nullptr;
+        }
+        return NB200_OK;
+    }
+
+    e = launch_tile<OP, MODE_COUNT>(A, B, cuts, cbits, tile_count, nullptr, nullptr, CsrOut{nullptr, nullptr, nullptr}, num_tiles, stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<count>"));
     {
         LaunchScope scope("scan_tiles", stream);
@@ -486,17 +844,8 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     const int64_t nnz = ws->host[0];
     if (nnz > INT32_MAX) return fail(NB200_E_OVERFLOW);
     z->nnz = (int32_t)nnz;
-
-    if (alloc) {
-        if (nnz > 0) {
-            e = cudaMallocAsync(reinterpret_cast<void **>(&z->col), sizeof(int32_t) * (size_t)nnz, stream);
-            if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&z->val), sizeof(float) * (size_t)nnz, stream);
-            if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMallocAsync"));
-        }
-    } else if (nnz > capacity) {
-        return NB200_E_CAPACITY;
-    }
-    e = launch_tile<OP, PASS_FILL>(A, B, cuts, cbits, tile_count, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
+    if (nnz > capacity) return NB200_E_CAPACITY;
+    e = launch_tile<OP, MODE_FILL>(A, B, cuts, cbits, tile_count, nullptr, nullptr, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fill>"));
     return NB200_OK;
 }

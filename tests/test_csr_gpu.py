@@ -161,6 +161,28 @@ def test_allocating_entry_points(nacho, csr_golden):
                 check(lib.nb200_free_async(p, None), "free")
 
 
+@pytest.mark.parametrize("case", ["smoke", "medium", "identical", "giant_row"])
+def test_two_pass_route_with_exact_capacity(nacho, csr_golden, case):
+    """A capacity below the worst-case bound but large enough for the result takes the
+    count -> scan -> fill route; it must give the same arrays as the single-pass route."""
+    import torch
+    from nacho_b200._capi import CsrStruct, check, lib
+    a, b = golden_csr(csr_golden, case, "a"), golden_csr(csr_golden, case, "b")
+    ga, gb = csr_to_gpu(a), csr_to_gpu(b)
+    for fn, tag in ((lib.nb200_csr_add_f32_into, "add"), (lib.nb200_csr_mul_f32_into, "mul")):
+        want = golden_csr(csr_golden, case, tag)
+        n = len(want.col)
+        rp = torch.empty(a.rows + 1, dtype=torch.int32, device="cuda")
+        col = torch.empty(max(n, 1), dtype=torch.int32, device="cuda")
+        val = torch.empty(max(n, 1), dtype=torch.float32, device="cuda")
+        z = CsrStruct(a.rows, a.cols, 0, rp.data_ptr(), col.data_ptr(), val.data_ptr())
+        sa, sb = ga._struct(), gb._struct()
+        check(fn(C.byref(sa), C.byref(sb), C.byref(z), n, None), tag)
+        torch.cuda.synchronize()
+        got = CSR(a.rows, a.cols, rp.cpu().numpy(), col[:n].cpu().numpy(), val[:n].cpu().numpy())
+        assert_same(got, want, f"{case} {tag} (two-pass)")
+
+
 def test_capacity_and_argument_errors(nacho, csr_golden):
     import torch
     from nacho_b200 import _capi
@@ -193,7 +215,7 @@ def test_launch_counter_and_profile(nacho, csr_golden):
     _capi.profile_enable(True)
     nacho.gpu_csr_add_f32(ga, gb)
     _capi.profile_enable(False)
-    assert _capi.launch_count() - before == 4  # partition, count, scan, fill
-    n, ms = _capi.profile_read("csr_add_fill")
+    assert _capi.launch_count() - before == 2  # partition + single-pass merge
+    n, ms = _capi.profile_read("csr_add_fused")
     assert n == 1 and ms > 0
     assert "csr2_partition" in _capi.profile_names()
