@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libnacho_b200.so")
+# NACHO_B200_LIB selects another build of the same library (e.g. a tuning variant).
+LIB_PATH = os.environ.get("NACHO_B200_LIB") or os.path.join(HERE, "libnacho_b200.so")
 
 _I32P = C.POINTER(C.c_int32)
 _F32P = C.POINTER(C.c_float)

@@ -16,6 +16,7 @@
 // :273-411, value expressions :426-440, empty-result path
 // src/backend/stitch_and_generate.cpp:168-220.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "block_utils.cuh"
@@ -26,10 +27,18 @@ namespace nb200 {
 
 namespace {
 
-constexpr int NT = 256;
+// Tuning knobs (compile-time): threads per CTA, merged entries per thread, and the number of
+// CTAs per SM the register allocator is asked to leave room for.
+#ifndef CSR2_NT
+#define CSR2_NT 256
+#endif
+#ifndef CSR2_VT
+#define CSR2_VT 15
+#endif
 #ifndef CSR2_MIN_CTAS
 #define CSR2_MIN_CTAS 4
 #endif
+constexpr int NT = CSR2_NT;
 
 enum SetOp { OP_UNION = 0, OP_INTERSECT = 1 };
 
@@ -340,15 +349,19 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
 // Shared-memory plan of the fast tile body, in 4-byte words. Keys and values use the same
 // word positions: A's entry e sits at word oa + e and B's at word obv + e, where oa and obv
 // are chosen so that a global address on a 16-byte boundary lands on a 16-byte boundary in
-// shared memory too (what a bulk copy needs). The two output staging arrays follow.
+// shared memory too (what a bulk copy needs). The column staging array of the result reuses
+// the key words (the keys live in registers by then); the value staging array follows.
 template <int VT>
 struct FastPlan {
     static constexpr int CAP = NT * VT;
+    static constexpr int NET = VT < 8 ? 8 : (VT < 16 ? 16 : 32);   // register merge network width
     static constexpr int CH = (VT + 1 + 3) & ~3;                   // words each thread scans
-    static constexpr int SLOTS = NT * CH + ((VT + 4 + 3) & ~3);    // key words = value words
+    static constexpr int SLOTS = NT * CH + ((NET + 4 + 3) & ~3);   // key words = value words
     static constexpr int OUT = CAP + 8;                            // staging words per array
-    static constexpr size_t BYTES = 4 * (size_t)(2 * SLOTS + 2 * OUT);
+    static constexpr size_t BYTES = 4 * (size_t)(2 * SLOTS + OUT);
+    static_assert(VT < NET, "the network needs one spare slot for the successor key");
     static_assert(NT * CH >= CAP + 12, "scan range must cover the padded tile");
+    static_assert(OUT <= SLOTS, "column staging must fit the key words it reuses");
 };
 
 constexpr int MBAR_POLL_LIMIT = 1 << 24;
@@ -359,8 +372,29 @@ __device__ __forceinline__ int head_elems(const void *p) {
     return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
 }
 
-// Fast tile body: 32-bit composite keys; operands staged with bulk copies, result written with
-// bulk stores, so that neither costs per-entry instructions.
+// Sorts a bitonic sequence (ascending run, then descending run) held in registers.
+template <int N>
+__device__ __forceinline__ void bitonic_merge(uint32_t (&r)[N]) {
+#pragma unroll
+    for (int d = N / 2; d > 0; d >>= 1) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            if ((i & d) == 0) {
+                const uint32_t lo = min(r[i], r[i + d]), hi = max(r[i], r[i + d]);
+                r[i] = lo;
+                r[i + d] = hi;
+            }
+        }
+    }
+}
+
+// Fast tile body. Keys are 32-bit composites (row in tile, column, operand bit):
+//     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
+// so that one unsigned compare orders entries by (row, column) with A first on ties, and
+// two entries are the same position exactly when their keys differ in the last bit only.
+// Operands are staged with bulk copies and the result is written with bulk stores, so neither
+// costs per-entry instructions; each thread merges its VT entries in registers with a bitonic
+// merge network instead of a serial loop over shared memory.
 template <int VT, int OP, int MODE>
 __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits,
                                                const int t, int32_t *tile_count, volatile uint64_t *tile_state,
@@ -368,6 +402,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
                                                int *scan_tmp, int *thread_rank, unsigned *thread_emit,
                                                uint64_t *mbar) {
     using P = FastPlan<VT>;
+    constexpr int NET = P::NET;
     constexpr bool WRITES = MODE != MODE_COUNT;
     constexpr uint32_t INF = 0xffffffffu;
     const int tid = threadIdx.x;
@@ -379,8 +414,8 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
 
     uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw);
     float *vals = reinterpret_cast<float *>(keys + P::SLOTS);
-    int32_t *out_col = reinterpret_cast<int32_t *>(vals + P::SLOTS);
-    float *out_val = reinterpret_cast<float *>(out_col + P::OUT);
+    int32_t *out_col = reinterpret_cast<int32_t *>(keys);
+    float *out_val = reinterpret_cast<float *>(vals + P::SLOTS);
 
     const int32_t *ga_col = A.col + a0, *gb_col = B.col + b0;
     const float *ga_val = A.val + a0, *gb_val = B.val + b0;
@@ -390,7 +425,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     const int obv = ob + ((4 - hb) & 3);         // word of B's entry 0
     const int scan_end = (obv + nb + 3) & ~3;
     uint32_t *kx = keys + oa, *ky = keys + obv;
-    const float *vx = vals + oa, *vy = vals + obv;
+    const float *vy = vals + obv;
 
     // ---- stage the tile. Thread 0 hands the 16-byte-aligned interior of each array to the copy
     // engine; a few other threads load the ragged ends (at most 3 entries each side).
@@ -423,11 +458,11 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     if (WRITES && !va_bulk) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
     if (WRITES && !vb_bulk) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
     // padding words that precede live keys must read as "no row mark"; the end-of-list
-    // sentinels are all-ones, which the row spreading below leaves intact
+    // sentinels are all-ones, which the row spreading below keeps above every live key
     if (tid >= 64 && tid < 64 + 3) { if (tid - 64 < oa) keys[tid - 64] = 0u; }
     if (tid >= 68 && tid < 68 + 3) { if (ob + (tid - 68) < obv) keys[ob + (tid - 68)] = 0u; }
     if (tid == 72) keys[oa + na] = INF;
-    if (tid >= 96 && tid < 96 + VT + 1) keys[obv + nb + (tid - 96)] = INF;
+    if (tid >= 96 - 64 * (NT < 256) && tid < 96 - 64 * (NT < 256) + NET + 1) keys[obv + nb + (tid - (96 - 64 * (NT < 256)))] = INF;
 
     // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over the
     // threads); kept in registers for the row-offset pass at the end
@@ -458,8 +493,9 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     }
     __syncthreads();
 
-    // ---- spread the marks forward (running maximum) so that every key carries its row.
-    // Each thread owns CH consecutive words; A's region and B's region run separately.
+    // ---- spread the marks forward (running maximum) so that every key carries its row, and
+    // append the operand bit. Each thread owns CH consecutive words; A's region and B's region
+    // run separately.
     {
         constexpr int NV = P::CH / 4;
         const int w_base = tid * P::CH;
@@ -478,59 +514,71 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         for (int j = 0; j < NV; ++j) {
             const int w = w_base + 4 * j;
             const bool in_a = w < ob;
+            const unsigned src = in_a ? 0u : 1u;
             unsigned run = in_a ? ea : eb;
             uint4 v = q[j];
-            run = max(run, v.x & ~cmask); v.x = run | (v.x & cmask);
-            run = max(run, v.y & ~cmask); v.y = run | (v.y & cmask);
-            run = max(run, v.z & ~cmask); v.z = run | (v.z & cmask);
-            run = max(run, v.w & ~cmask); v.w = run | (v.w & cmask);
+            run = max(run, v.x & ~cmask); v.x = ((run | (v.x & cmask)) << 1) | src;
+            run = max(run, v.y & ~cmask); v.y = ((run | (v.y & cmask)) << 1) | src;
+            run = max(run, v.z & ~cmask); v.z = ((run | (v.z & cmask)) << 1) | src;
+            run = max(run, v.w & ~cmask); v.w = ((run | (v.w & cmask)) << 1) | src;
             if (in_a) ea = run; else eb = run;
             if (w < scan_end) *reinterpret_cast<uint4 *>(keys + w) = v;
         }
     }
     __syncthreads();
 
-    // ---- split the tile among threads: merge-path diagonal tid * VT, ties take A first
+    // ---- split the tile among threads: merge-path diagonal tid * VT (the operand bit makes
+    // an A entry smaller than the B entry at the same position, so ties take A first)
     const int diag = min(tid * VT, n);
-    int x, y;
+    int x0;
     {
         int lo = max(0, diag - nb), hi = min(diag, na);
         while (lo < hi) {
             const int mid = (lo + hi) >> 1;
-            if (kx[mid] <= ky[diag - 1 - mid]) lo = mid + 1; else hi = mid;
+            if (kx[mid] < ky[diag - 1 - mid]) lo = mid + 1; else hi = mid;
         }
-        x = lo;
-        y = diag - lo;
+        x0 = lo;
     }
-    const int x0 = x, y0 = y;
+    const int y0 = diag - x0;
+    thread_rank[tid] = x0;  // borrowed to pass every thread's split to its left neighbour
+    __syncthreads();
+    const int cnt = min(VT, n - diag);
+    const int x1 = tid + 1 < NT ? thread_rank[tid + 1] : na;
+    const int a = min(x1, x0 + cnt) - x0, b = cnt - a;
 
-    // ---- merge VT entries; straight-line code. Bit i of `from_a`: entry i came from A; of
-    // `twin`: the same (row, column) is in B too; of `emit`: the entry goes to the result.
-    unsigned from_a = 0, twin = 0, emit = 0;
+    // ---- merge in registers: A's entries ascending, the successor of the thread's range, an
+    // all-ones plateau, B's entries descending -- a bitonic sequence -- through a merge network
+    uint32_t r[NET];
     {
-        const int valid = min(VT, n - diag);
-        uint32_t hx = kx[x], hy = ky[y];
-        uint32_t last_x = x > 0 ? kx[x - 1] : INF;
+        const uint32_t succ = min(kx[x0 + a], ky[y0 + b]);  // next merged key after this thread's range
 #pragma unroll
-        for (int i = 0; i < VT; ++i) {
-            const bool tx = hx <= hy;
-            const bool both = hx == hy;
-            const bool out = OP == OP_UNION ? (tx || hy != last_x) : both;
-            from_a |= (unsigned)tx << i;
-            twin |= (unsigned)both << i;
-            emit |= (unsigned)(out && i < valid) << i;
-            last_x = tx ? hx : last_x;
-            x += tx;
-            y += !tx;
-            hx = kx[x];
-            hy = ky[y];
+        for (int i = 0; i < NET; ++i) {
+            const bool is_a = i < a, is_b = i >= NET - b;
+            const uint32_t *p = is_a ? kx + x0 + i : ky + y0 + (NET - 1 - i);
+            const uint32_t v = *p;  // stays inside the slack-padded key array either way
+            r[i] = (is_a || is_b) ? v : (i == a ? succ : INF);
         }
     }
+    const uint32_t prev_a = x0 > 0 ? kx[x0 - 1] : 0u;  // only an A entry can pair with a B entry
+    bitonic_merge<NET>(r);
+
+    // Bit i of `from_a`: entry i came from A; of `same`: entries i and i+1 are one position (an A
+    // entry and its B twin); of `emit`: entry i goes to the result.
+    unsigned from_a = 0, same = 0;
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+        from_a |= (unsigned)((r[i] & 1u) == 0u) << i;
+        same |= (unsigned)((r[i] ^ r[i + 1]) == 1u) << i;
+    }
+    const unsigned live = cnt >= 32 ? 0xffffffffu : ((1u << cnt) - 1u);
+    const unsigned dup = (same << 1) | (unsigned)(x0 > 0 && (prev_a ^ r[0]) == 1u);  // B entries whose A twin precedes them
+    const unsigned twin = same & from_a & live;
+    const unsigned emit = OP == OP_UNION ? (live & ~dup) : twin;
 
     // ---- rank the survivors inside the tile
     int total;
     const int mine = __popc(emit);
-    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);
+    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // its syncs also retire the key reads
     if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
         return;
@@ -541,8 +589,8 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     thread_rank[tid] = rank;
     thread_emit[tid] = emit;
     if (MODE == MODE_FUSED && warp_id() == 0) {
-        const int64_t b = lookback_exclusive(tile_state, t, total, &ctl->status);
-        if (lane_id() == 0) s_base = b;
+        const int64_t bse = lookback_exclusive(tile_state, t, total, &ctl->status);
+        if (lane_id() == 0) s_base = bse;
     }
     __syncthreads();
     const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
@@ -553,13 +601,13 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     // tile those are the survivors among the first d = (A entries before row r) + (B entries
     // before row r) merged entries, read off the per-thread ranks. The tile owns rows
     // i0+1 .. i1 (the next tile's first row).
-    for (int64_t r = my_row; r <= i1; r += NT) {
-        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
-        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
+    for (int64_t rw = my_row; rw <= i1; rw += NT) {
+        const int sa = rw == my_row ? my_sa : ld_nc(A.rp + rw) - a0;
+        const int sb = rw == my_row ? my_sb : ld_nc(B.rp + rw) - b0;
         const int d = sa + sb;
         const int owner = d / VT, off = d - owner * VT;
         const int before = owner >= NT ? total : thread_rank[owner] + __popc(thread_emit[owner] & ((1u << off) - 1u));
-        Z.rp[r] = (int32_t)(base + before);
+        Z.rp[rw] = (int32_t)(base + before);
     }
     if (t == 0 && tid == 0) Z.rp[0] = 0;
 
@@ -569,20 +617,19 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     float *gz_val = Z.val + base;
     const int sc = (4 - head_elems(gz_col)) & 3, sv = (4 - head_elems(gz_val)) & 3;
     {
-        int r = rank, xi = x0, yi = y0;
+        int o = rank, xi = x0, yi = y0;
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
             const bool tx = (from_a >> i) & 1u;
             const bool both = (twin >> i) & 1u;
             const bool out = (emit >> i) & 1u;
-            const int w = tx ? oa + xi : obv + yi;
-            const float v1 = vals[w], v2 = vy[yi];  // both reads stay inside the padded arrays
-            const float v = both ? (OP == OP_UNION ? v1 + v2 : v1 * v2) : v1;
+            float v = vals[tx ? oa + xi : obv + yi];
+            if (both) v = OP == OP_UNION ? v + vy[yi] : v * vy[yi];
             if (out) {
-                out_col[sc + r] = (int32_t)(keys[w] & cmask);
-                out_val[sv + r] = v;
+                out_col[sc + o] = (int32_t)((r[i] >> 1) & cmask);
+                out_val[sv + o] = v;
             }
-            r += out;
+            o += out;
             xi += tx;
             yi += !tx;
         }
@@ -604,8 +651,8 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         const int e = is_val ? k - 6 : k;
         const int head = is_val ? hv : hc, nv = is_val ? nvv : nvc;
         const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
-        const bool live = e < 3 ? e < head : idx < total;
-        if (live) {
+        const bool alive = e < 3 ? e < head : idx < total;
+        if (alive) {
             if (is_val) gz_val[idx] = out_val[sv + idx];
             else gz_col[idx] = out_col[sc + idx];
         }
@@ -634,7 +681,7 @@ __global__ void __launch_bounds__(NT, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, CsrIn 
     // 32-bit composite keys hold (row in tile << cbits | column) when that fits; tiles that
     // span too many rows for that (long runs of empty rows) fall back to 64-bit keys.
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
-    const bool narrow = cbits < 32 && (nr << cbits) < 0xffffffffull;
+    const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;  // one bit is kept for the operand flag
     if (narrow) csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar);
     else csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit);
 }
@@ -681,7 +728,7 @@ __global__ void __launch_bounds__(1024) k_scan_tiles(int32_t *counts, int32_t n,
 
 // ------------------------------------------------------------------------ host driver ----
 
-constexpr int VT_CSR2 = 11;
+constexpr int VT_CSR2 = CSR2_VT;
 
 template <int VT>
 constexpr size_t csr2_smem_bytes() {
@@ -790,7 +837,9 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
 
     const CsrIn A{a->row_ptr, a->col, a->val, a->nnz}, B{b->row_ptr, b->col, b->val, b->nnz};
     const int cbits = col_bits(a->cols);
-    const bool fused = alloc || capacity >= bound;
+    // NACHO_B200_TWO_PASS=1 forces the count -> scan -> fill route (for comparisons).
+    static const bool force_two_pass = [] { const char *e = std::getenv("NACHO_B200_TWO_PASS"); return e && e[0] == '1'; }();
+    const bool fused = alloc || (capacity >= bound && !force_two_pass);
     cudaError_t e;
     if (fused) {
         e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream);
