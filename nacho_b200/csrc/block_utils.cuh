@@ -28,39 +28,50 @@ __device__ __forceinline__ unsigned warp_incl_max(unsigned v) {
     return v;
 }
 
-// Exclusive sum over the CTA; `total` receives the CTA-wide sum. `tmp` is >= 33 ints of
-// shared memory; the function syncs before reusing it, so calls may follow one another.
-template <int NT>
+// Barrier policies for the CTA-level scans below: the whole CTA, or the first COUNT threads
+// of it on hardware barrier ID (used when one extra warp of the CTA has another job).
+struct WholeCta {
+    __device__ static __forceinline__ void sync() { __syncthreads(); }
+};
+template <int ID, int COUNT>
+struct NamedBarrier {
+    __device__ static __forceinline__ void sync() { asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory"); }
+    __device__ static __forceinline__ void arrive() { asm volatile("bar.arrive %0, %1;" ::"n"(ID), "n"(COUNT) : "memory"); }
+};
+
+// Exclusive sum over the first NT threads of the CTA; `total` receives their sum. `tmp` is >= 33
+// ints of shared memory; the function syncs before reusing it, so calls may follow one another.
+template <int NT, typename Bar = WholeCta>
 __device__ __forceinline__ int block_excl_sum(int v, int *tmp, int &total) {
     constexpr int NW = NT / 32;
     int incl = warp_incl_sum(v);
-    __syncthreads();
+    Bar::sync();
     if (lane_id() == 31) tmp[warp_id()] = incl;
-    __syncthreads();
+    Bar::sync();
     if (warp_id() == 0) {
         int w = lane_id() < NW ? tmp[lane_id()] : 0;
         int wi = warp_incl_sum(w);
         if (lane_id() < NW) tmp[lane_id()] = wi - w;
         if (lane_id() == NW - 1) tmp[32] = wi;
     }
-    __syncthreads();
+    Bar::sync();
     total = tmp[32];
     return tmp[warp_id()] + incl - v;
 }
 
 // Exclusive running maximum over the CTA for two independent sequences at once (va, vb).
 // `tmp` is >= 64 unsigned of shared memory.
-template <int NT>
+template <int NT, typename Bar = WholeCta>
 __device__ __forceinline__ void block_excl_max2(unsigned va, unsigned vb, unsigned *tmp,
                                                 unsigned &ea, unsigned &eb) {
     constexpr int NW = NT / 32;
     unsigned ia = warp_incl_max(va), ib = warp_incl_max(vb);
-    __syncthreads();
+    Bar::sync();
     if (lane_id() == 31) {
         tmp[warp_id()] = ia;
         tmp[32 + warp_id()] = ib;
     }
-    __syncthreads();
+    Bar::sync();
     if (warp_id() == 0) {
         unsigned wa = lane_id() < NW ? tmp[lane_id()] : 0u;
         unsigned wb = lane_id() < NW ? tmp[32 + lane_id()] : 0u;
@@ -73,7 +84,7 @@ __device__ __forceinline__ void block_excl_max2(unsigned va, unsigned vb, unsign
             tmp[32 + lane_id()] = pb;
         }
     }
-    __syncthreads();
+    Bar::sync();
     unsigned pa = __shfl_up_sync(FULL_MASK, ia, 1), pb = __shfl_up_sync(FULL_MASK, ib, 1);
     if (lane_id() == 0) pa = pb = 0u;
     ea = max(tmp[warp_id()], pa);
@@ -136,49 +147,74 @@ constexpr uint64_t LB_VALUE_MASK = (1ull << 62) - 1;
 constexpr int LOOKBACK_POLL_LIMIT = 1 << 22;
 constexpr int ERR_LOOKBACK_TIMEOUT = 1;
 
+__device__ __forceinline__ uint64_t ld_relaxed_gpu(const volatile uint64_t *p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_relaxed_gpu(volatile uint64_t *p, uint64_t v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
 // Called by all 32 lanes of one warp. Returns the sum of the aggregates of tiles [0, t).
+// Each round inspects LOOKBACK_DEPTH * 32 predecessors with all of a lane's loads in flight
+// together, so a round costs one memory round trip however many words it covers.
+constexpr int LOOKBACK_DEPTH = 1;
+
 __device__ __forceinline__ int64_t lookback_exclusive(volatile uint64_t *state, int t, int64_t aggregate,
                                                       DeviceStatus *status) {
-    if (lane_id() == 0) state[t] = (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)aggregate;
+    if (lane_id() == 0) st_relaxed_gpu(state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)aggregate);
     if (t == 0) return 0;
     int64_t exclusive = 0;
-    bool failed = false;
-    for (int pos = t - 1;; pos -= 32) {
-        const int idx = pos - lane_id();
-        uint64_t s = LB_PREFIX;  // lanes that fall before tile 0 stand for an empty prefix
+    bool failed = false, done = false;
+    for (int pos = t - 1; !done; pos -= 32 * LOOKBACK_DEPTH) {
+        uint64_t s[LOOKBACK_DEPTH];
         bool timed_out = false;
-        if (idx >= 0) {
-            int polls = 0;
-            s = state[idx];
-            while ((s >> 62) == 0) {
-                if (++polls >= LOOKBACK_POLL_LIMIT) {
-                    timed_out = true;
-                    break;
-                }
-                __nanosleep(64);
-                s = state[idx];
+        int polls = 0;
+        for (;;) {
+            bool ready = true;
+#pragma unroll
+            for (int j = 0; j < LOOKBACK_DEPTH; ++j) {
+                const int idx = pos - 32 * j - lane_id();
+                // lanes that fall before tile 0 stand for an empty prefix
+                s[j] = idx >= 0 ? ld_relaxed_gpu(state + idx) : LB_PREFIX;
             }
+#pragma unroll
+            for (int j = 0; j < LOOKBACK_DEPTH; ++j) ready = ready && (s[j] >> 62) != 0;
+            // only words up to the nearest prefix matter; waiting for all of them is simpler and
+            // they belong to tiles that started earlier still
+            if (ready) break;
+            if (++polls >= LOOKBACK_POLL_LIMIT) {
+                timed_out = true;
+                break;
+            }
+            __nanosleep(32);
         }
         if (__any_sync(FULL_MASK, timed_out)) {
             failed = true;
             break;
         }
-        const unsigned prefix_lanes = __ballot_sync(FULL_MASK, (s >> 62) == 2);
-        const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 32;
-        long long v = lane_id() <= first ? (long long)(s & LB_VALUE_MASK) : 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
-        exclusive += v;
-        if (prefix_lanes) break;
+        for (int j = 0; j < LOOKBACK_DEPTH; ++j) {
+            if (done) break;
+            const unsigned prefix_lanes = __ballot_sync(FULL_MASK, (s[j] >> 62) == 2);
+            const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 32;
+            long long v = lane_id() <= first ? (long long)(s[j] & LB_VALUE_MASK) : 0;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
+            exclusive += v;
+            if (prefix_lanes) done = true;
+        }
     }
     if (failed) {
         if (lane_id() == 0) {
             if (atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
-            state[t] = LB_PREFIX;  // unblock successors; the call reports the failure
+            st_relaxed_gpu(state + t, LB_PREFIX);  // unblock successors; the call reports the failure
         }
         return -1;
     }
-    if (lane_id() == 0) state[t] = LB_PREFIX | (uint64_t)(exclusive + aggregate);
+    if (lane_id() == 0) st_relaxed_gpu(state + t, LB_PREFIX | (uint64_t)(exclusive + aggregate));
     return exclusive;
 }
 

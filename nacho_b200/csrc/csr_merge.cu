@@ -33,12 +33,20 @@ namespace {
 #define CSR2_NT 256
 #endif
 #ifndef CSR2_VT
-#define CSR2_VT 15
+#define CSR2_VT 19
 #endif
 #ifndef CSR2_MIN_CTAS
-#define CSR2_MIN_CTAS 4
+#define CSR2_MIN_CTAS 3
 #endif
 constexpr int NT = CSR2_NT;
+// Profiling aid: building with -DCSR2_STOP_AFTER=k makes the fast tile body return after its
+// k-th phase (results are then wrong), so that instruction and shared-memory counters can be
+// attributed to phases by difference. Never defined in a normal build.
+#ifdef CSR2_STOP_AFTER
+#define CSR2_PHASE_END(k, keep) do { if (CSR2_STOP_AFTER == (k)) { if ((keep) == 0x7fff1234) ctl->total = (keep); return; } } while (0)
+#else
+#define CSR2_PHASE_END(k, keep) do { } while (0)
+#endif
 
 enum SetOp { OP_UNION = 0, OP_INTERSECT = 1 };
 
@@ -354,12 +362,14 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
 template <int VT>
 struct FastPlan {
     static constexpr int CAP = NT * VT;
-    static constexpr int NET = VT < 8 ? 8 : (VT < 16 ? 16 : 32);   // register merge network width
-    static constexpr int CH = (VT + 1 + 3) & ~3;                   // words each thread scans
-    static constexpr int SLOTS = NT * CH + ((NET + 4 + 3) & ~3);   // key words = value words
-    static constexpr int OUT = CAP + 8;                            // staging words per array
+    static constexpr int NETV = VT + 1;                          // merge-network slots in use
+    static constexpr int CH = (VT + 1 + 3) & ~3;                 // words each thread scans
+    static constexpr int SLOTS = NT * CH + ((NETV + 4 + 3) & ~3);  // key words = value words
+    static constexpr int OUT = CAP + 8;                          // staging words per array
     static constexpr size_t BYTES = 4 * (size_t)(2 * SLOTS + OUT);
-    static_assert(VT < NET, "the network needs one spare slot for the successor key");
+    // A thread's CH-word chunk is read and written as 16-byte vectors; an odd number of
+    // vectors per chunk keeps those accesses free of shared-memory bank conflicts.
+    static_assert((CH / 4) % 2 == 1, "choose VT so that (VT + 1) rounded up to 4 is an odd multiple of 4");
     static_assert(NT * CH >= CAP + 12, "scan range must cover the padded tile");
     static_assert(OUT <= SLOTS, "column staging must fit the key words it reuses");
 };
@@ -372,29 +382,42 @@ __device__ __forceinline__ int head_elems(const void *p) {
     return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
 }
 
-// Sorts a bitonic sequence (ascending run, then descending run) held in registers.
+// Sorts N keys held in registers that form a bitonic sequence (ascending run, then descending
+// run). For N that is not a power of two the keys are treated as the top N slots of the next
+// power-of-two network whose lower slots hold zeros; compare-exchanges that would touch
+// those virtual slots leave them unchanged and are dropped at compile time.
 template <int N>
 __device__ __forceinline__ void bitonic_merge(uint32_t (&r)[N]) {
+    constexpr int NET = N <= 8 ? 8 : (N <= 16 ? 16 : 32);
+    constexpr int PAD = NET - N;
 #pragma unroll
-    for (int d = N / 2; d > 0; d >>= 1) {
+    for (int d = NET / 2; d > 0; d >>= 1) {
 #pragma unroll
-        for (int i = 0; i < N; ++i) {
+        for (int i = PAD; i < NET; ++i) {
             if ((i & d) == 0) {
-                const uint32_t lo = min(r[i], r[i + d]), hi = max(r[i], r[i + d]);
-                r[i] = lo;
-                r[i + d] = hi;
+                const uint32_t lo = min(r[i - PAD], r[i + d - PAD]), hi = max(r[i - PAD], r[i + d - PAD]);
+                r[i - PAD] = lo;
+                r[i + d - PAD] = hi;
             }
         }
     }
 }
 
+// Hardware barriers of the tile kernel: 0 = the whole CTA (__syncthreads), 1 = the NT worker
+// threads, 2 = workers arrive / the scan warp waits ("the tile's count is known").
+using WorkerBar = NamedBarrier<1, NT>;
+using CountBar = NamedBarrier<2, NT + 32>;
+
 // Fast tile body. Keys are 32-bit composites (row in tile, column, operand bit):
 //     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
 // so that one unsigned compare orders entries by (row, column) with A first on ties, and
 // two entries are the same position exactly when their keys differ in the last bit only.
-// Operands are staged with bulk copies and the result is written with bulk stores, so neither
-// costs per-entry instructions; each thread merges its VT entries in registers with a bitonic
-// merge network instead of a serial loop over shared memory.
+//
+// The CTA has NT worker threads and one more warp, the scan warp. Workers stage the operands
+// with bulk copies, build keys, split the tile by merge-path, merge VT entries each in
+// registers with a bitonic network, and compact the survivors into shared memory. In the
+// single-pass mode the scan warp meanwhile turns the tile's count into its output base by
+// look-back over earlier tiles, so that this wait overlaps the workers' compaction.
 template <int VT, int OP, int MODE>
 __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits,
                                                const int t, int32_t *tile_count, volatile uint64_t *tile_state,
@@ -402,10 +425,13 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
                                                int *scan_tmp, int *thread_rank, unsigned *thread_emit,
                                                uint64_t *mbar) {
     using P = FastPlan<VT>;
-    constexpr int NET = P::NET;
+    constexpr int NETV = P::NETV;
     constexpr bool WRITES = MODE != MODE_COUNT;
     constexpr uint32_t INF = 0xffffffffu;
+    __shared__ long long s_base;
+    __shared__ int s_total;
     const int tid = threadIdx.x;
+    const bool scan_warp = tid >= NT;
     const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
     const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
@@ -427,8 +453,8 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     uint32_t *kx = keys + oa, *ky = keys + obv;
     const float *vy = vals + obv;
 
-    // ---- stage the tile. Thread 0 hands the 16-byte-aligned interior of each array to the copy
-    // engine; a few other threads load the ragged ends (at most 3 entries each side).
+    // ---- stage the tile. One thread hands the 16-byte-aligned interior of each array to the
+    // copy engine; a few other threads load the ragged ends (at most 3 entries each side).
     // Value arrays whose alignment differs from their column arrays' take plain loads.
     const bool va_bulk = !WRITES || head_elems(ga_val) == ha, vb_bulk = !WRITES || head_elems(gb_val) == hb;
     const int head_a = min(na, ha), head_b = min(nb, hb);
@@ -455,20 +481,21 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
             if (WRITES && (is_b ? vb_bulk : va_bulk)) vals[w] = ld_nc((is_b ? gb_val : ga_val) + idx);
         }
     }
-    if (WRITES && !va_bulk) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
-    if (WRITES && !vb_bulk) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
+    if (WRITES && !va_bulk && !scan_warp) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
+    if (WRITES && !vb_bulk && !scan_warp) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
     // padding words that precede live keys must read as "no row mark"; the end-of-list
     // sentinels are all-ones, which the row spreading below keeps above every live key
     if (tid >= 64 && tid < 64 + 3) { if (tid - 64 < oa) keys[tid - 64] = 0u; }
     if (tid >= 68 && tid < 68 + 3) { if (ob + (tid - 68) < obv) keys[ob + (tid - 68)] = 0u; }
     if (tid == 72) keys[oa + na] = INF;
-    if (tid >= 96 - 64 * (NT < 256) && tid < 96 - 64 * (NT < 256) + NET + 1) keys[obv + nb + (tid - (96 - 64 * (NT < 256)))] = INF;
+    if (tid >= 76 && tid < 76 + NETV + 1) keys[obv + nb + (tid - 76)] = INF;
+    static_assert(76 + NETV + 1 <= NT, "sentinel writers must be worker threads");
 
     // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over the
-    // threads); kept in registers for the row-offset pass at the end
+    // workers); kept in registers for the row-offset pass at the end
     const int64_t my_row = (int64_t)i0 + 1 + tid;
     int32_t my_sa = 0, my_sb = 0;
-    if (my_row <= i1) {
+    if (!scan_warp && my_row <= i1) {
         my_sa = ld_nc(A.rp + my_row) - a0;
         my_sb = ld_nc(B.rp + my_row) - b0;
     }
@@ -481,6 +508,21 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         }
         return;
     }
+    CSR2_PHASE_END(1, (int)keys[tid]);
+
+    if (scan_warp) {
+        // ---- scan warp: wait for the tile's count, turn it into the output base
+        if (MODE != MODE_FUSED) return;
+        CountBar::sync();
+        const int total = s_total;
+        const int64_t bse = lookback_exclusive(tile_state, t, total, &ctl->status);
+        if (lane_id() == 0) {
+            s_base = bse;
+            if (bse >= 0 && t == (int)gridDim.x - 1) ctl->total = bse + total;
+        }
+        __syncthreads();
+        return;
+    }
 
     // ---- mark the first entry of every row that starts inside the tile with its row number
     // relative to i0, in the bits above the column (max wins where empty rows share a start)
@@ -491,7 +533,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         if (sa < na) atomicMax(kx + sa, (rr << cbits) | (kx[sa] & cmask));
         if (sb < nb) atomicMax(ky + sb, (rr << cbits) | (ky[sb] & cmask));
     }
-    __syncthreads();
+    WorkerBar::sync();
 
     // ---- spread the marks forward (running maximum) so that every key carries its row, and
     // append the operand bit. Each thread owns CH consecutive words; A's region and B's region
@@ -509,7 +551,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
             if (w < ob) ma = max(ma, m); else mb = max(mb, m);
         }
         unsigned ea, eb;
-        block_excl_max2<NT>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
+        block_excl_max2<NT, WorkerBar>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int w = w_base + 4 * j;
@@ -525,7 +567,8 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
             if (w < scan_end) *reinterpret_cast<uint4 *>(keys + w) = v;
         }
     }
-    __syncthreads();
+    WorkerBar::sync();
+    CSR2_PHASE_END(2, (int)keys[tid]);
 
     // ---- split the tile among threads: merge-path diagonal tid * VT (the operand bit makes
     // an A entry smaller than the B entry at the same position, so ties take A first)
@@ -540,27 +583,28 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         x0 = lo;
     }
     const int y0 = diag - x0;
+    CSR2_PHASE_END(3, x0);
     thread_rank[tid] = x0;  // borrowed to pass every thread's split to its left neighbour
-    __syncthreads();
+    WorkerBar::sync();
     const int cnt = min(VT, n - diag);
     const int x1 = tid + 1 < NT ? thread_rank[tid + 1] : na;
     const int a = min(x1, x0 + cnt) - x0, b = cnt - a;
 
     // ---- merge in registers: A's entries ascending, the successor of the thread's range, an
     // all-ones plateau, B's entries descending -- a bitonic sequence -- through a merge network
-    uint32_t r[NET];
+    uint32_t r[NETV];
     {
         const uint32_t succ = min(kx[x0 + a], ky[y0 + b]);  // next merged key after this thread's range
 #pragma unroll
-        for (int i = 0; i < NET; ++i) {
-            const bool is_a = i < a, is_b = i >= NET - b;
-            const uint32_t *p = is_a ? kx + x0 + i : ky + y0 + (NET - 1 - i);
+        for (int i = 0; i < NETV; ++i) {
+            const bool is_a = i < a, is_b = i >= NETV - b;
+            const uint32_t *p = is_a ? kx + x0 + i : ky + y0 + (NETV - 1 - i);
             const uint32_t v = *p;  // stays inside the slack-padded key array either way
             r[i] = (is_a || is_b) ? v : (i == a ? succ : INF);
         }
     }
     const uint32_t prev_a = x0 > 0 ? kx[x0 - 1] : 0u;  // only an A entry can pair with a B entry
-    bitonic_merge<NET>(r);
+    bitonic_merge<NETV>(r);
 
     // Bit i of `from_a`: entry i came from A; of `same`: entries i and i+1 are one position (an A
     // entry and its B twin); of `emit`: entry i goes to the result.
@@ -570,32 +614,55 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         from_a |= (unsigned)((r[i] & 1u) == 0u) << i;
         same |= (unsigned)((r[i] ^ r[i + 1]) == 1u) << i;
     }
-    const unsigned live = cnt >= 32 ? 0xffffffffu : ((1u << cnt) - 1u);
+    const unsigned live = (1u << cnt) - 1u;
     const unsigned dup = (same << 1) | (unsigned)(x0 > 0 && (prev_a ^ r[0]) == 1u);  // B entries whose A twin precedes them
     const unsigned twin = same & from_a & live;
     const unsigned emit = OP == OP_UNION ? (live & ~dup) : twin;
+    static_assert(VT < 32, "entry masks are 32 bits wide");
 
     // ---- rank the survivors inside the tile
     int total;
     const int mine = __popc(emit);
-    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // its syncs also retire the key reads
+    const int rank = block_excl_sum<NT, WorkerBar>(mine, scan_tmp, total);  // its syncs also retire the key reads
     if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
         return;
     }
-
-    // ---- output base of the tile
-    __shared__ long long s_base;
     thread_rank[tid] = rank;
     thread_emit[tid] = emit;
-    if (MODE == MODE_FUSED && warp_id() == 0) {
-        const int64_t bse = lookback_exclusive(tile_state, t, total, &ctl->status);
-        if (lane_id() == 0) s_base = bse;
+    if (MODE == MODE_FUSED) {
+        if (tid == 0) s_total = total;
+        __threadfence_block();
+        CountBar::arrive();  // the scan warp starts its look-back now
     }
-    __syncthreads();
+    CSR2_PHASE_END(4, rank + (int)r[3]);
+
+    // ---- compact columns and values of the survivors into the staging arrays
+    {
+        int o = rank, xi = x0, yi = y0;
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = (from_a >> i) & 1u;
+            const bool both = (twin >> i) & 1u;
+            const bool out = (emit >> i) & 1u;
+            float v = vals[tx ? oa + xi : obv + yi];
+            if (both) v = OP == OP_UNION ? v + vy[yi] : v * vy[yi];
+            if (out) {
+                out_col[o] = (int32_t)((r[i] >> 1) & cmask);
+                out_val[o] = v;
+            }
+            o += out;
+            xi += tx;
+            yi += !tx;
+        }
+    }
+    CSR2_PHASE_END(6, out_col[tid]);
+
+    // ---- output base of the tile
+    if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
     const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
     if (base < 0) return;  // a bounded wait gave up; the host reports it
-    if (MODE == MODE_FUSED && t == (int)gridDim.x - 1 && tid == 0) ctl->total = base + total;
+    CSR2_PHASE_END(5, (int)base);
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
     // tile those are the survivors among the first d = (A entries before row r) + (B entries
@@ -611,58 +678,18 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     }
     if (t == 0 && tid == 0) Z.rp[0] = 0;
 
-    // ---- gather columns and values of the survivors into the staging arrays, shifted so that
-    // 16-byte boundaries of the result arrays fall on 16-byte boundaries of shared memory
+    // ---- store the compacted tile, coalesced
     int32_t *gz_col = Z.col + base;
     float *gz_val = Z.val + base;
-    const int sc = (4 - head_elems(gz_col)) & 3, sv = (4 - head_elems(gz_val)) & 3;
-    {
-        int o = rank, xi = x0, yi = y0;
-#pragma unroll
-        for (int i = 0; i < VT; ++i) {
-            const bool tx = (from_a >> i) & 1u;
-            const bool both = (twin >> i) & 1u;
-            const bool out = (emit >> i) & 1u;
-            float v = vals[tx ? oa + xi : obv + yi];
-            if (both) v = OP == OP_UNION ? v + vy[yi] : v * vy[yi];
-            if (out) {
-                out_col[sc + o] = (int32_t)((r[i] >> 1) & cmask);
-                out_val[sv + o] = v;
-            }
-            o += out;
-            xi += tx;
-            yi += !tx;
-        }
+    for (int i = tid; i < total; i += NT) {
+        gz_col[i] = out_col[i];
+        gz_val[i] = out_val[i];
     }
-    fence_async_smem();
-    __syncthreads();
-
-    // ---- store: aligned interior by bulk store, ragged ends by a few threads
-    const int hc = min(total, (4 - sc) & 3), hv = min(total, (4 - sv) & 3);
-    const int nvc = (total - hc) >> 2, nvv = (total - hv) >> 2;
-    if (tid == 0) {
-        if (nvc) bulk_store(gz_col + hc, out_col + sc + hc, 16u * nvc);
-        if (nvv) bulk_store(gz_val + hv, out_val + sv + hv, 16u * nvv);
-        bulk_commit();
-    }
-    if (tid >= 32 && tid < 32 + 12) {
-        const int k = tid - 32;
-        const bool is_val = k >= 6;
-        const int e = is_val ? k - 6 : k;
-        const int head = is_val ? hv : hc, nv = is_val ? nvv : nvc;
-        const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
-        const bool alive = e < 3 ? e < head : idx < total;
-        if (alive) {
-            if (is_val) gz_val[idx] = out_val[sv + idx];
-            else gz_col[idx] = out_col[sc + idx];
-        }
-    }
-    if (tid == 0) bulk_wait_read_all();  // shared memory must outlive the engine's reads
 }
 
 template <int VT, int OP, int MODE>
-__global__ void __launch_bounds__(NT, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, CsrIn B, Cuts cuts, int cbits, int32_t *tile_count,
-                                                  uint64_t *tile_state, FusedCtl *ctl, CsrOut Z) {
+__global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, CsrIn B, Cuts cuts, int cbits, int32_t *tile_count,
+                                                       uint64_t *tile_state, FusedCtl *ctl, CsrOut Z) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
     __shared__ int thread_rank[NT];
@@ -678,12 +705,16 @@ __global__ void __launch_bounds__(NT, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, CsrIn 
     }
     __syncthreads();
     if (MODE == MODE_FUSED) t = s_tile;
-    // 32-bit composite keys hold (row in tile << cbits | column) when that fits; tiles that
-    // span too many rows for that (long runs of empty rows) fall back to 64-bit keys.
+    // 32-bit composite keys hold ((row in tile << cbits | column) << 1 | operand) when that
+    // fits; tiles that span too many rows for that (long runs of empty rows) use 64-bit keys.
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
-    const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;  // one bit is kept for the operand flag
-    if (narrow) csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar);
-    else csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit);
+    const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
+    if (narrow) {
+        csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar);
+    } else {
+        if (threadIdx.x >= NT) return;  // the generic body works with the NT worker threads alone
+        csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit);
+    }
 }
 
 // Exclusive prefix of the per-tile counts, in place, by one CTA; the grand total goes to
@@ -763,7 +794,7 @@ cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cb
     static const char *const names[2][3] = {{"csr_add_count", "csr_add_fill", "csr_add_fused"},
                                             {"csr_mul_count", "csr_mul_fill", "csr_mul_fused"}};
     LaunchScope scope(names[OP][MODE], stream);
-    kernel<<<num_tiles, NT, smem, stream>>>(A, B, cuts, cbits, tile_count, tile_state, ctl, Z);
+    kernel<<<num_tiles, NT + 32, smem, stream>>>(A, B, cuts, cbits, tile_count, tile_state, ctl, Z);
     return cudaGetLastError();
 }
 
