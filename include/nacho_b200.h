@@ -127,6 +127,30 @@ int nb200_csr_add_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
 int nb200_csr_add_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
                            int64_t capacity, void *stream);
 
+/* Z = A + B for callers that must not trigger any device or pinned-host allocation while they
+ * run -- code inside a framework's memory-pool callback or an out-of-memory handler, plug-ins
+ * living under a fixed memory budget that the host application has already handed out, and
+ * latency-critical loops where an allocator call could take a lock or synchronise the device.
+ * Has no counterpart in the reference, whose drivers allocate on every call.
+ *
+ * Same result as nb200_csr_add_f32_into, but the scratch memory of the kernels (tile cuts and
+ * the cross-tile counters) is a fixed 1 MiB array inside the library's device image instead of
+ * a pool that grows on demand. The call makes no cudaMalloc / cudaFree / cudaHostAlloc and
+ * calls no allocating library routine; the caller provides every operand and result array.
+ * Limits and rules:
+ *   - nnz(A) + nnz(B) may not exceed 32768 tiles' worth of entries (about 159 million);
+ *     larger inputs return NB200_E_UNSUPPORTED and nothing is launched.
+ *   - `capacity` (entries in z->col / z->val) must be at least nnz(A) + nnz(B); otherwise
+ *     NB200_E_CAPACITY. z->row_ptr holds rows + 1 entries.
+ *   - The first call on each device looks up the array's device address and raises the
+ *     kernel's shared-memory limit; make that first call before any stream capture begins.
+ *   - All calls on a device share the one array: it is re-zeroed at the start of each call,
+ *     and two calls that overlap on the GPU (different streams, different host threads)
+ *     would corrupt each other. Serialise them.
+ *   - Launches made here are not counted by nb200_launch_count nor timed by the profile. */
+int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
+                              int64_t capacity, void *stream);
+
 /* Z = A .* B, sorted intersection per row, value a * b. Replaces
  * csr_mul::csr_mul_gpu_i32_f32 (compiler.cpp:116; src/backend/compute.cpp:434-440). An empty
  * result has an all-zero row_ptr (src/backend/stitch_and_generate.cpp:168-220).

@@ -52,6 +52,7 @@ PROTOTYPES = {
     "nb200_profile_names": (C.c_int, [C.c_char_p, C.c_size_t]),
     "nb200_csr_add_f32": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),
     "nb200_csr_add_f32_into": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p]),
+    "nb200_csr_add_f32_noalloc": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p]),
     "nb200_csr_mul_f32": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),
     "nb200_csr_mul_f32_into": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p]),
 }

@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "block_utils.cuh"
 #include "common.cuh"
@@ -930,6 +931,90 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     return NB200_OK;
 }
 
+// ------------------------------------------------------- entry point that allocates nothing ----
+
+// Scratch of nb200_csr_add_f32_noalloc: tile cuts, the single-pass control block and one
+// 8-byte word per tile, carved out of one fixed array that lives in the library's device image
+// (so every GPU that loads the library holds these bytes until the process exits).
+constexpr int NOALLOC_MAX_TILES = 32768;
+constexpr size_t NOALLOC_SCRATCH_BYTES = 1u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// Device address of the array above for each device, looked up once per device. The array's
+// name is only a host-side handle; kernels must be given the address from
+// cudaGetSymbolAddress, taken while that device is current.
+int noalloc_scratch_address(void **out) {
+    static void *address[64] = {};
+    static std::mutex lock;
+    int dev = 0;
+    NB200_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return NB200_E_UNSUPPORTED;
+    std::lock_guard<std::mutex> g(lock);
+    if (!address[dev]) {
+        void *p = nullptr;
+        NB200_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        // the tile kernel needs more dynamic shared memory than the default limit; set that
+        // here too so that later calls are launches and nothing else
+        NB200_CUDA(cudaFuncSetAttribute(k_csr2_tile<VT_CSR2, OP_UNION, MODE_FUSED>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csr2_smem_bytes<VT_CSR2>()));
+        address[dev] = p;
+    }
+    *out = address[dev];
+    return NB200_OK;
+}
+
+int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream_v) {
+    int st;
+    if ((st = check_csr(a, true)) || (st = check_csr(b, true))) return st;
+    if (!z || !z->row_ptr || capacity < 0 || a->rows != b->rows || a->cols != b->cols) return NB200_E_BADARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int32_t rows = a->rows;
+    const int64_t total = (int64_t)a->nnz + b->nnz;
+    constexpr int tile_step = NT * VT_CSR2 - 1;
+    const int64_t tiles64 = (total + tile_step - 1) / tile_step;
+    if (tiles64 > NOALLOC_MAX_TILES) return NB200_E_UNSUPPORTED;
+    if (capacity < total) return NB200_E_CAPACITY;  // this entry point has the single-pass route only
+    if (total > 0 && (!z->col || !z->val)) return NB200_E_BADARG;
+    const int num_tiles = (int)tiles64;
+    z->rows = rows;
+    z->cols = a->cols;
+    z->nnz = 0;
+    if (num_tiles == 0) {
+        NB200_CUDA(cudaMemsetAsync(z->row_ptr, 0, sizeof(int32_t) * ((size_t)rows + 1), stream));
+        return NB200_OK;
+    }
+    void *scratch = nullptr;
+    if ((st = noalloc_scratch_address(&scratch))) return st;
+    Carver carve(scratch);
+    uint64_t *fused_block = carve.take<uint64_t>((size_t)NOALLOC_MAX_TILES + 8);
+    Cuts cuts;
+    cuts.row = carve.take<int32_t>((size_t)NOALLOC_MAX_TILES + 1);
+    cuts.a = carve.take<int32_t>((size_t)NOALLOC_MAX_TILES + 1);
+    cuts.b = carve.take<int32_t>((size_t)NOALLOC_MAX_TILES + 1);
+    static_assert(8 * (NOALLOC_MAX_TILES + 8 + 32) + 3 * (4 * (NOALLOC_MAX_TILES + 1) + 256) <= NOALLOC_SCRATCH_BYTES,
+                  "scratch layout must fit the fixed array");
+    FusedCtl *ctl = reinterpret_cast<FusedCtl *>(fused_block);
+    uint64_t *tile_state = fused_block + 4;
+    // the array keeps the previous call's contents: the ticket, the status and every tile word
+    // must start at zero
+    NB200_CUDA(cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream));
+
+    const CsrIn A{a->row_ptr, a->col, a->val, a->nnz}, B{b->row_ptr, b->col, b->val, b->nnz};
+    const int warps = num_tiles + 1;
+    k_csr2_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts);
+    NB200_CUDA(cudaGetLastError());
+    k_csr2_tile<VT_CSR2, OP_UNION, MODE_FUSED><<<num_tiles, NT + 32, csr2_smem_bytes<VT_CSR2>(), stream>>>(
+        A, B, cuts, col_bits(a->cols), nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val});
+    NB200_CUDA(cudaGetLastError());
+    FusedCtl h;  // read back into ordinary host memory: no pinned buffer is taken for this
+    NB200_CUDA(cudaMemcpyAsync(&h, ctl, sizeof(h), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaStreamSynchronize(stream));
+    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.total > INT32_MAX) return NB200_E_OVERFLOW;
+    z->nnz = (int32_t)h.total;
+    return NB200_OK;
+}
+
 }  // namespace
 
 }  // namespace nb200
@@ -952,6 +1037,10 @@ int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int3
 
 int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {
     return csr2_run<OP_INTERSECT>(a, b, z, false, capacity, stream);
+}
+
+int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {
+    return csr_add_noalloc(a, b, z, capacity, stream);
 }
 
 }  // extern "C"
