@@ -160,6 +160,28 @@ int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
 int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
                            int64_t capacity, void *stream);
 
+/* ---- 3-mode tensor add ------------------------------------------------------------------ */
+
+/* Z = A + B over lexicographically sorted unique (i, j, k). Replaces
+ * coo3d_add::coo3d_add_gpu_i32_f32 (compiler.cpp:138; merged coordinate level
+ * src/Compile.cpp:66-154). Capacity that always suffices: nnz(A) + nnz(B). */
+int nb200_coo3d_add_f32(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z,
+                        int32_t num_blocks, int32_t threads_per_block, void *stream);
+int nb200_coo3d_add_f32_into(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z,
+                             int64_t capacity, void *stream);
+
+/* Z = A + B for CSF3 operands. Replaces csf_add::csf_add_gpu_i32_f32 (compiler.cpp:135).
+ * Capacities that always suffice (for _into): i_idx n_i(A)+n_i(B); j_ptr that + 1;
+ * j_idx n_j(A)+n_j(B); k_ptr that + 1; k_idx / val n_k(A)+n_k(B). The _into form takes the
+ * three capacities (entries of i_idx, j_idx, k_idx); j_ptr / k_ptr must hold one entry more
+ * than cap_i / cap_j, and cap_k must be at least n_k(A)+n_k(B) (the merge works in place in
+ * the result's k_idx / val arrays). Extents needing more than 63 bits in total
+ * (bits(dim0)+bits(dim1)+bits(dim2)) return NB200_E_UNSUPPORTED, here and for COO3. */
+int nb200_csf_add_f32(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z,
+                      int32_t num_blocks, int32_t threads_per_block, void *stream);
+int nb200_csf_add_f32_into(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z,
+                           int64_t cap_i, int64_t cap_j, int64_t cap_k, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

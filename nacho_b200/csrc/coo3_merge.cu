@@ -1,0 +1,420 @@
+// COO3 tensor add: sorted union of two 3-mode tensors stored as parallel (i, j, k) coordinate
+// arrays, as one flat merge-path over lexicographic coordinate order.
+//
+// The reference flattens the three COO levels into one merged coordinate and compares
+// tuples (src/Compile.cpp:66-154, src/backend/tensor.cpp:447-560); its partition is the 2-way
+// merge-path with the rule that equal coordinates are never split
+// (src/backend/partition.cpp:813-993, :964-983). Here each coordinate is packed into one
+// 64-bit key, i in the top bits, then j, then k, using just enough bits for each extent, so
+// that tuple order is integer order. Tensors whose three extents need more than 63 bits in
+// total are refused with NB200_E_UNSUPPORTED.
+//
+// Kernels: k_coo3_partition (one warp per tile cut, 32-ary diagonal search) and k_coo3_tile
+// (one CTA per tile: pack keys into shared memory, split by merge-path, merge VT entries per
+// thread, rank survivors, obtain the output base -- single pass with bounded look-back, or
+// from the scanned counts of a first pass -- compact through shared memory, store coalesced).
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "merge_common.cuh"
+
+namespace nb200 {
+
+namespace {
+
+#ifndef COO3_NT
+#define COO3_NT 256
+#endif
+#ifndef COO3_VT
+#define COO3_VT 11
+#endif
+constexpr int NT = COO3_NT;
+constexpr int VT = COO3_VT;
+constexpr int CAP = NT * VT;
+constexpr int KEY_SLOTS = CAP + 2 + VT;
+constexpr uint64_t INF = ~0ull;
+
+struct Coo3In {
+    const int32_t *i, *j, *k;
+    const float *val;
+    int32_t nnz;
+};
+
+struct Coo3Out {
+    int32_t *i, *j, *k;
+    float *val;
+};
+
+struct Packing {
+    int bj, bk;  // bits of j and k; i takes the rest
+    __host__ __device__ uint64_t pack(int32_t i, int32_t j, int32_t k) const {
+        return ((((uint64_t)(uint32_t)i << bj) | (uint32_t)j) << bk) | (uint32_t)k;
+    }
+    __host__ __device__ int32_t i_of(uint64_t key) const { return (int32_t)(key >> (bj + bk)); }
+    __host__ __device__ int32_t j_of(uint64_t key) const { return (int32_t)((key >> bk) & ((1ull << bj) - 1ull)); }
+    __host__ __device__ int32_t k_of(uint64_t key) const { return (int32_t)(key & ((1ull << bk) - 1ull)); }
+};
+
+struct Cuts2 {
+    int32_t *a;
+    int32_t *b;
+};
+
+__device__ __forceinline__ uint64_t key_at(const Coo3In &T, const Packing &pk, int64_t p) {
+    return pk.pack(ld_nc(T.i + p), ld_nc(T.j + p), ld_nc(T.k + p));
+}
+
+// One warp per cut. Cut t sits at merged position min(t * tile_step, total); equal
+// coordinates stay on one side of a cut.
+__global__ void __launch_bounds__(NT) k_coo3_partition(Coo3In A, Coo3In B, Packing pk, int64_t total, int32_t tile_step,
+                                                       int32_t num_tiles, Cuts2 cuts) {
+    const int t = (blockIdx.x * NT + threadIdx.x) >> 5;
+    if (t > num_tiles) return;
+    const int64_t d = (int64_t)t * tile_step;
+    int32_t pa, pb;
+    if (t == 0) {
+        pa = pb = 0;
+    } else if (t == num_tiles || d >= total) {
+        pa = A.nnz;
+        pb = B.nnz;
+    } else {
+        const int64_t x_lo = d - B.nnz > 0 ? d - B.nnz : 0;
+        const int64_t x_hi = d < A.nnz ? d : A.nnz;
+        const int64_t x = warp_count_true(x_lo, x_hi, [&](int64_t m) { return key_at(A, pk, m) <= key_at(B, pk, d - 1 - m); });
+        int64_t y = d - x;
+        if (x > 0 && y < B.nnz && key_at(A, pk, x - 1) == key_at(B, pk, y)) ++y;
+        pa = (int32_t)x;
+        pb = (int32_t)y;
+    }
+    if (lane_id() == 0) {
+        cuts.a[t] = pa;
+        cuts.b[t] = pb;
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NT) k_coo3_tile(Coo3In A, Coo3In B, Packing pk, Cuts2 cuts, int32_t *tile_count,
+                                                  uint64_t *tile_state_raw, FusedCtl *ctl, Coo3Out Z) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int scan_tmp[72];
+    __shared__ int s_tile;
+    __shared__ long long s_base;
+    constexpr bool WRITES = MODE != MODE_COUNT;
+    volatile uint64_t *tile_state = tile_state_raw;
+    const int tid = threadIdx.x;
+    int t = blockIdx.x;
+    if (MODE == MODE_FUSED) {
+        // number tiles in the order CTAs start, so a tile only waits on running CTAs
+        if (tid == 0) s_tile = atomicAdd(&ctl->ticket, 1);
+        __syncthreads();
+        t = s_tile;
+    }
+    const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
+    const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
+    const int n = na + nb;
+
+    // Shared layout: keys of A, a sentinel, keys of B, sentinels and slack; values mirror the
+    // positions; the value staging array of the result follows (key staging reuses the keys).
+    uint64_t *kx = reinterpret_cast<uint64_t *>(smem_raw);
+    uint64_t *ky = kx + na + 1;
+    float *vx = reinterpret_cast<float *>(smem_raw + sizeof(uint64_t) * KEY_SLOTS);
+    float *vy = vx + na + 1;
+    float *out_val = vx + KEY_SLOTS;
+    uint64_t *out_key = kx;
+
+    // ---- stage: every load of a thread is issued before the first use, so that their
+    // latencies overlap; coordinates are packed on the way into shared memory
+    {
+        uint64_t hi[VT];
+#pragma unroll
+        for (int q = 0; q < VT; ++q) {
+            const int e = tid + q * NT;  // merged staging slot: A's entries first, then B's
+            hi[q] = 0;
+            if (e < na) hi[q] = ((uint64_t)(uint32_t)ld_nc(A.i + a0 + e) << pk.bj) | (uint32_t)ld_nc(A.j + a0 + e);
+            else if (e < n) hi[q] = ((uint64_t)(uint32_t)ld_nc(B.i + b0 + (e - na)) << pk.bj) | (uint32_t)ld_nc(B.j + b0 + (e - na));
+        }
+#pragma unroll
+        for (int q = 0; q < VT; ++q) {
+            const int e = tid + q * NT;
+            if (e < na) kx[e] = (hi[q] << pk.bk) | (uint32_t)ld_nc(A.k + a0 + e);
+            else if (e < n) ky[e - na] = (hi[q] << pk.bk) | (uint32_t)ld_nc(B.k + b0 + (e - na));
+        }
+        if (WRITES) {
+#pragma unroll
+            for (int q = 0; q < VT; ++q) {
+                const int e = tid + q * NT;
+                if (e < na) vx[e] = ld_nc(A.val + a0 + e);
+                else if (e < n) vy[e - na] = ld_nc(B.val + b0 + (e - na));
+            }
+        }
+        if (tid < VT + 1) ky[nb + tid] = INF;
+        if (tid == 0) kx[na] = INF;
+    }
+    __syncthreads();
+
+    // ---- split the tile among threads: merge-path diagonal tid * VT, ties take A first
+    const int diag = min(tid * VT, n);
+    int x, y;
+    {
+        int lo = max(0, diag - nb), hi = min(diag, na);
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (kx[mid] <= ky[diag - 1 - mid]) lo = mid + 1; else hi = mid;
+        }
+        x = lo;
+        y = diag - lo;
+    }
+    const int x0 = x, y0 = y;
+
+    // ---- merge VT entries, straight-line. Bit i of `from_a`: entry i came from A; of `twin`:
+    // the same coordinate is in B too; of `emit`: the entry goes to the result (B's copy of a
+    // shared coordinate does not).
+    uint64_t key[VT];
+    unsigned from_a = 0, twin = 0, emit = 0;
+    {
+        const int valid = min(VT, n - diag);
+        uint64_t hx = kx[x], hy = ky[y];
+        uint64_t last_x = x > 0 ? kx[x - 1] : INF;
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = hx <= hy;
+            const bool both = hx == hy;
+            key[i] = tx ? hx : hy;
+            from_a |= (unsigned)tx << i;
+            twin |= (unsigned)(tx && both) << i;
+            emit |= (unsigned)(i < valid && (tx || hy != last_x)) << i;
+            last_x = tx ? hx : last_x;
+            x += tx;
+            y += !tx;
+            hx = kx[x];
+            hy = ky[y];
+        }
+    }
+
+    // ---- rank the survivors inside the tile
+    int total;
+    const int mine = __popc(emit);
+    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // syncs: key reads are done
+    if (MODE == MODE_COUNT) {
+        if (tid == 0) tile_count[t] = total;
+        return;
+    }
+
+    // ---- output base of the tile
+    long long base;
+    if (MODE == MODE_FILL) {
+        base = tile_count[t];
+    } else {
+        if (warp_id() == 0) {
+            const int64_t bse = lookback_exclusive(tile_state, t, total, &ctl->status);
+            if (lane_id() == 0) s_base = bse;
+        }
+        __syncthreads();
+        base = s_base;
+        if (base < 0) return;  // a bounded wait gave up; the host reports it
+        if (t == (int)gridDim.x - 1 && tid == 0) ctl->total = base + total;
+    }
+
+    // ---- compact through shared memory, then unpack and store coalesced
+    {
+        int r = rank, xi = x0, yi = y0;
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = (from_a >> i) & 1u;
+            const bool both = (twin >> i) & 1u;
+            const bool out = (emit >> i) & 1u;
+            float v = tx ? vx[xi] : vy[yi];
+            if (both) v = v + vy[yi];
+            if (out) {
+                out_key[r] = key[i];
+                out_val[r] = v;
+            }
+            r += out;
+            xi += tx;
+            yi += !tx;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < total; i += NT) {
+        const uint64_t kq = out_key[i];
+        Z.i[base + i] = pk.i_of(kq);
+        Z.j[base + i] = pk.j_of(kq);
+        Z.k[base + i] = pk.k_of(kq);
+        Z.val[base + i] = out_val[i];
+    }
+}
+
+constexpr size_t coo3_smem_bytes() { return (sizeof(uint64_t) + 2 * sizeof(float)) * (size_t)KEY_SLOTS; }
+
+int bits_for(int32_t extent) {
+    int b = 1;
+    while (b < 32 && (int64_t(1) << b) < (int64_t)extent) ++b;
+    return b;
+}
+
+template <int MODE>
+cudaError_t launch_coo3_tile(const Coo3In &A, const Coo3In &B, const Packing &pk, const Cuts2 &cuts, int32_t *tile_count,
+                             uint64_t *tile_state, FusedCtl *ctl, const Coo3Out &Z, int num_tiles, cudaStream_t stream) {
+    auto kernel = k_coo3_tile<MODE>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)coo3_smem_bytes());
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    static const char *const names[3] = {"coo3_add_count", "coo3_add_fill", "coo3_add_fused"};
+    LaunchScope scope(names[MODE], stream);
+    kernel<<<num_tiles, NT, coo3_smem_bytes(), stream>>>(A, B, pk, cuts, tile_count, tile_state, ctl, Z);
+    return cudaGetLastError();
+}
+
+int check_coo3(const nb200_coo3 *t) {
+    if (!t || t->nnz < 0 || t->dims[0] < 0 || t->dims[1] < 0 || t->dims[2] < 0) return NB200_E_BADARG;
+    if (t->nnz > 0 && (!t->i || !t->j || !t->k || !t->val)) return NB200_E_BADARG;
+    return NB200_OK;
+}
+
+}  // namespace
+
+// Shared by the COO3 entry points and the CSF3 add (which merges expanded coordinates).
+// When `alloc` is set the four result arrays are allocated here (one cudaMallocAsync each, at
+// the worst-case length nnz(A) + nnz(B)); otherwise they are the caller's, `capacity` entries.
+//
+// `scratch` / `host_slot`, when given, replace the library's pooled workspace (the caller then
+// owns a block of coo3_add_scratch_bytes() bytes and a pinned int64[8]); the CSF3 add uses this
+// to keep its own temporaries and this function's in one pool block.
+size_t coo3_add_scratch_bytes(int64_t total_entries) {
+    const int64_t tiles = (total_entries + (CAP - 1) - 1) / (CAP - 1);
+    Carver sizes;
+    sizes.take<int32_t>((size_t)tiles + 1);
+    sizes.take<int32_t>((size_t)tiles + 1);
+    sizes.take<int32_t>((size_t)tiles + 1);
+    sizes.take<int64_t>(1);
+    sizes.take<uint64_t>((size_t)tiles + 8);
+    return sizes.used();
+}
+
+int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool alloc, int64_t capacity, void *stream_v,
+                 void *scratch, int64_t *host_slot) {
+    int st;
+    if ((st = check_coo3(a)) || (st = check_coo3(b))) return st;
+    if (!z || a->dims[0] != b->dims[0] || a->dims[1] != b->dims[1] || a->dims[2] != b->dims[2]) return NB200_E_BADARG;
+    if (!alloc && capacity < 0) return NB200_E_BADARG;
+    const int bi = bits_for(a->dims[0]), bj = bits_for(a->dims[1]), bk = bits_for(a->dims[2]);
+    if (bi + bj + bk > 63) return NB200_E_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int64_t total = (int64_t)a->nnz + b->nnz;
+    constexpr int tile_step = CAP - 1;
+    const int64_t tiles64 = (total + tile_step - 1) / tile_step;
+    if (tiles64 > INT32_MAX - 1) return NB200_E_OVERFLOW;
+    const int num_tiles = (int)tiles64;
+    for (int d = 0; d < 3; ++d) z->dims[d] = a->dims[d];
+    z->nnz = 0;
+    if (alloc) z->i = z->j = z->k = nullptr, z->val = nullptr;
+    if (num_tiles == 0) return NB200_OK;
+    if (!alloc && capacity > 0 && (!z->i || !z->j || !z->k || !z->val)) return NB200_E_BADARG;
+
+    auto fail = [&](int code) {
+        if (alloc) {
+            if (z->i) cudaFreeAsync(z->i, stream);
+            if (z->j) cudaFreeAsync(z->j, stream);
+            if (z->k) cudaFreeAsync(z->k, stream);
+            if (z->val) cudaFreeAsync(z->val, stream);
+            z->i = z->j = z->k = nullptr;
+            z->val = nullptr;
+        }
+        return code;
+    };
+
+    if (!scratch) {
+        Workspace *ws = nullptr;
+        if ((st = acquire_workspace(stream, coo3_add_scratch_bytes(total), &ws))) return st;
+        scratch = ws->dev;
+        host_slot = ws->host;
+    }
+    Carver carve(scratch);
+    Cuts2 cuts;
+    cuts.a = carve.take<int32_t>((size_t)num_tiles + 1);
+    cuts.b = carve.take<int32_t>((size_t)num_tiles + 1);
+    int32_t *tile_count = carve.take<int32_t>((size_t)num_tiles + 1);
+    int64_t *d_total = carve.take<int64_t>(1);
+    uint64_t *fused_block = carve.take<uint64_t>((size_t)num_tiles + 8);
+    FusedCtl *ctl = reinterpret_cast<FusedCtl *>(fused_block);
+    uint64_t *tile_state = fused_block + 4;
+
+    const Coo3In A{a->i, a->j, a->k, a->val, a->nnz}, B{b->i, b->j, b->k, b->val, b->nnz};
+    const Packing pk{bj, bk};
+    static const bool force_two_pass = [] { const char *e = std::getenv("NACHO_B200_TWO_PASS"); return e && e[0] == '1'; }();
+    const bool fused = alloc || (capacity >= total && !force_two_pass);
+    cudaError_t e;
+    if (fused) {
+        e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream);
+        if (e != cudaSuccess) return note_cuda_error(e, "cudaMemsetAsync");
+        if (alloc) {
+            void **arrays[4] = {reinterpret_cast<void **>(&z->i), reinterpret_cast<void **>(&z->j),
+                                reinterpret_cast<void **>(&z->k), reinterpret_cast<void **>(&z->val)};
+            for (auto p : arrays) {
+                e = cudaMallocAsync(p, 4 * (size_t)total, stream);
+                if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMallocAsync"));
+            }
+        }
+    }
+    {
+        LaunchScope scope("coo3_partition", stream);
+        const int warps = num_tiles + 1;
+        k_coo3_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "k_coo3_partition"));
+    const Coo3Out Z{z->i, z->j, z->k, z->val};
+    if (fused) {
+        e = launch_coo3_tile<MODE_FUSED>(A, B, pk, cuts, nullptr, tile_state, ctl, Z, num_tiles, stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "k_coo3_tile<fused>"));
+        e = cudaMemcpyAsync(host_slot, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "read result length"));
+        FusedCtl h;
+        std::memcpy(&h, host_slot, sizeof(h));
+        if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+        if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
+        z->nnz = (int32_t)h.total;
+        return NB200_OK;
+    }
+    e = launch_coo3_tile<MODE_COUNT>(A, B, pk, cuts, tile_count, nullptr, nullptr, Coo3Out{}, num_tiles, stream);
+    if (e != cudaSuccess) return note_cuda_error(e, "k_coo3_tile<count>");
+    {
+        LaunchScope scope("scan_tiles", stream);
+        k_scan_tiles<<<1, 1024, 0, stream>>>(tile_count, num_tiles, d_total);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) return note_cuda_error(e, "k_scan_tiles");
+    e = cudaMemcpyAsync(host_slot, d_total, sizeof(int64_t), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return note_cuda_error(e, "read result length");
+    const int64_t nnz = host_slot[0];
+    if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
+    z->nnz = (int32_t)nnz;
+    if (nnz > capacity) return NB200_E_CAPACITY;
+    e = launch_coo3_tile<MODE_FILL>(A, B, pk, cuts, tile_count, nullptr, nullptr, Z, num_tiles, stream);
+    if (e != cudaSuccess) return note_cuda_error(e, "k_coo3_tile<fill>");
+    return NB200_OK;
+}
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nb200_coo3d_add_f32(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, int32_t, int32_t, void *stream) {
+    return coo3_add_run(a, b, z, true, 0, stream, nullptr, nullptr);
+}
+
+int nb200_coo3d_add_f32_into(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, int64_t capacity, void *stream) {
+    return coo3_add_run(a, b, z, false, capacity, stream, nullptr, nullptr);
+}
+
+}  // extern "C"

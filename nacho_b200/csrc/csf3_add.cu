@@ -1,0 +1,275 @@
+// CSF3 tensor add: Z = A + B for tensors stored as three compressed levels (i list, j fibres
+// under each i, k fibres under each (i, j)). The reference emits a three-level nested union
+// (src/backend/compute.cpp:619-1392 with the runtime-exclusion partition of
+// src/backend/partition.cpp:286-328, 586-811): merge the i lists, under equal i merge the j
+// fibres, under equal (i, j) merge k, otherwise copy the subtree. The result is the unique
+// canonical tree of the union of the coordinate sets, so it is produced here in three steps
+// that reuse the flat coordinate merge:
+//   1. k_csf_expand    every stored entry gets its (i, j) written out next to its k: one thread
+//                      per (i, j) fibre finds its i by binary search and fills the fibre's range;
+//   2. coo3_add_run    the sorted-union merge of the two coordinate lists (coo3_merge.cu); k and
+//                      the values go straight into the result's k_idx / val arrays;
+//   3. k_csf_compress  one pass over the merged (i, j) columns: head flags for new i and new
+//                      (i, j), a packed two-counter scan across tiles by bounded look-back, and
+//                      the scatter of i_idx / j_ptr / j_idx / k_ptr.
+#include <algorithm>
+#include <cstring>
+
+#include "merge_common.cuh"
+
+namespace nb200 {
+
+int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool alloc, int64_t capacity, void *stream_v,
+                 void *scratch, int64_t *host_slot);
+size_t coo3_add_scratch_bytes(int64_t total_entries);
+
+namespace {
+
+constexpr int NT = 256;
+
+// One thread per (i, j) fibre q: its i is the last fibre-list start <= q; the thread then
+// writes (i, j) for every entry of the fibre.
+__global__ void __launch_bounds__(NT) k_csf_expand(int32_t n_i, int32_t n_j, const int32_t *__restrict__ i_idx,
+                                                   const int32_t *__restrict__ j_ptr, const int32_t *__restrict__ j_idx,
+                                                   const int32_t *__restrict__ k_ptr, int32_t *__restrict__ out_i,
+                                                   int32_t *__restrict__ out_j) {
+    const int q = blockIdx.x * NT + threadIdx.x;
+    if (q >= n_j) return;
+    int lo = 0, hi = n_i - 1;  // largest r with j_ptr[r] <= q
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (ld_nc(j_ptr + mid) <= q) lo = mid; else hi = mid - 1;
+    }
+    const int32_t i = ld_nc(i_idx + lo), j = ld_nc(j_idx + q);
+    const int32_t p0 = ld_nc(k_ptr + q), p1 = ld_nc(k_ptr + q + 1);
+    for (int32_t p = p0; p < p1; ++p) {
+        out_i[p] = i;
+        out_j[p] = j;
+    }
+}
+
+struct CompressCtl {
+    int ticket;
+    DeviceStatus status;
+    int n_i, n_j;
+};
+
+constexpr int CVT = 8;  // entries per thread in the compress pass
+
+// Head flags + packed scan + scatter. A tile's count is (new i's << 31 | new (i, j)'s).
+__global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t *__restrict__ zi,
+                                                     const int32_t *__restrict__ zj, int32_t cap_i, int32_t cap_j,
+                                                     int32_t *__restrict__ i_idx, int32_t *__restrict__ j_ptr,
+                                                     int32_t *__restrict__ j_idx, int32_t *__restrict__ k_ptr,
+                                                     uint64_t *tile_state_raw, CompressCtl *ctl) {
+    __shared__ int scan_tmp[72];
+    __shared__ int s_tile;
+    __shared__ long long s_base;
+    volatile uint64_t *tile_state = tile_state_raw;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_tile = atomicAdd(&ctl->ticket, 1);
+    __syncthreads();
+    const int t = s_tile;
+    const int64_t p0 = ((int64_t)t * NT + tid) * CVT;
+    int32_t ci[CVT + 1], cj[CVT + 1];
+#pragma unroll
+    for (int q = 0; q <= CVT; ++q) {
+        const int64_t p = p0 - 1 + q;
+        const bool in = p >= 0 && p < nnz;
+        ci[q] = in ? ld_nc(zi + p) : -1;
+        cj[q] = in ? ld_nc(zj + p) : -1;
+    }
+    unsigned head_i = 0, head_ij = 0;
+#pragma unroll
+    for (int q = 0; q < CVT; ++q) {
+        const bool live = p0 + q < nnz;
+        const bool ni = live && ci[q + 1] != ci[q];
+        const bool nij = live && (ni || cj[q + 1] != cj[q]);
+        head_i |= (unsigned)ni << q;
+        head_ij |= (unsigned)nij << q;
+    }
+    int tot_i, tot_ij;
+    int rank_i = block_excl_sum<NT>(__popc(head_i), scan_tmp, tot_i);
+    int rank_ij = block_excl_sum<NT>(__popc(head_ij), scan_tmp, tot_ij);
+    if (warp_id() == 0) {
+        const int64_t packed = ((int64_t)tot_i << 31) | (int64_t)tot_ij;
+        const int64_t b = lookback_exclusive(tile_state, t, packed, &ctl->status);
+        if (lane_id() == 0) s_base = b;
+    }
+    __syncthreads();
+    const long long base = s_base;
+    if (base < 0) return;
+    int r = (int)(base >> 31) + rank_i;
+    int f = (int)(base & 0x7fffffff) + rank_ij;
+#pragma unroll
+    for (int q = 0; q < CVT; ++q) {
+        const int64_t p = p0 + q;
+        if ((head_ij >> q) & 1u) {
+            if (f < cap_j) {
+                j_idx[f] = cj[q + 1];
+                k_ptr[f] = (int32_t)p;
+            }
+            if ((head_i >> q) & 1u) {
+                if (r < cap_i) {
+                    i_idx[r] = ci[q + 1];
+                    j_ptr[r] = f;
+                }
+                ++r;
+            }
+            ++f;
+        }
+    }
+    if (t == (int)gridDim.x - 1 && tid == NT - 1) {  // last thread of the last tile holds the totals
+        ctl->n_i = r;
+        ctl->n_j = f;
+        if (f <= cap_j) k_ptr[f] = nnz;
+        if (r <= cap_i) j_ptr[r] = f;
+    }
+}
+
+int check_csf3(const nb200_csf3 *t) {
+    if (!t || t->n_i < 0 || t->n_j < 0 || t->n_k < 0) return NB200_E_BADARG;
+    if (t->n_k > 0 && (!t->i_idx || !t->j_ptr || !t->j_idx || !t->k_ptr || !t->k_idx || !t->val)) return NB200_E_BADARG;
+    return NB200_OK;
+}
+
+int csf_add_run(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, bool alloc, int64_t cap_i, int64_t cap_j,
+                int64_t cap_k, void *stream_v) {
+    int st;
+    if ((st = check_csf3(a)) || (st = check_csf3(b))) return st;
+    if (!z || a->dims[0] != b->dims[0] || a->dims[1] != b->dims[1] || a->dims[2] != b->dims[2]) return NB200_E_BADARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int64_t total = (int64_t)a->n_k + b->n_k;
+    if (total > INT32_MAX) return NB200_E_OVERFLOW;
+    const int64_t bound_i = (int64_t)a->n_i + b->n_i, bound_j = (int64_t)a->n_j + b->n_j;
+    for (int d = 0; d < 3; ++d) z->dims[d] = a->dims[d];
+    z->n_i = z->n_j = z->n_k = 0;
+    cudaError_t e;
+    if (alloc) {
+        z->i_idx = z->j_ptr = z->j_idx = z->k_ptr = z->k_idx = nullptr;
+        z->val = nullptr;
+        cap_i = bound_i;
+        cap_j = bound_j;
+        cap_k = total;
+        struct { void **p; size_t n; } arrays[6] = {
+            {reinterpret_cast<void **>(&z->i_idx), (size_t)bound_i}, {reinterpret_cast<void **>(&z->j_ptr), (size_t)bound_i + 1},
+            {reinterpret_cast<void **>(&z->j_idx), (size_t)bound_j}, {reinterpret_cast<void **>(&z->k_ptr), (size_t)bound_j + 1},
+            {reinterpret_cast<void **>(&z->k_idx), (size_t)total},   {reinterpret_cast<void **>(&z->val), (size_t)total}};
+        for (auto &arr : arrays) {
+            if (arr.n == 0) continue;
+            e = cudaMallocAsync(arr.p, 4 * arr.n, stream);
+            if (e != cudaSuccess) {
+                for (auto &other : arrays) {
+                    if (*other.p) cudaFreeAsync(*other.p, stream);
+                    *other.p = nullptr;
+                }
+                return note_cuda_error(e, "cudaMallocAsync");
+            }
+        }
+    } else {
+        if (cap_i < 0 || cap_j < 0 || cap_k < 0 || !z->j_ptr || !z->k_ptr) return NB200_E_BADARG;
+        if (cap_k < total) return NB200_E_CAPACITY;  // the merge needs room for every operand entry
+        if (total > 0 && (!z->i_idx || !z->j_idx || !z->k_idx || !z->val)) return NB200_E_BADARG;
+    }
+    auto fail = [&](int code) {
+        if (alloc) {
+            void **ps[6] = {reinterpret_cast<void **>(&z->i_idx), reinterpret_cast<void **>(&z->j_ptr),
+                            reinterpret_cast<void **>(&z->j_idx), reinterpret_cast<void **>(&z->k_ptr),
+                            reinterpret_cast<void **>(&z->k_idx), reinterpret_cast<void **>(&z->val)};
+            for (auto p : ps) {
+                if (*p) cudaFreeAsync(*p, stream);
+                *p = nullptr;
+            }
+        }
+        return code;
+    };
+    if (total == 0) {  // empty result: the two offset arrays hold their single leading zero
+        e = cudaMemsetAsync(z->j_ptr, 0, sizeof(int32_t), stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(z->k_ptr, 0, sizeof(int32_t), stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
+        return NB200_OK;
+    }
+
+    // one pool block: expanded (i, j) of A, of B and of the merged list, the merge's own scratch
+    // and the compress pass's control block and tile words
+    const int64_t compress_tiles = (total + NT * CVT - 1) / (NT * CVT);
+    Carver sizes;
+    sizes.take<int32_t>((size_t)a->n_k);
+    sizes.take<int32_t>((size_t)a->n_k);
+    sizes.take<int32_t>((size_t)b->n_k);
+    sizes.take<int32_t>((size_t)b->n_k);
+    sizes.take<int32_t>((size_t)total);
+    sizes.take<int32_t>((size_t)total);
+    sizes.take<uint64_t>((size_t)compress_tiles + 8);
+    const size_t own = sizes.used();
+    Workspace *ws = nullptr;
+    if ((st = acquire_workspace(stream, own + coo3_add_scratch_bytes(total) + 256, &ws))) return fail(st);
+    Carver carve(ws->dev);
+    int32_t *ai = carve.take<int32_t>((size_t)a->n_k), *aj = carve.take<int32_t>((size_t)a->n_k);
+    int32_t *bi = carve.take<int32_t>((size_t)b->n_k), *bj = carve.take<int32_t>((size_t)b->n_k);
+    int32_t *zi = carve.take<int32_t>((size_t)total), *zj = carve.take<int32_t>((size_t)total);
+    uint64_t *compress_block = carve.take<uint64_t>((size_t)compress_tiles + 8);
+    void *merge_scratch = static_cast<unsigned char *>(ws->dev) + own;
+
+    if (a->n_j > 0) {
+        LaunchScope scope("csf_expand", stream);
+        k_csf_expand<<<(a->n_j + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
+    }
+    if (b->n_j > 0) {
+        LaunchScope scope("csf_expand", stream);
+        k_csf_expand<<<(b->n_j + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csf_expand"));
+
+    nb200_coo3 ca{{a->dims[0], a->dims[1], a->dims[2]}, a->n_k, ai, aj, a->k_idx, a->val};
+    nb200_coo3 cb{{b->dims[0], b->dims[1], b->dims[2]}, b->n_k, bi, bj, b->k_idx, b->val};
+    nb200_coo3 cz{{0, 0, 0}, 0, zi, zj, z->k_idx, z->val};
+    if ((st = coo3_add_run(&ca, &cb, &cz, false, total, stream, merge_scratch, ws->host))) return fail(st);
+    const int32_t nnz = cz.nnz;
+    z->n_k = nnz;
+
+    CompressCtl *ctl = reinterpret_cast<CompressCtl *>(compress_block);
+    static_assert(sizeof(CompressCtl) <= 4 * sizeof(uint64_t), "control block must fit its slot");
+    uint64_t *tile_state = compress_block + 4;
+    const int tiles = (int)(((int64_t)nnz + NT * CVT - 1) / (NT * CVT));
+    e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)tiles + 4), stream);
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
+    {
+        LaunchScope scope("csf_compress", stream);
+        k_csf_compress<<<tiles, NT, 0, stream>>>(nnz, zi, zj, (int32_t)std::min<int64_t>(cap_i, INT32_MAX),
+                                                 (int32_t)std::min<int64_t>(cap_j, INT32_MAX), z->i_idx, z->j_ptr, z->j_idx,
+                                                 z->k_ptr, tile_state, ctl);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csf_compress"));
+    e = cudaMemcpyAsync(ws->host, ctl, sizeof(CompressCtl), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "read result lengths"));
+    CompressCtl h;
+    std::memcpy(&h, ws->host, sizeof(h));
+    if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+    z->n_i = h.n_i;
+    z->n_j = h.n_j;
+    if (h.n_i > cap_i || h.n_j > cap_j) return fail(NB200_E_CAPACITY);
+    return NB200_OK;
+}
+
+}  // namespace
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nb200_csf_add_f32(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, int32_t, int32_t, void *stream) {
+    return csf_add_run(a, b, z, true, 0, 0, 0, stream);
+}
+
+int nb200_csf_add_f32_into(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, int64_t cap_i, int64_t cap_j,
+                           int64_t cap_k, void *stream) {
+    return csf_add_run(a, b, z, false, cap_i, cap_j, cap_k, stream);
+}
+
+}  // extern "C"

@@ -22,6 +22,7 @@
 
 #include "block_utils.cuh"
 #include "common.cuh"
+#include "merge_common.cuh"
 #include "tma.cuh"
 
 namespace nb200 {
@@ -49,7 +50,6 @@ constexpr int NT = CSR2_NT;
 #define CSR2_PHASE_END(k, keep) do { } while (0)
 #endif
 
-enum SetOp { OP_UNION = 0, OP_INTERSECT = 1 };
 
 struct CsrIn {
     const int32_t *rp;
@@ -138,19 +138,6 @@ struct KeyTraits<uint64_t> {
     __device__ static __forceinline__ uint32_t row_of(uint64_t k, int) { return (uint32_t)(k >> 32); }
     __device__ static __forceinline__ uint32_t col_of(uint64_t k, int) { return (uint32_t)k; }
     __device__ static __forceinline__ uint64_t make(uint32_t row, uint32_t col, int) { return ((uint64_t)row << 32) | col; }
-};
-
-// What one launch of the tile kernel does.
-//   MODE_COUNT  count the tile's result entries (first pass of the two-pass scheme)
-//   MODE_FILL   write the result; the tile's output base comes from the scanned counts
-//   MODE_FUSED  single pass: count, obtain the base by look-back over earlier tiles, write
-enum Mode { MODE_COUNT = 0, MODE_FILL = 1, MODE_FUSED = 2 };
-
-// Device-side control block of a fused launch.
-struct FusedCtl {
-    int ticket;           // next tile number to hand out
-    DeviceStatus status;  // bounded-wait failures
-    long long total;      // result entries, written by the last tile
 };
 
 // Generic tile body: any key width, plain loads and stores. Used for the tiles whose rows do not
@@ -716,46 +703,6 @@ __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, C
         if (threadIdx.x >= NT) return;  // the generic body works with the NT worker threads alone
         csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit);
     }
-}
-
-// Exclusive prefix of the per-tile counts, in place, by one CTA; the grand total goes to
-// *total_out (64-bit so that the host can detect int32 overflow).
-__global__ void __launch_bounds__(1024) k_scan_tiles(int32_t *counts, int32_t n, int64_t *total_out) {
-    __shared__ long long warp_sums[33];
-    __shared__ long long carry_s;
-    if (threadIdx.x == 0) carry_s = 0;
-    __syncthreads();
-    for (int base = 0; base < n; base += 1024) {
-        const int i = base + threadIdx.x;
-        const long long v = i < n ? counts[i] : 0;
-        long long incl = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            long long nb = __shfl_up_sync(FULL_MASK, incl, o);
-            if (lane_id() >= o) incl += nb;
-        }
-        if (lane_id() == 31) warp_sums[warp_id()] = incl;
-        __syncthreads();
-        if (warp_id() == 0) {
-            long long w = warp_sums[lane_id()];
-            long long wi = w;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                long long nb = __shfl_up_sync(FULL_MASK, wi, o);
-                if (lane_id() >= o) wi += nb;
-            }
-            warp_sums[lane_id()] = wi - w;
-            if (lane_id() == 31) warp_sums[32] = wi;
-        }
-        __syncthreads();
-        const long long carry = carry_s;
-        const long long excl = carry + warp_sums[warp_id()] + incl - v;
-        if (i < n) counts[i] = (int32_t)min(excl, (long long)INT32_MAX);
-        __syncthreads();
-        if (threadIdx.x == 0) carry_s = carry + warp_sums[32];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *total_out = carry_s;
 }
 
 // ------------------------------------------------------------------------ host driver ----

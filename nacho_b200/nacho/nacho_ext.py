@@ -16,9 +16,10 @@ import ctypes as C
 import torch
 
 from .. import _capi
-from .._capi import CsrStruct, lib
+from .._capi import Coo3Struct, CsrStruct, Csf3Struct, lib
 
-__all__ = ["CSR_gpu", "gpu_csr_add_f32", "gpu_csr_mul_f32"]
+__all__ = ["CSR_gpu", "COO3_gpu", "CSF3_gpu", "gpu_csr_add_f32", "gpu_csr_mul_f32", "gpu_coo3d_add_f32",
+           "gpu_csf_add_f32"]
 
 
 def _dev_array(t, dtype, name):
@@ -115,3 +116,118 @@ def gpu_csr_mul_f32(a: CSR_gpu, b: CSR_gpu, num_blocks: int = 256, threads_per_b
     """Z = A .* B (sorted intersection per row)."""
     return _csr_binary(lib.nb200_csr_mul_f32_into, "gpu_csr_mul_f32", a, b,
                        min(a.values.numel(), b.values.numel()))
+
+
+class COO3_gpu:
+    """3-mode tensor as parallel coordinate arrays:
+    ``COO3_gpu(dim_i_indices, dim_j_indices, dim_k_indices, values, shape)``."""
+
+    __slots__ = ("_i", "_j", "_k", "_values", "_shape")
+
+    def __init__(self, dim_i_indices, dim_j_indices, dim_k_indices, values, shape):
+        self._i = _dev_array(dim_i_indices, torch.int32, "dim_i_indices")
+        self._j = _dev_array(dim_j_indices, torch.int32, "dim_j_indices")
+        self._k = _dev_array(dim_k_indices, torch.int32, "dim_k_indices")
+        self._values = _dev_array(values, torch.float32, "values")
+        self._shape = _shape_array(shape, 3)
+        n = self._values.numel()
+        if not (self._i.numel() == self._j.numel() == self._k.numel() == n):
+            raise ValueError("coordinate arrays and values differ in length")
+
+    dim_i_indices = property(lambda self: self._i)
+    dim_j_indices = property(lambda self: self._j)
+    dim_k_indices = property(lambda self: self._k)
+    values = property(lambda self: self._values)
+    shape = property(lambda self: self._shape)
+
+    @property
+    def device(self):
+        return self._values.device
+
+    def _struct(self) -> Coo3Struct:
+        dims = (C.c_int32 * 3)(*[int(x) for x in self._shape])
+        return Coo3Struct(dims, self._values.numel(), self._i.data_ptr(), self._j.data_ptr(), self._k.data_ptr(),
+                          self._values.data_ptr())
+
+    def __repr__(self):
+        return f"COO3_gpu(shape={tuple(int(x) for x in self._shape)}, nnz={self._values.numel()})"
+
+
+class CSF3_gpu:
+    """3-mode tensor with three compressed levels: ``CSF3_gpu(dim_i_indices, dim_j_offsets,
+    dim_j_indices, dim_k_offsets, dim_k_indices, values, shape)``; ``dim_j_offsets`` holds
+    ``len(dim_i_indices) + 1`` entries and ``dim_k_offsets`` ``len(dim_j_indices) + 1``
+    (src/backend/generate_bindings.cpp:119-143)."""
+
+    __slots__ = ("_i", "_jp", "_j", "_kp", "_k", "_values", "_shape")
+
+    def __init__(self, dim_i_indices, dim_j_offsets, dim_j_indices, dim_k_offsets, dim_k_indices, values, shape):
+        self._i = _dev_array(dim_i_indices, torch.int32, "dim_i_indices")
+        self._jp = _dev_array(dim_j_offsets, torch.int32, "dim_j_offsets")
+        self._j = _dev_array(dim_j_indices, torch.int32, "dim_j_indices")
+        self._kp = _dev_array(dim_k_offsets, torch.int32, "dim_k_offsets")
+        self._k = _dev_array(dim_k_indices, torch.int32, "dim_k_indices")
+        self._values = _dev_array(values, torch.float32, "values")
+        self._shape = _shape_array(shape, 3)
+        if self._jp.numel() != self._i.numel() + 1 or self._kp.numel() != self._j.numel() + 1:
+            raise ValueError("offset arrays must hold one entry more than the level above has coordinates")
+        if self._k.numel() != self._values.numel():
+            raise ValueError("dim_k_indices and values differ in length")
+
+    dim_i_indices = property(lambda self: self._i)
+    dim_j_offsets = property(lambda self: self._jp)
+    dim_j_indices = property(lambda self: self._j)
+    dim_k_offsets = property(lambda self: self._kp)
+    dim_k_indices = property(lambda self: self._k)
+    values = property(lambda self: self._values)
+    shape = property(lambda self: self._shape)
+
+    @property
+    def device(self):
+        return self._values.device
+
+    def _struct(self) -> Csf3Struct:
+        dims = (C.c_int32 * 3)(*[int(x) for x in self._shape])
+        return Csf3Struct(dims, self._i.numel(), self._j.numel(), self._k.numel(), self._i.data_ptr(),
+                          self._jp.data_ptr(), self._j.data_ptr(), self._kp.data_ptr(), self._k.data_ptr(),
+                          self._values.data_ptr())
+
+    def __repr__(self):
+        return (f"CSF3_gpu(shape={tuple(int(x) for x in self._shape)}, levels=({self._i.numel()}, "
+                f"{self._j.numel()}, {self._k.numel()}))")
+
+
+def gpu_coo3d_add_f32(a: COO3_gpu, b: COO3_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> COO3_gpu:
+    """Z = A + B over sorted unique (i, j, k) coordinates."""
+    if not isinstance(a, COO3_gpu) or not isinstance(b, COO3_gpu):
+        raise TypeError("gpu_coo3d_add_f32: operands must be COO3_gpu")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    cap = sa.nnz + sb.nnz
+    with torch.cuda.device(dev):
+        zi, zj, zk = (torch.empty(max(cap, 1), dtype=torch.int32, device=dev) for _ in range(3))
+        zv = torch.empty(max(cap, 1), dtype=torch.float32, device=dev)
+        sz = Coo3Struct((C.c_int32 * 3)(), 0, zi.data_ptr(), zj.data_ptr(), zk.data_ptr(), zv.data_ptr())
+        status = lib.nb200_coo3d_add_f32_into(C.byref(sa), C.byref(sb), C.byref(sz), cap, _stream_for(zv))
+    _capi.check(status, "gpu_coo3d_add_f32")
+    n = int(sz.nnz)
+    return COO3_gpu(zi[:n], zj[:n], zk[:n], zv[:n], torch.tensor(list(sz.dims), dtype=torch.int32))
+
+
+def gpu_csf_add_f32(a: CSF3_gpu, b: CSF3_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSF3_gpu:
+    """Z = A + B for CSF3 operands."""
+    if not isinstance(a, CSF3_gpu) or not isinstance(b, CSF3_gpu):
+        raise TypeError("gpu_csf_add_f32: operands must be CSF3_gpu")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    cap_i, cap_j, cap_k = sa.n_i + sb.n_i, sa.n_j + sb.n_j, sa.n_k + sb.n_k
+    with torch.cuda.device(dev):
+        new = lambda n, dt=torch.int32: torch.empty(max(n, 1), dtype=dt, device=dev)
+        zi, zjp, zj, zkp, zk, zv = new(cap_i), new(cap_i + 1), new(cap_j), new(cap_j + 1), new(cap_k), new(cap_k, torch.float32)
+        sz = Csf3Struct((C.c_int32 * 3)(), 0, 0, 0, zi.data_ptr(), zjp.data_ptr(), zj.data_ptr(), zkp.data_ptr(),
+                        zk.data_ptr(), zv.data_ptr())
+        status = lib.nb200_csf_add_f32_into(C.byref(sa), C.byref(sb), C.byref(sz), cap_i, cap_j, cap_k, _stream_for(zv))
+    _capi.check(status, "gpu_csf_add_f32")
+    ni, nj, nk = int(sz.n_i), int(sz.n_j), int(sz.n_k)
+    return CSF3_gpu(zi[:ni], zjp[:ni + 1], zj[:nj], zkp[:nj + 1], zk[:nk], zv[:nk],
+                    torch.tensor(list(sz.dims), dtype=torch.int32))

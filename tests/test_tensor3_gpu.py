@@ -1,0 +1,124 @@
+"""GPU suite: COO3 and CSF3 tensor add through the C ABI against the golden vectors made by the
+reference's CPU kernels, against the C oracle on seeded inputs, and through properties at a
+size the oracle would not finish quickly."""
+import numpy as np
+import pytest
+
+from helpers import T3_CASES, assert_same, csf3_levels, golden_coo3, golden_csf3
+from oracle.cpu_oracle import COO3, CSF3
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nacho():
+    import torch
+    assert torch.cuda.is_available(), "GPU suite needs a CUDA device"
+    from nacho_b200 import nacho as mod
+    return mod
+
+
+def coo3_to_gpu(nacho, t: COO3):
+    coords = np.stack([t.i, t.j, t.k], axis=1).reshape(-1, 3)
+    return nacho.to_coo3(coords, t.val, t.dims, "cuda")
+
+
+def coo3_from_gpu(z) -> COO3:
+    import torch
+    torch.cuda.synchronize()
+    return COO3(tuple(int(x) for x in z.shape), z.dim_i_indices.cpu().numpy(), z.dim_j_indices.cpu().numpy(),
+                z.dim_k_indices.cpu().numpy(), z.values.cpu().numpy())
+
+
+def csf3_from_gpu(z) -> CSF3:
+    import torch
+    torch.cuda.synchronize()
+    return CSF3(tuple(int(x) for x in z.shape), z.dim_i_indices.cpu().numpy(), z.dim_j_offsets.cpu().numpy(),
+                z.dim_j_indices.cpu().numpy(), z.dim_k_offsets.cpu().numpy(), z.dim_k_indices.cpu().numpy(),
+                z.values.cpu().numpy())
+
+
+@pytest.mark.parametrize("case", T3_CASES)
+def test_golden_coo3_and_csf3(nacho, tensor3_golden, case):
+    a, b = golden_coo3(tensor3_golden, case, "a"), golden_coo3(tensor3_golden, case, "b")
+    z = nacho.gpu_coo3d_add_f32(coo3_to_gpu(nacho, a), coo3_to_gpu(nacho, b))
+    assert_same(coo3_from_gpu(z), golden_coo3(tensor3_golden, case, "coo3"), f"{case} coo3")
+    ca, cb = np.stack([a.i, a.j, a.k], 1).reshape(-1, 3), np.stack([b.i, b.j, b.k], 1).reshape(-1, 3)
+    f = nacho.gpu_csf_add_f32(nacho.to_csf3(ca, a.val, a.dims, "cuda"), nacho.to_csf3(cb, b.val, b.dims, "cuda"))
+    assert_same(csf3_from_gpu(f), golden_csf3(tensor3_golden, case), f"{case} csf3")
+
+
+def _seeded(dims, n, seed, overlap=0.3):
+    rng = np.random.default_rng(seed)
+    def draw(m):
+        c = np.unique(np.stack([rng.integers(0, e, m) for e in dims], axis=1), axis=0)
+        return c
+    ca = draw(n)
+    keep = ca[rng.random(len(ca)) < overlap]
+    cb = np.unique(np.concatenate([keep, draw(n)]), axis=0)
+    va = rng.uniform(-1, 1, len(ca)).astype(np.float32)
+    vb = rng.uniform(-1, 1, len(cb)).astype(np.float32)
+    return (ca.astype(np.int32), va), (cb.astype(np.int32), vb)
+
+
+@pytest.mark.parametrize("dims,n,seed", [((40, 30, 25), 900, 1), ((1 << 12, 1 << 10, 1 << 8), 200_000, 2),
+                                          ((5, 1 << 16, 1 << 12), 150_000, 3), ((1 << 17, 4, 4), 100_000, 4),
+                                          ((3, 3, 1 << 20), 50_000, 5)])
+def test_seeded_vs_oracle(nacho, oracle, dims, n, seed):
+    (ca, va), (cb, vb) = _seeded(dims, n, seed)
+    a, b = COO3(dims, ca[:, 0], ca[:, 1], ca[:, 2], va), COO3(dims, cb[:, 0], cb[:, 1], cb[:, 2], vb)
+    z = nacho.gpu_coo3d_add_f32(nacho.to_coo3(ca, va, dims, "cuda"), nacho.to_coo3(cb, vb, dims, "cuda"))
+    assert_same(coo3_from_gpu(z), oracle.coo3_add(a, b, 8), "coo3")
+    fa, fb = CSF3(dims, *csf3_levels(ca), va), CSF3(dims, *csf3_levels(cb), vb)
+    f = nacho.gpu_csf_add_f32(nacho.to_csf3(ca, va, dims, "cuda"), nacho.to_csf3(cb, vb, dims, "cuda"))
+    assert_same(csf3_from_gpu(f), oracle.csf3_add(fa, fb), "csf3")
+
+
+def test_config5_reduced_vs_oracle(nacho, oracle):
+    """Configuration 5 at one hundredth of its entry count (same extents and slice skew)."""
+    from nacho_b200 import synth
+    ta, tb = synth.c5_pair(nnz=1_000_000, seed=5100)
+    def to_np(t):
+        dims, i, j, k, v = synth.to_numpy(t)
+        return COO3(dims, i, j, k, v)
+    a, b = to_np(ta), to_np(tb)
+    z = nacho.gpu_coo3d_add_f32(coo3_to_gpu(nacho, a), coo3_to_gpu(nacho, b))
+    want = oracle.coo3_add(a, b, 8)
+    assert_same(coo3_from_gpu(z), want, "config 5 (1 M entries) coo3")
+    ca, cb = np.stack([a.i, a.j, a.k], 1), np.stack([b.i, b.j, b.k], 1)
+    f = nacho.gpu_csf_add_f32(nacho.to_csf3(ca, a.val, a.dims, "cuda"), nacho.to_csf3(cb, b.val, b.dims, "cuda"))
+    fa, fb = CSF3(a.dims, *csf3_levels(ca), a.val), CSF3(b.dims, *csf3_levels(cb), b.val)
+    assert_same(csf3_from_gpu(f), oracle.csf3_add(fa, fb), "config 5 (1 M entries) csf3")
+
+
+def test_coo3_properties_at_scale(nacho):
+    """20 M entries per operand with configuration 5's extents: properties of a sorted union."""
+    import torch
+    from nacho_b200 import synth
+    ta, tb = synth.c5_pair(nnz=20_000_000, seed=5200, device="cuda")
+    mk = lambda t: nacho.COO3_gpu(t[1], t[2], t[3], t[4], torch.tensor(list(t[0]), dtype=torch.int32))
+    a, b = mk(ta), mk(tb)
+    z = nacho.gpu_coo3d_add_f32(a, b)
+    torch.cuda.synchronize()
+    d1, d2 = ta[0][1], ta[0][2]
+    key = lambda t: (t.dim_i_indices.to(torch.int64) * d1 + t.dim_j_indices.to(torch.int64)) * d2 + t.dim_k_indices.to(torch.int64)
+    ka, kb, kz = key(a), key(b), key(z)
+    assert bool((kz[1:] > kz[:-1]).all()), "result coordinates not strictly increasing"
+    union = torch.unique(torch.cat([ka, kb]))
+    assert torch.equal(union, kz)
+    s = lambda t: float(t.values.to(torch.float64).sum())
+    assert abs(s(z) - (s(a) + s(b))) <= 1e-3
+    # adding B again keeps the coordinate set (idempotent structure)
+    z2 = nacho.gpu_coo3d_add_f32(z, b)
+    assert torch.equal(key(z2), kz)
+
+
+def test_too_wide_extents_are_refused(nacho):
+    import torch
+    from nacho_b200._capi import NachoB200Error
+    dims = (1 << 30, 1 << 30, 1 << 30)
+    c = np.array([[1, 2, 3]], np.int32)
+    v = np.ones(1, np.float32)
+    t = nacho.to_coo3(c, v, dims, "cuda")
+    with pytest.raises(NachoB200Error):
+        nacho.gpu_coo3d_add_f32(t, t)
