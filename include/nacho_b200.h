@@ -160,6 +160,36 @@ int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
 int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
                            int64_t capacity, void *stream);
 
+/* Z = (A + B) + C in one pass, left-to-right association. Replaces
+ * csr_add_3::csr_add_3_gpu_i32_f32 (compiler.cpp:114; src/backend/compute.cpp:426-432).
+ * Capacity that always suffices: nnz(A) + nnz(B) + nnz(C). */
+int nb200_csr_add_3_f32(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c,
+                        nb200_csr *z, int32_t num_blocks, int32_t threads_per_block,
+                        void *stream);
+int nb200_csr_add_3_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c,
+                             nb200_csr *z, int64_t capacity, void *stream);
+
+/* ---- SpGEMM ----------------------------------------------------------------------------- */
+
+/* C = A * B by expand-sort-compress; columns sorted per row, explicit zeros kept, rows
+ * without products empty. Replaces spgemm::spgemm_gpu_i32_f32 (compiler.cpp:145-148;
+ * expand src/backend/compute.cpp:526-611, sort/compress
+ * src/backend/stitch_and_generate_gpu.cpp:14-139,257-363). Unlike the reference, product
+ * counts are 64-bit (a product count above 2^31 is fine as long as nnz(C) fits int32) and
+ * rows with at most 2048 products sum equal-column products in a fixed order (ascending j);
+ * longer rows accumulate in float64 with atomics. Rows longer than 2048 products need a dense
+ * per-row accumulator over B's column range; if one such accumulator exceeds 2 GiB the call
+ * returns NB200_E_NOMEM / NB200_E_UNSUPPORTED. */
+int nb200_spgemm_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int32_t num_blocks,
+                     int32_t threads_per_block, void *stream);
+/* Two-step form for caller-owned memory: _symbolic fills c->row_ptr (rows + 1, caller-owned)
+ * and c->nnz; the caller then provides col/val of c->nnz entries to _numeric.
+ * `products` (may be NULL) receives the number of scalar products. */
+int nb200_spgemm_f32_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
+                              int64_t *products, void *stream);
+int nb200_spgemm_f32_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
+                             void *stream);
+
 /* ---- 3-mode tensor add ------------------------------------------------------------------ */
 
 /* Z = A + B over lexicographically sorted unique (i, j, k). Replaces

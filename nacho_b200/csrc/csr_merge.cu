@@ -878,6 +878,28 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     return NB200_OK;
 }
 
+// Three-operand add Z = (A + B) + C. The association is the reference's
+// (src/backend/compute.cpp:426-432 builds a + b first), so running the two-operand union twice
+// gives bit-identical values to the reference's fused three-way merge: positions present in A
+// and C only hold a + c, in B and C only b + c, in all three (a + b) + c, and explicit zeros
+// stay. The intermediate A + B lives in stream-ordered allocations that are released before
+// the call returns; it costs one extra write and read of that intermediate compared with a
+// single three-way pass.
+int csr_add3_run(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z, bool alloc,
+                 int64_t capacity, void *stream_v) {
+    int st;
+    if ((st = check_csr(c, true))) return st;
+    if (!a || !b || a->rows != c->rows || a->cols != c->cols) return NB200_E_BADARG;
+    nb200_csr t{};
+    if ((st = csr2_run<OP_UNION>(a, b, &t, true, 0, stream_v))) return st;
+    st = csr2_run<OP_UNION>(&t, c, z, alloc, capacity, stream_v);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (t.row_ptr) cudaFreeAsync(t.row_ptr, stream);
+    if (t.col) cudaFreeAsync(t.col, stream);
+    if (t.val) cudaFreeAsync(t.val, stream);
+    return st;
+}
+
 // ------------------------------------------------------- entry point that allocates nothing ----
 
 // Scratch of nb200_csr_add_f32_noalloc: tile cuts, the single-pass control block and one
@@ -984,6 +1006,16 @@ int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int3
 
 int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {
     return csr2_run<OP_INTERSECT>(a, b, z, false, capacity, stream);
+}
+
+int nb200_csr_add_3_f32(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z, int32_t, int32_t,
+                        void *stream) {
+    return csr_add3_run(a, b, c, z, true, 0, stream);
+}
+
+int nb200_csr_add_3_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z,
+                             int64_t capacity, void *stream) {
+    return csr_add3_run(a, b, c, z, false, capacity, stream);
 }
 
 int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {

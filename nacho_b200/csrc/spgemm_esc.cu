@@ -1,0 +1,488 @@
+// SpGEMM C = A * B by expand - sort - compress, row by row.
+//
+// What the reference does (GPU only, compiler.cpp:145-148): expand every product
+// a.values[p] * b.values[q] with key k = b.cols[q] in (i, j ascending, k ascending) order
+// (src/backend/compute.cpp:526-611), sort each row's products by k with a global segmented sort
+// (src/backend/stitch_and_generate_gpu.cpp:79-94), flag run heads, scan, and sum runs with
+// warp shuffles plus atomics (:96-124, :257-363). All its counters are int32 and it
+// materialises every product in HBM.
+//
+// Here rows are binned by their product count P_i (64-bit counters throughout) and each bin
+// keeps its products on chip:
+//   small   P_i <= 32     one warp per row: products in registers, bitonic sort by shuffles
+//   medium  P_i <= 2048   one CTA per row: products in shared memory, bitonic sort there
+//   long    P_i  > 2048   a dense accumulator per row (bitmap + float64 values over the column
+//                         range, L2 resident), filled with atomics, compacted by a bitmap scan
+// Two passes: symbolic (unique columns per row -> row offsets by a scan) and numeric (fill).
+// Small and medium rows sum equal-column products in expansion order (ascending j), a fixed
+// order; long rows sum in float64 with atomics.
+#include <algorithm>
+#include <cstring>
+
+#include "merge_common.cuh"
+
+namespace nb200 {
+
+namespace {
+
+constexpr int SMALL_P = 32;
+constexpr int MEDIUM_P = 2048;
+constexpr int MED_NT = 128;
+constexpr int LONG_NT = 256;
+
+struct CsrView {
+    const int32_t *rp;
+    const int32_t *col;
+    const float *val;
+};
+
+// Device-side counters of one call.
+struct EscCtl {
+    unsigned long long products;
+    int n_small, n_medium, n_long;
+    int pad;
+};
+
+struct RowLists {
+    int32_t *small_rows, *medium_rows, *long_rows;
+};
+
+// Expand phase 1 (src/backend/compute.cpp:541-611): per-row product counts, and the bins.
+// Rows without products get their count (0) written here.
+__global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32_t rows, int32_t *__restrict__ row_count,
+                                                     RowLists lists, EscCtl *ctl) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    unsigned long long p = 0;
+    if (i < rows) {
+        const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
+        for (int32_t e = lo; e < hi; ++e) {
+            const int32_t j = ld_nc(A.col + e);
+            p += (unsigned long long)(ld_nc(B.rp + j + 1) - ld_nc(B.rp + j));
+        }
+        if (p == 0) {
+            if (row_count) row_count[i] = 0;
+        } else if (p <= SMALL_P) {
+            lists.small_rows[atomicAdd(&ctl->n_small, 1)] = i;
+        } else if (p <= MEDIUM_P) {
+            lists.medium_rows[atomicAdd(&ctl->n_medium, 1)] = i;
+        } else {
+            lists.long_rows[atomicAdd(&ctl->n_long, 1)] = i;
+        }
+    }
+    // one atomic per warp for the product total
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL_MASK, p, o);
+    if (lane_id() == 0 && p) atomicAdd(&ctl->products, p);
+}
+
+// ------------------------------------------------------------------------- small rows ----
+
+// Compare-exchange step of a 32-wide bitonic sort held one key per lane.
+__device__ __forceinline__ uint64_t warp_bitonic_sort(uint64_t key) {
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const uint64_t other = __shfl_xor_sync(FULL_MASK, key, j);
+            const bool up = (lane_id() & k) == 0;        // ascending block?
+            const bool lower = (lane_id() & j) == 0;     // lower lane of the pair?
+            const bool take_min = up == lower;
+            key = take_min ? min(key, other) : max(key, other);
+        }
+    }
+    return key;
+}
+
+// One warp per row with at most 32 products. Lane l holds product l of the row's expansion
+// order; the sort key is (column << 32 | l), so equal columns stay in expansion order.
+template <bool NUMERIC>
+__global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const int32_t *__restrict__ row_list, int n_rows,
+                                                   int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
+                                                   int32_t *__restrict__ c_col, float *__restrict__ c_val) {
+    const int w = (blockIdx.x * 256 + threadIdx.x) >> 5;
+    if (w >= n_rows) return;
+    const int lane = lane_id();
+    const int32_t i = ld_nc(row_list + w);
+    const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
+    uint32_t my_col = 0;
+    float my_val = 0.f;
+    bool have = false;
+    int base = 0;
+    for (int32_t e = lo; e < hi; ++e) {  // uniform across the warp
+        const int32_t j = ld_nc(A.col + e);
+        const int32_t b_lo = ld_nc(B.rp + j), len = ld_nc(B.rp + j + 1) - b_lo;
+        if (lane >= base && lane < base + len) {
+            my_col = (uint32_t)ld_nc(B.col + b_lo + (lane - base));
+            if (NUMERIC) my_val = ld_nc(A.val + e) * ld_nc(B.val + b_lo + (lane - base));
+            have = true;
+        }
+        base += len;
+    }
+    uint64_t key = have ? (((uint64_t)my_col << 32) | (uint32_t)lane) : ~0ull;
+    key = warp_bitonic_sort(key);
+    const uint32_t col = (uint32_t)(key >> 32);
+    const int src = (int)(key & 31u);
+    const bool valid = key != ~0ull;
+    const uint32_t prev_col = __shfl_up_sync(FULL_MASK, col, 1);
+    const bool head = valid && (lane == 0 || prev_col != col);
+    const unsigned heads = __ballot_sync(FULL_MASK, head);
+    if (!NUMERIC) {
+        if (lane == 0) row_count[i] = __popc(heads);
+        return;
+    }
+    float v = __shfl_sync(FULL_MASK, my_val, src);  // value of the product now at this lane
+    float acc = v;
+#pragma unroll
+    for (int t = 1; t < 32; ++t) {  // head lanes add their run in sorted (= expansion) order
+        const float nv = __shfl_down_sync(FULL_MASK, v, t);
+        const uint32_t nc = __shfl_down_sync(FULL_MASK, col, t);
+        const bool nvalid = __shfl_down_sync(FULL_MASK, (int)valid, t) != 0;
+        if (lane + t < 32 && nvalid && nc == col) acc += nv;
+    }
+    if (head) {
+        const int pos = ld_nc(c_rp + i) + __popc(heads & ((1u << lane) - 1u));
+        c_col[pos] = (int32_t)col;
+        c_val[pos] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------ medium rows ----
+
+// One CTA per row with at most MEDIUM_P products: expand into shared memory in expansion
+// order, bitonic sort on (column << 32 | expansion index), then each run head sums its run.
+template <bool NUMERIC>
+__global__ void __launch_bounds__(MED_NT) k_esc_medium(CsrView A, CsrView B, const int32_t *__restrict__ row_list,
+                                                       int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
+                                                       int32_t *__restrict__ c_col, float *__restrict__ c_val) {
+    __shared__ uint64_t keys[MEDIUM_P];
+    __shared__ float vals[NUMERIC ? MEDIUM_P : 1];
+    __shared__ int scan_tmp[40];
+    const int tid = threadIdx.x;
+    const int32_t i = ld_nc(row_list + blockIdx.x);
+    const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
+
+    int p_total = 0;
+    for (int32_t chunk = lo; chunk < hi; chunk += MED_NT) {  // expand phase 2, MED_NT entries of A at a time
+        const int32_t e = chunk + tid;
+        int32_t b_lo = 0, len = 0;
+        float a = 0.f;
+        if (e < hi) {
+            const int32_t j = ld_nc(A.col + e);
+            b_lo = ld_nc(B.rp + j);
+            len = ld_nc(B.rp + j + 1) - b_lo;
+            if (NUMERIC) a = ld_nc(A.val + e);
+        }
+        int chunk_total;
+        const int off = block_excl_sum<MED_NT>(len, scan_tmp, chunk_total);
+        for (int q = 0; q < len; ++q) {
+            const int idx = p_total + off + q;
+            keys[idx] = ((uint64_t)(uint32_t)ld_nc(B.col + b_lo + q) << 32) | (uint32_t)idx;
+            if (NUMERIC) vals[idx] = a * ld_nc(B.val + b_lo + q);
+        }
+        p_total += chunk_total;
+    }
+    int n2 = 2;
+    while (n2 < p_total) n2 <<= 1;
+    for (int p = p_total + tid; p < n2; p += MED_NT) keys[p] = ~0ull;
+    __syncthreads();
+
+    for (int k = 2; k <= n2; k <<= 1) {  // sort
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int p = tid; p < (n2 >> 1); p += MED_NT) {
+                const int i1 = 2 * j * (p / j) + (p % j), i2 = i1 + j;
+                const bool up = (i1 & k) == 0;
+                const uint64_t x = keys[i1], y = keys[i2];
+                if ((x > y) == up) {
+                    keys[i1] = y;
+                    keys[i2] = x;
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // compress: thread t looks after sorted positions [t * per, (t + 1) * per)
+    const int per = (n2 + MED_NT - 1) / MED_NT;
+    const int p_lo = min(tid * per, p_total), p_hi = min(p_lo + per, p_total);
+    int heads = 0;
+    for (int p = p_lo; p < p_hi; ++p) heads += p == 0 || (uint32_t)(keys[p] >> 32) != (uint32_t)(keys[p - 1] >> 32);
+    int unique;
+    int rank = block_excl_sum<MED_NT>(heads, scan_tmp, unique);
+    if (!NUMERIC) {
+        if (tid == 0) row_count[i] = unique;
+        return;
+    }
+    const int32_t out = ld_nc(c_rp + i);
+    for (int p = p_lo; p < p_hi; ++p) {
+        const uint32_t col = (uint32_t)(keys[p] >> 32);
+        if (p == 0 || col != (uint32_t)(keys[p - 1] >> 32)) {
+            float acc = vals[(uint32_t)keys[p]];
+            for (int q = p + 1; q < p_total && (uint32_t)(keys[q] >> 32) == col; ++q) acc += vals[(uint32_t)keys[q]];
+            c_col[out + rank] = (int32_t)col;
+            c_val[out + rank] = acc;
+            ++rank;
+        }
+    }
+}
+
+// -------------------------------------------------------------------------- long rows ----
+
+// Dense accumulator of one long row: a bit per column, and (numeric pass) a float64 per column.
+struct LongSlots {
+    uint32_t *bitmap;  // slots x words
+    double *acc;       // slots x cols (numeric only)
+    int32_t words;
+    int32_t cols;
+};
+
+// A CTA takes long rows round-robin and owns one accumulator slot. Products are scattered
+// with atomics; the row is then read off the bitmap in column order and the slot is wiped
+// for the next row (only where it was touched).
+template <bool NUMERIC>
+__global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, const int32_t *__restrict__ row_list, int n_rows,
+                                                      LongSlots slots, int32_t *__restrict__ row_count,
+                                                      const int32_t *__restrict__ c_rp, int32_t *__restrict__ c_col,
+                                                      float *__restrict__ c_val) {
+    __shared__ int scan_tmp[40];
+    const int tid = threadIdx.x;
+    uint32_t *bitmap = slots.bitmap + (size_t)blockIdx.x * slots.words;
+    double *acc = NUMERIC ? slots.acc + (size_t)blockIdx.x * slots.cols : nullptr;
+    for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+        const int32_t i = ld_nc(row_list + r);
+        const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
+        for (int32_t e = lo + warp_id(); e < hi; e += LONG_NT / 32) {
+            const int32_t j = ld_nc(A.col + e);
+            const int32_t b_lo = ld_nc(B.rp + j), b_hi = ld_nc(B.rp + j + 1);
+            const float a = NUMERIC ? ld_nc(A.val + e) : 0.f;
+            for (int32_t q = b_lo + lane_id(); q < b_hi; q += 32) {
+                const uint32_t col = (uint32_t)ld_nc(B.col + q);
+                atomicOr(bitmap + (col >> 5), 1u << (col & 31u));
+                if (NUMERIC) atomicAdd(acc + col, (double)(a * ld_nc(B.val + q)));
+            }
+        }
+        __syncthreads();
+        int base = 0;
+        const int32_t out = NUMERIC ? ld_nc(c_rp + i) : 0;
+        for (int w0 = 0; w0 < slots.words; w0 += LONG_NT) {
+            const int w = w0 + tid;
+            uint32_t bits = w < slots.words ? __ldcg(bitmap + w) : 0u;
+            int chunk_total;
+            int pos = block_excl_sum<LONG_NT>(__popc(bits), scan_tmp, chunk_total);
+            if (bits) {
+                bitmap[w] = 0u;
+                if (NUMERIC) {
+                    pos += out + base;
+                    while (bits) {
+                        const uint32_t col = (uint32_t)w * 32u + (uint32_t)(__ffs(bits) - 1);
+                        bits &= bits - 1;
+                        c_col[pos] = (int32_t)col;
+                        c_val[pos] = (float)__ldcg(acc + col);
+                        acc[col] = 0.0;
+                        ++pos;
+                    }
+                }
+            }
+            base += chunk_total;
+        }
+        if (!NUMERIC && tid == 0) row_count[i] = base;
+        __syncthreads();
+    }
+}
+
+// Turns the exclusive prefix of the per-row counts into row offsets (rows + 1 entries).
+__global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restrict__ excl, const int64_t *__restrict__ total,
+                                                         int32_t rows, int32_t *__restrict__ c_rp) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i < rows) c_rp[i] = excl[i];
+    if (i == rows) c_rp[rows] = (int32_t)min(*total, (int64_t)INT32_MAX);
+}
+
+// ------------------------------------------------------------------------ host driver ----
+
+int check_operand(const nb200_csr *m) {
+    if (!m || m->rows < 0 || m->cols < 0 || m->nnz < 0 || !m->row_ptr) return NB200_E_BADARG;
+    if (m->nnz > 0 && (!m->col || !m->val)) return NB200_E_BADARG;
+    return NB200_OK;
+}
+
+constexpr size_t LONG_SLOT_BUDGET = size_t(2) << 30;  // bytes of accumulator slots per call
+
+struct EscPlan {
+    Workspace *ws;
+    RowLists lists;
+    int32_t *row_count;  // rows entries (symbolic pass)
+    int64_t *d_total;
+    EscCtl *ctl;
+    LongSlots slots;
+    int n_slots;
+    EscCtl host;  // counters read back after the row-work kernel
+};
+
+// Bins the rows (kernel + one read-back) and carves the scratch of one pass.
+int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream_t stream, EscPlan *plan) {
+    const int32_t rows = a->rows;
+    const int32_t words = (b->cols + 31) / 32;
+    const size_t slot_bytes = (size_t)words * 4 + (numeric ? (size_t)b->cols * 8 : 0);
+    int max_slots = (int)std::min<size_t>(2 * 148, std::max<size_t>(1, LONG_SLOT_BUDGET / std::max<size_t>(slot_bytes, 1)));
+    Carver sizes;
+    sizes.take<int32_t>((size_t)rows);
+    sizes.take<int32_t>((size_t)rows);
+    sizes.take<int32_t>((size_t)rows);
+    sizes.take<int32_t>((size_t)rows + 1);
+    sizes.take<int64_t>(1);
+    sizes.take<EscCtl>(1);
+    const size_t fixed = sizes.used();
+    // the slots are only needed if there are long rows, which is known after the row-work
+    // kernel; reserve them up front so that the pool block does not move in between
+    int st;
+    if ((st = acquire_workspace(stream, fixed + (size_t)max_slots * (slot_bytes + 512) + 1024, &plan->ws))) {
+        if (st != NB200_E_NOMEM || max_slots == 1) return st;
+        max_slots = 1;
+        if ((st = acquire_workspace(stream, fixed + slot_bytes + 2048, &plan->ws))) return st;
+    }
+    Carver carve(plan->ws->dev);
+    plan->lists.small_rows = carve.take<int32_t>((size_t)rows);
+    plan->lists.medium_rows = carve.take<int32_t>((size_t)rows);
+    plan->lists.long_rows = carve.take<int32_t>((size_t)rows);
+    plan->row_count = carve.take<int32_t>((size_t)rows + 1);
+    plan->d_total = carve.take<int64_t>(1);
+    plan->ctl = carve.take<EscCtl>(1);
+    plan->slots.words = words;
+    plan->slots.cols = b->cols;
+    plan->slots.bitmap = carve.take<uint32_t>((size_t)max_slots * words);
+    plan->slots.acc = numeric ? carve.take<double>((size_t)max_slots * b->cols) : nullptr;
+    plan->n_slots = max_slots;
+
+    NB200_CUDA(cudaMemsetAsync(plan->ctl, 0, sizeof(EscCtl), stream));
+    const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val};
+    if (rows > 0) {
+        LaunchScope scope("esc_rowwork", stream);
+        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, numeric ? nullptr : plan->row_count, plan->lists, plan->ctl);
+        NB200_CUDA(cudaGetLastError());
+    }
+    NB200_CUDA(cudaMemcpyAsync(plan->ws->host, plan->ctl, sizeof(EscCtl), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaStreamSynchronize(stream));
+    std::memcpy(&plan->host, plan->ws->host, sizeof(EscCtl));
+    if (plan->host.n_long > 0) {
+        plan->n_slots = std::min(plan->n_slots, plan->host.n_long);
+        NB200_CUDA(cudaMemsetAsync(plan->slots.bitmap, 0, (size_t)plan->n_slots * words * 4, stream));
+        if (numeric) NB200_CUDA(cudaMemsetAsync(plan->slots.acc, 0, (size_t)plan->n_slots * b->cols * 8, stream));
+    }
+    return NB200_OK;
+}
+
+template <bool NUMERIC>
+int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, const nb200_csr *c, cudaStream_t stream) {
+    const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val};
+    int32_t *count = NUMERIC ? nullptr : plan.row_count;
+    const int32_t *c_rp = NUMERIC ? c->row_ptr : nullptr;
+    int32_t *c_col = NUMERIC ? c->col : nullptr;
+    float *c_val = NUMERIC ? c->val : nullptr;
+    if (plan.host.n_small > 0) {
+        LaunchScope scope(NUMERIC ? "esc_small_numeric" : "esc_small_symbolic", stream);
+        const int warps = plan.host.n_small;
+        k_esc_small<NUMERIC><<<(warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
+        NB200_CUDA(cudaGetLastError());
+    }
+    if (plan.host.n_medium > 0) {
+        LaunchScope scope(NUMERIC ? "esc_medium_numeric" : "esc_medium_symbolic", stream);
+        k_esc_medium<NUMERIC><<<plan.host.n_medium, MED_NT, 0, stream>>>(A, B, plan.lists.medium_rows, count, c_rp, c_col, c_val);
+        NB200_CUDA(cudaGetLastError());
+    }
+    if (plan.host.n_long > 0) {
+        LaunchScope scope(NUMERIC ? "esc_long_numeric" : "esc_long_symbolic", stream);
+        k_esc_long<NUMERIC><<<plan.n_slots, LONG_NT, 0, stream>>>(A, B, plan.lists.long_rows, plan.host.n_long, plan.slots, count, c_rp,
+                                                                 c_col, c_val);
+        NB200_CUDA(cudaGetLastError());
+    }
+    return NB200_OK;
+}
+
+int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_t *products, void *stream_v) {
+    int st;
+    if ((st = check_operand(a)) || (st = check_operand(b))) return st;
+    if (!c || !c->row_ptr || a->cols != b->rows) return NB200_E_BADARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    c->rows = a->rows;
+    c->cols = b->cols;
+    c->nnz = 0;
+    if (products) *products = 0;
+    if (a->rows == 0) {
+        NB200_CUDA(cudaMemsetAsync(c->row_ptr, 0, sizeof(int32_t), stream));
+        return NB200_OK;
+    }
+    EscPlan plan{};
+    if ((st = esc_prepare(a, b, false, stream, &plan))) return st;
+    if (products) *products = (int64_t)plan.host.products;
+    if ((st = esc_run_bins<false>(a, b, plan, nullptr, stream))) return st;
+    {
+        LaunchScope scope("scan_tiles", stream);
+        k_scan_tiles<<<1, 1024, 0, stream>>>(plan.row_count, a->rows, plan.d_total);
+        NB200_CUDA(cudaGetLastError());
+    }
+    {
+        LaunchScope scope("esc_row_offsets", stream);
+        k_esc_row_offsets<<<(a->rows + 256) / 256, 256, 0, stream>>>(plan.row_count, plan.d_total, a->rows, c->row_ptr);
+        NB200_CUDA(cudaGetLastError());
+    }
+    NB200_CUDA(cudaMemcpyAsync(plan.ws->host, plan.d_total, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaStreamSynchronize(stream));
+    const int64_t nnz = plan.ws->host[0];
+    if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
+    c->nnz = (int32_t)nnz;
+    return NB200_OK;
+}
+
+int spgemm_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, void *stream_v) {
+    int st;
+    if ((st = check_operand(a)) || (st = check_operand(b))) return st;
+    if (!c || !c->row_ptr || a->cols != b->rows || c->nnz < 0) return NB200_E_BADARG;
+    if (c->nnz > 0 && (!c->col || !c->val)) return NB200_E_BADARG;
+    if (a->rows == 0 || c->nnz == 0) return NB200_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    EscPlan plan{};
+    if ((st = esc_prepare(a, b, true, stream, &plan))) return st;
+    return esc_run_bins<true>(a, b, plan, c, stream);
+}
+
+}  // namespace
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nb200_spgemm_f32_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_t *products, void *stream) {
+    return spgemm_symbolic(a, b, c, products, stream);
+}
+
+int nb200_spgemm_f32_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, void *stream) {
+    return spgemm_numeric(a, b, c, stream);
+}
+
+int nb200_spgemm_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int32_t, int32_t, void *stream_v) {
+    if (!a || !c) return NB200_E_BADARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    c->row_ptr = nullptr;
+    c->col = nullptr;
+    c->val = nullptr;
+    NB200_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&c->row_ptr), sizeof(int32_t) * ((size_t)std::max(a->rows, 0) + 1), stream));
+    int st = spgemm_symbolic(a, b, c, nullptr, stream_v);
+    if (st == NB200_OK && c->nnz > 0) {
+        cudaError_t e = cudaMallocAsync(reinterpret_cast<void **>(&c->col), sizeof(int32_t) * (size_t)c->nnz, stream);
+        if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&c->val), sizeof(float) * (size_t)c->nnz, stream);
+        if (e != cudaSuccess) st = note_cuda_error(e, "cudaMallocAsync");
+        else st = spgemm_numeric(a, b, c, stream_v);
+    }
+    if (st != NB200_OK) {
+        if (c->row_ptr) cudaFreeAsync(c->row_ptr, stream);
+        if (c->col) cudaFreeAsync(c->col, stream);
+        if (c->val) cudaFreeAsync(c->val, stream);
+        c->row_ptr = c->col = nullptr;
+        c->val = nullptr;
+    }
+    return st;
+}
+
+}  // extern "C"

@@ -18,7 +18,7 @@ import torch
 from .. import _capi
 from .._capi import Coo3Struct, CsrStruct, Csf3Struct, lib
 
-__all__ = ["CSR_gpu", "COO3_gpu", "CSF3_gpu", "gpu_csr_add_f32", "gpu_csr_mul_f32", "gpu_coo3d_add_f32",
+__all__ = ["CSR_gpu", "COO3_gpu", "CSF3_gpu", "gpu_csr_add_f32", "gpu_csr_add_3_f32", "gpu_csr_mul_f32", "gpu_spgemm_f32", "gpu_coo3d_add_f32",
            "gpu_csf_add_f32"]
 
 
@@ -116,6 +116,46 @@ def gpu_csr_mul_f32(a: CSR_gpu, b: CSR_gpu, num_blocks: int = 256, threads_per_b
     """Z = A .* B (sorted intersection per row)."""
     return _csr_binary(lib.nb200_csr_mul_f32_into, "gpu_csr_mul_f32", a, b,
                        min(a.values.numel(), b.values.numel()))
+
+
+def gpu_csr_add_3_f32(a: CSR_gpu, b: CSR_gpu, c: CSR_gpu, num_blocks: int = 256,
+                      threads_per_block: int = 256) -> CSR_gpu:
+    """Z = (A + B) + C, the reference's association."""
+    for t in (a, b, c):
+        if not isinstance(t, CSR_gpu):
+            raise TypeError("gpu_csr_add_3_f32: operands must be CSR_gpu")
+    dev = _same_device(a, b, c)
+    sa, sb, sc = a._struct(), b._struct(), c._struct()
+    capacity = sa.nnz + sb.nnz + sc.nnz
+    with torch.cuda.device(dev):
+        row_ptr = _csr_result(sa.rows, sa.cols, dev)
+        col = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+        val = torch.empty(max(capacity, 1), dtype=torch.float32, device=dev)
+        sz = CsrStruct(sa.rows, sa.cols, 0, row_ptr.data_ptr(), col.data_ptr(), val.data_ptr())
+        status = lib.nb200_csr_add_3_f32_into(C.byref(sa), C.byref(sb), C.byref(sc), C.byref(sz), capacity,
+                                              _stream_for(row_ptr))
+    _capi.check(status, "gpu_csr_add_3_f32")
+    n = int(sz.nnz)
+    return CSR_gpu(row_ptr, col[:n], val[:n], torch.tensor([sz.rows, sz.cols], dtype=torch.int32))
+
+
+def gpu_spgemm_f32(a: CSR_gpu, b: CSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSR_gpu:
+    """C = A @ B by expand-sort-compress; sorted columns per row, explicit zeros kept."""
+    if not isinstance(a, CSR_gpu) or not isinstance(b, CSR_gpu):
+        raise TypeError("gpu_spgemm_f32: operands must be CSR_gpu")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    with torch.cuda.device(dev):
+        row_ptr = torch.empty(sa.rows + 1, dtype=torch.int32, device=dev)
+        sc = CsrStruct(sa.rows, sb.cols, 0, row_ptr.data_ptr(), None, None)
+        stream = _stream_for(row_ptr)
+        _capi.check(lib.nb200_spgemm_f32_symbolic(C.byref(sa), C.byref(sb), C.byref(sc), None, stream), "gpu_spgemm_f32")
+        n = int(sc.nnz)
+        col = torch.empty(n, dtype=torch.int32, device=dev)
+        val = torch.empty(n, dtype=torch.float32, device=dev)
+        sc.col, sc.val = col.data_ptr() if n else None, val.data_ptr() if n else None
+        _capi.check(lib.nb200_spgemm_f32_numeric(C.byref(sa), C.byref(sb), C.byref(sc), stream), "gpu_spgemm_f32")
+    return CSR_gpu(row_ptr, col, val, torch.tensor([sc.rows, sc.cols], dtype=torch.int32))
 
 
 class COO3_gpu:

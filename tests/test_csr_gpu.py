@@ -26,6 +26,8 @@ def test_golden_add_mul(nacho, csr_golden, case):
     ga, gb = csr_to_gpu(a), csr_to_gpu(b)
     assert_same(csr_from_gpu(nacho.gpu_csr_add_f32(ga, gb)), golden_csr(csr_golden, case, "add"), f"{case} add")
     assert_same(csr_from_gpu(nacho.gpu_csr_mul_f32(ga, gb)), golden_csr(csr_golden, case, "mul"), f"{case} mul")
+    gc = csr_to_gpu(golden_csr(csr_golden, case, "c"))
+    assert_same(csr_from_gpu(nacho.gpu_csr_add_3_f32(ga, gb, gc)), golden_csr(csr_golden, case, "add3"), f"{case} add3")
     # the two launch-shape arguments of the reference signature are accepted
     z = nacho.gpu_csr_add_f32(ga, gb, num_blocks=64, threads_per_block=128)
     assert_same(csr_from_gpu(z), golden_csr(csr_golden, case, "add"), f"{case} add (grid args)")
@@ -46,6 +48,8 @@ def test_seeded_vs_oracle(nacho, oracle, rows, cols, density, seed):
     ga, gb = synth_to_gpu(ta), synth_to_gpu(tb)
     assert_same(csr_from_gpu(nacho.gpu_csr_add_f32(ga, gb)), oracle.csr_add(a, b, 8), "add")
     assert_same(csr_from_gpu(nacho.gpu_csr_mul_f32(ga, gb)), oracle.csr_mul(a, b, 8), "mul")
+    tc = synth.random_csr(rows, cols, density, seed + 900)
+    assert_same(csr_from_gpu(nacho.gpu_csr_add_3_f32(ga, gb, synth_to_gpu(tc))), oracle.csr_add_3(a, b, synth_csr(tc), 8), "add3")
 
 
 def test_config1_vs_oracle(nacho, oracle):
@@ -69,6 +73,9 @@ def test_config3_small_vs_oracle(nacho, oracle, sigma):
     tb = synth.c3_csr(1, sigma, rows=1 << 14, cols=1 << 20, nnz=1 << 20)
     assert_same(csr_from_gpu(nacho.gpu_csr_add_f32(synth_to_gpu(ta), synth_to_gpu(tb))),
                 oracle.csr_add(synth_csr(ta), synth_csr(tb), 8), f"config 3 sigma={sigma}")
+    tc = synth.c3_csr(2, sigma, rows=1 << 14, cols=1 << 20, nnz=1 << 20)
+    assert_same(csr_from_gpu(nacho.gpu_csr_add_3_f32(synth_to_gpu(ta), synth_to_gpu(tb), synth_to_gpu(tc))),
+                oracle.csr_add_3(synth_csr(ta), synth_csr(tb), synth_csr(tc), 8), f"config 3 add3 sigma={sigma}")
 
 
 def test_long_runs_of_empty_rows(nacho, oracle):

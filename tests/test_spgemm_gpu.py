@@ -1,0 +1,143 @@
+"""GPU suite: expand-sort-compress SpGEMM through the C ABI against the C oracle (the
+reference has no CPU SpGEMM; the oracle restates its GPU algorithm and is itself pinned
+against a float64 product in the CPU suite). Structure must match exactly. Values: rows of
+at most 2048 products sum in the oracle's order and must match bit-for-bit; longer rows are
+held to |x - x64| <= 1e-5 * sum|a*b| (relative 1e-5 per entry wherever there is no
+cancellation), the tolerance of the task statement."""
+import numpy as np
+import pytest
+
+from helpers import csr_from_gpu, csr_to_gpu, synth_csr, synth_to_gpu
+from oracle.cpu_oracle import CSR
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def nacho():
+    import torch
+    assert torch.cuda.is_available(), "GPU suite needs a CUDA device"
+    from nacho_b200 import nacho as mod
+    return mod
+
+
+def check(nacho, oracle, a: CSR, b: CSR, ga=None, gb=None, exact_rows_only=False):
+    want, v64, abs64, products = oracle.spgemm(a, b, 8, extras=True)
+    got = csr_from_gpu(nacho.gpu_spgemm_f32(ga or csr_to_gpu(a), gb or csr_to_gpu(b)))
+    assert got.rows == a.rows and got.cols == b.cols
+    assert np.array_equal(got.row_ptr, want.row_ptr), "row offsets differ"
+    assert np.array_equal(got.col, want.col), "columns differ"
+    # per-row product counts decide which path a row took
+    b_len = np.diff(b.row_ptr)
+    per_entry = b_len[a.col] if len(a.col) else np.zeros(0, np.int64)
+    row_products = np.add.reduceat(np.append(per_entry, 0), a.row_ptr[:-1].clip(max=len(per_entry)))
+    row_products[np.diff(a.row_ptr) == 0] = 0
+    short = np.repeat(row_products <= 2048, np.diff(want.row_ptr))
+    same = got.val.view(np.uint32) == want.val.view(np.uint32)
+    assert same[short].all(), "a row of <= 2048 products differs from the fixed-order float32 sum"
+    assert np.all(np.abs(got.val.astype(np.float64) - v64) <= REL_TOL * abs64 + 1e-30)
+    return got, products
+
+
+def test_smoke_shape(nacho, oracle):
+    from nacho_b200 import synth
+    a = synth_csr(synth.random_csr(200, 180, 0.05, 7))
+    b = synth_csr(synth.random_csr(180, 150, 0.05, 8))
+    check(nacho, oracle, a, b)
+
+
+def test_empty_and_degenerate(nacho, oracle):
+    from nacho_b200 import synth
+    a = synth_csr(synth.random_csr(64, 50, 0.0, 1))
+    b = synth_csr(synth.random_csr(50, 70, 0.2, 2))
+    got, _ = check(nacho, oracle, a, b)
+    assert len(got.col) == 0
+    a = synth_csr(synth.random_csr(64, 50, 0.2, 3))
+    check(nacho, oracle, a, synth_csr(synth.random_csr(50, 70, 0.0, 4)))   # B empty: no products at all
+    check(nacho, oracle, synth_csr(synth.random_csr(1, 300, 0.5, 5)), synth_csr(synth.random_csr(300, 1, 0.5, 6)))
+
+
+def test_exact_cancellation_is_kept(nacho, oracle):
+    """C = [1, 1] @ [[1], [-1]] stores an explicit 0.0, as the reference's compress does."""
+    a = CSR(1, 2, np.array([0, 2], np.int32), np.array([0, 1], np.int32), np.array([1, 1], np.float32))
+    b = CSR(2, 1, np.array([0, 1, 2], np.int32), np.array([0, 0], np.int32), np.array([1, -1], np.float32))
+    got, _ = check(nacho, oracle, a, b)
+    assert got.row_ptr.tolist() == [0, 1] and got.val.tolist() == [0.0]
+
+
+def test_medium_and_long_rows(nacho, oracle):
+    """Rows in every bin: <= 32, <= 2048 and > 2048 products, next to empty rows."""
+    rng = np.random.default_rng(3)
+    rows, inner, cols = 300, 4000, 6000
+    lens = rng.integers(0, 6, rows)
+    lens[10] = 200      # medium: 200 entries x ~8 = 1600 products
+    lens[20] = 900      # long
+    lens[21] = 3000     # long, most of the inner dimension
+    lens[50:60] = 0
+    rp = np.zeros(rows + 1, np.int32)
+    rp[1:] = np.cumsum(lens)
+    col = np.concatenate([np.sort(rng.choice(inner, int(n), replace=False)) for n in lens]).astype(np.int32)
+    a = CSR(rows, inner, rp, col, rng.uniform(-1, 1, len(col)).astype(np.float32))
+    from nacho_b200 import synth
+    b = synth_csr(synth.random_csr(inner, cols, 0.002, 9))
+    check(nacho, oracle, a, b)
+
+
+def test_laplacian_squared_reduced(nacho, oracle):
+    """Configuration 4b on a 96 x 96 grid: 13-point stencil, at most 13 entries per row."""
+    from nacho_b200 import synth
+    t = synth.laplacian_csr(96)
+    a = synth_csr(t)
+    got, products = check(nacho, oracle, a, a, synth_to_gpu(t), synth_to_gpu(t))
+    assert np.diff(got.row_ptr).max() == 13
+    assert products == int((np.diff(a.row_ptr)[a.col]).sum())
+
+
+def test_rmat_reduced(nacho, oracle):
+    """Configuration 4a at scale 12 (4096 rows, B = A^T): skewed rows, some in the long bin."""
+    from nacho_b200 import synth
+    ta = synth.rmat_csr(scale=12, seed=4012)
+    tb = synth.transpose_csr(ta)
+    check(nacho, oracle, synth_csr(ta), synth_csr(tb), synth_to_gpu(ta), synth_to_gpu(tb))
+
+
+def test_full_size_laplacian_properties(nacho):
+    """Configuration 4b at full size (512 x 512 grid): known structure of the squared stencil."""
+    import torch
+    from nacho_b200 import synth
+    t = synth.laplacian_csr(512, device="cuda")
+    a = synth_to_gpu(t)
+    c = nacho.gpu_spgemm_f32(a, a)
+    torch.cuda.synchronize()
+    assert c.values.numel() == 3_397_636  # 13-point stencil on a 512 x 512 grid
+    rp = c.dim_j_offsets.to(torch.int64)
+    rows = torch.repeat_interleave(torch.arange(512 * 512, device="cuda"), rp[1:] - rp[:-1])
+    key = rows * (512 * 512) + c.dim_j_indices.to(torch.int64)
+    assert bool((key[1:] > key[:-1]).all())
+    # the Laplacian has zero row sums away from the boundary, so does its square; all sums are small integers
+    dense_sum = float(c.values.to(torch.float64).sum())
+    a_sum = torch.zeros(512 * 512, dtype=torch.float64, device="cuda").index_add_(
+        0, torch.repeat_interleave(torch.arange(512 * 512, device="cuda"), (a.dim_j_offsets[1:] - a.dim_j_offsets[:-1]).to(torch.int64)),
+        a.values.to(torch.float64))
+    # sum(C) = 1^T A A 1 = (A^T 1) . (A 1) = |A 1|^2 for symmetric A
+    assert abs(dense_sum - float((a_sum * a_sum).sum())) < 1e-6 * max(1.0, abs(dense_sum))
+    assert bool((c.values == c.values.round()).all())
+
+
+def test_symbolic_reports_products(nacho, oracle):
+    import ctypes as C
+    import torch
+    from nacho_b200 import synth
+    from nacho_b200._capi import CsrStruct, check as ck, lib
+    ta, tb = synth.random_csr(500, 400, 0.03, 21), synth.random_csr(400, 300, 0.03, 22)
+    want, _, _, products = oracle.spgemm(synth_csr(ta), synth_csr(tb), 4, extras=True)
+    ga, gb = synth_to_gpu(ta), synth_to_gpu(tb)
+    rp = torch.empty(501, dtype=torch.int32, device="cuda")
+    c = CsrStruct(0, 0, 0, rp.data_ptr(), None, None)
+    p = C.c_int64(0)
+    sa, sb = ga._struct(), gb._struct()
+    ck(lib.nb200_spgemm_f32_symbolic(C.byref(sa), C.byref(sb), C.byref(c), C.byref(p), None), "symbolic")
+    assert p.value == products and c.nnz == len(want.col)
+    assert np.array_equal(rp.cpu().numpy(), want.row_ptr)
