@@ -10,16 +10,17 @@ entries per operand, uniform rows). Rank 0 prints one JSON line:
   value      effective GB/s = algorithmic bytes (operands + result) / time, operands resident in
              HBM when the timed region starts, whole job over all ranks
   e2e        the same metric through the public operator with HOST operands: pinned host ->
-             device copies of the operands and a device -> host copy of the result are inside
-             the timed region
-  roofline   dominant kernel: algorithmic bytes per launch / its mean launch time (CUDA events
-             on the launching stream), against the measured HBM copy peak
-  cpu_baseline  the reference's own CPU kernels (or the C oracle port when they are not built)
-             timed on the host cores on a bounded row block of the same workload
+             device copies of the operands and a device -> pinned host copy of the result are
+             inside the timed region
+  roofline   dominant kernel: algorithmic bytes per step / the time the step spends in that
+             kernel (CUDA events on the launching stream), against the measured HBM copy peak
+  cpu_baseline  the reference's own CPU kernels (the C oracle port where the reference has
+             none, i.e. SpGEMM) timed on the host cores on a bounded sample of the workload
 
 With N > 1 (launched by torch.distributed.run) every rank holds its own row block of the same
 size (weak scaling); the only exchange is the all-gather of (rows, nnz) per block that stitches
-the global row offsets, and it is inside the timed region.
+the global row offsets, and it is inside the timed region. SpGEMM's B is replicated by a
+broadcast before the timed region.
 """
 from __future__ import annotations
 
@@ -49,44 +50,90 @@ def measured_peaks():
 
 # ------------------------------------------------------------------------------ workloads ----
 
+# name -> operator, tensor format, generator parameters
 WORKLOADS = {
-    # name: (operator, generator description)
-    "c3_csr_add_sigma0": dict(op="csr_add", sigma=0),
-    "c3_csr_add_sigma1": dict(op="csr_add", sigma=1),
-    "c3_csr_add_sigma2": dict(op="csr_add", sigma=2),
-    "c3_csr_add_sigma3": dict(op="csr_add", sigma=3),
-    "c2_csr_mul": dict(op="csr_mul"),
-    "c1_csr_add": dict(op="csr_add"),
+    "c1_csr_add": dict(op="csr_add", fmt="csr"),
+    "c2_csr_mul": dict(op="csr_mul", fmt="csr"),
+    "c3_csr_add_sigma0": dict(op="csr_add", fmt="csr", sigma=0),
+    "c3_csr_add_sigma1": dict(op="csr_add", fmt="csr", sigma=1),
+    "c3_csr_add_sigma2": dict(op="csr_add", fmt="csr", sigma=2),
+    "c3_csr_add_sigma3": dict(op="csr_add", fmt="csr", sigma=3),
+    "c3_csr_add_3_sigma0": dict(op="csr_add_3", fmt="csr", sigma=0),
+    "c3_csr_add_3_sigma2": dict(op="csr_add_3", fmt="csr", sigma=2),
+    "c4a_spgemm_rmat": dict(op="spgemm", fmt="csr"),
+    "c4b_spgemm_laplacian": dict(op="spgemm", fmt="csr"),
+    "c5_coo3d_add": dict(op="coo3d_add", fmt="coo3"),
+    "c5_csf_add": dict(op="csf_add", fmt="csf3"),
 }
 
 
-def make_operands(name: str, rank: int, device, rows_scale: float = 1.0):
-    """Synthetic operands (tuples from nacho_b200.synth) of workload `name` for one rank."""
+def make_operands(name: str, rank: int, device, scale: float = 1.0, rmat_scale: int = 16):
+    """Synthetic operands (tuples from nacho_b200.synth) of workload `name` for one rank.
+    `scale` shrinks rows and entries together (CPU samples, profiling captures)."""
     from nacho_b200 import synth
-    seed_shift = 7919 * rank
-    if name.startswith("c3_csr_add"):
-        sigma = WORKLOADS[name]["sigma"]
-        rows = int((1 << 20) * rows_scale)
-        nnz = int((1 << 26) * rows_scale)
-        return [synth.c3_csr(k, sigma, rows=rows, cols=1 << 20, nnz=nnz, seed=3000 + seed_shift, device=device)
-                for k in range(2)]
+    shift = 7919 * rank
+    spec = WORKLOADS[name]
+    if name.startswith("c3_"):
+        rows, nnz = max(1, int((1 << 20) * scale)), max(1, int((1 << 26) * scale))
+        n_ops = 3 if spec["op"] == "csr_add_3" else 2
+        return [synth.c3_csr(k, spec["sigma"], rows=rows, cols=1 << 20, nnz=nnz, seed=3000 + shift, device=device)
+                for k in range(n_ops)]
     if name == "c2_csr_mul":
-        return list(synth.c2_pair(rows=int((1 << 20) * rows_scale), seed=2000 + seed_shift, device=device))
+        return list(synth.c2_pair(rows=max(1, int((1 << 20) * scale)), seed=2000 + shift, device=device))
     if name == "c1_csr_add":
-        return [synth.c1_csr(k, seed=1000 + seed_shift, device=device) for k in range(2)]
+        return [synth.c1_csr(k, seed=1000 + shift, device=device) for k in range(2)]
+    if name == "c4a_spgemm_rmat":
+        a = synth.rmat_csr(scale=rmat_scale, seed=4000 + shift, device=device)
+        return [a, synth.transpose_csr(a)]
+    if name == "c4b_spgemm_laplacian":
+        a = synth.laplacian_csr(max(8, int(512 * scale ** 0.5)), device=device)
+        return [a, a]
+    if name in ("c5_coo3d_add", "c5_csf_add"):
+        return list(synth.c5_pair(nnz=max(1000, int(100_000_000 * scale)), seed=5000 + shift, device=device))
     raise SystemExit(f"unknown workload {name}")
 
 
-def algorithmic_bytes(rows: int, nnz_in: int, nnz_out: int, n_ops: int) -> int:
-    """Operand + result bytes of a CSR element-wise operator: 4-byte row offsets of every
-    operand and of the result, 8 bytes (column + value) per stored entry read or written."""
-    return 4 * (rows + 1) * (n_ops + 1) + 8 * nnz_in + 8 * nnz_out
+def csf3_arrays(t, device):
+    """COO3 synth tuple -> the six CSF3 level arrays as torch tensors on `device` (computed
+    with torch so that 100 M entries take seconds)."""
+    import torch
+    dims, i, j, k, v = t
+    n = i.numel()
+    new_ij = torch.ones(n, dtype=torch.bool, device=i.device)
+    if n > 1:
+        new_ij[1:] = (i[1:] != i[:-1]) | (j[1:] != j[:-1])
+    ij = torch.nonzero(new_ij).squeeze(1)
+    ii = i[ij]
+    new_i = torch.ones(ij.numel(), dtype=torch.bool, device=i.device)
+    if ij.numel() > 1:
+        new_i[1:] = ii[1:] != ii[:-1]
+    ist = torch.nonzero(new_i).squeeze(1)
+    cat = lambda a, x: torch.cat([a, torch.tensor([x], device=a.device, dtype=a.dtype)])
+    out = (ii[ist], cat(ist, ij.numel()), j[ij], cat(ij, n), k, v)
+    return dims, tuple(x.to(device=device, dtype=torch.float32 if x.dtype.is_floating_point else torch.int32).contiguous()
+                       for x in out)
+
+
+def bytes_csr(rows: int, nnz: int) -> int:
+    return 4 * (rows + 1) + 8 * nnz
+
+
+def algorithmic_bytes(spec, operands_meta, result_meta) -> int:
+    """Operand + result bytes of one step. CSR: 4-byte row offsets of every operand and of the
+    result plus 8 bytes (column + value) per stored entry; COO3: 16 bytes per entry; CSF3: the
+    level arrays as built."""
+    if spec["fmt"] == "csr":
+        return sum(bytes_csr(r, n) for r, n in operands_meta) + bytes_csr(*result_meta)
+    if spec["fmt"] == "coo3":
+        return 16 * (sum(operands_meta) + result_meta)
+    return sum(operands_meta) + result_meta  # csf3: metas are byte counts already
 
 
 # --------------------------------------------------------------------------------- clocks ----
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi; `window` keeps the samples that
+    arrived between two wall-clock instants (the timed region)."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -95,36 +142,37 @@ class ClockSampler:
         self.samples = []
         self.proc = None
         self.gpu_index = gpu_index
-        self.thread = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
+        threading.Thread(target=self._read, daemon=True).start()
 
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
 
-    def stop(self):
+    def stop(self, t0: float, t1: float):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        inside = [p for t, p in self.samples if t0 <= t <= t1 + 0.03]
+        used = inside or [p for _, p in self.samples[-3:]]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for p in self.samples:
+        for p in used:
             try:
                 sm.append(float(p[0]))
                 mx.append(float(p[1]))
@@ -134,24 +182,48 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_in_timed_region": len(inside)}
 
 
 # --------------------------------------------------------------------------- CPU baseline ----
 
-def cpu_baseline(name: str, operands_np, steps: int = 3, warmup: int = 1):
-    """Times the reference's emitted CPU kernels (all host threads) -- or, when they are not
-    built on this machine, the C oracle port -- on `operands_np` (oracle-style CSR tuples)."""
+def to_oracle(spec, t):
+    """Synth tuple (torch) -> oracle-style numpy tuple of the workload's format."""
+    import numpy as np
+    from nacho_b200 import synth
+    from oracle.cpu_oracle import COO3, CSF3, CSR
+    if spec["fmt"] == "csr":
+        return CSR(*synth.to_numpy(t))
+    dims, i, j, k, v = synth.to_numpy(t)
+    if spec["fmt"] == "coo3":
+        return COO3(dims, i, j, k, v)
+    from nacho_b200.nacho.convert import csf3_levels
+    lv = [np.asarray(x, np.int32) for x in csf3_levels(np.stack([i, j, k], 1))]
+    return CSF3(dims, *lv, v)
+
+
+def cpu_baseline(name: str, operands, steps: int = 3, warmup: int = 1):
+    """Times the reference's emitted CPU kernels with all host threads (kind "reference"), or
+    the C oracle port where the reference has no CPU kernel (SpGEMM) or is not built here
+    (kind "port"), on `operands` (oracle-style tuples). Returns the result dict and metas."""
     from oracle.cpu_oracle import Oracle, Reference, default_threads
-    op = WORKLOADS[name]["op"]
-    if Reference.available():
-        impl, kind = Reference(), "reference"
+    spec = WORKLOADS[name]
+    op = spec["op"]
+    cores = default_threads()
+    use_ref = Reference.available() and op != "spgemm"
+    if use_ref:
+        impl = Reference()
         cores = impl.threads()
-        run = {"csr_add": lambda: impl.csr_add(*operands_np), "csr_mul": lambda: impl.csr_mul(*operands_np)}[op]
+        run = {"csr_add": lambda: impl.csr_add(*operands), "csr_mul": lambda: impl.csr_mul(*operands),
+               "csr_add_3": lambda: impl.csr_add_3(*operands), "coo3d_add": lambda: impl.coo3_add(*operands),
+               "csf_add": lambda: impl.csf3_add(*operands)}[op]
     else:
-        impl, kind = Oracle(), "port"
-        cores = default_threads()
-        run = {"csr_add": lambda: impl.csr_add(*operands_np, cores), "csr_mul": lambda: impl.csr_mul(*operands_np, cores)}[op]
+        impl = Oracle()
+        run = {"csr_add": lambda: impl.csr_add(*operands, cores), "csr_mul": lambda: impl.csr_mul(*operands, cores),
+               "csr_add_3": lambda: impl.csr_add_3(*operands, cores), "coo3d_add": lambda: impl.coo3_add(*operands, cores),
+               "csf_add": lambda: impl.csf3_add(*operands), "spgemm": lambda: impl.spgemm(*operands, cores)}[op]
+        if op == "csf_add":
+            cores = 1
     out = None
     for _ in range(warmup):
         out = run()
@@ -160,41 +232,44 @@ def cpu_baseline(name: str, operands_np, steps: int = 3, warmup: int = 1):
         t0 = time.perf_counter()
         out = run()
         times.append(time.perf_counter() - t0)
-    a = operands_np[0]
-    nnz_in = sum(len(m.col) for m in operands_np)
-    nbytes = algorithmic_bytes(a.rows, nnz_in, len(out.col), len(operands_np))
+    if spec["fmt"] == "csr":
+        metas = [(m.rows, len(m.col)) for m in operands]
+        nbytes = algorithmic_bytes(spec, metas, (out.rows, len(out.col)))
+        nnz_in = sum(n for _, n in metas)
+    elif spec["fmt"] == "coo3":
+        nbytes = algorithmic_bytes(spec, [len(m.val) for m in operands], len(out.val))
+        nnz_in = sum(len(m.val) for m in operands)
+    else:
+        size = lambda m: sum(getattr(m, f).nbytes for f in ("i_idx", "j_ptr", "j_idx", "k_ptr", "k_idx", "val"))
+        nbytes = algorithmic_bytes(spec, [size(m) for m in operands], size(out))
+        nnz_in = sum(len(m.val) for m in operands)
     t = statistics.mean(times)
-    return {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
-            "nnz_per_s": nnz_in / t, "ms": t * 1e3}, nbytes
+    return {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "nnz_per_s": nnz_in / t, "ms": t * 1e3}
 
 
-def row_block(t, rows_keep: int):
-    """First `rows_keep` rows of a synth CSR tuple, as an oracle-style numpy CSR."""
-    import numpy as np
-    from oracle.cpu_oracle import CSR
-    rows, cols, rp, col, val = t
-    rows_keep = min(rows_keep, rows)
-    rp_np = rp[: rows_keep + 1].cpu().numpy()
-    n = int(rp_np[-1])
-    return CSR(rows_keep, cols, np.ascontiguousarray(rp_np), col[:n].cpu().numpy(), val[:n].cpu().numpy())
+def cpu_sample_scale(name: str, requested: float) -> float:
+    """Fraction of the workload used for CPU timing: about 10-30 s of CPU work in total."""
+    if name == "c1_csr_add" or name.startswith("c4"):
+        return 1.0
+    return requested
 
-
-# ----------------------------------------------------------------------------------- main ----
 
 def run_reference(args):
     """`--impl reference`: the reference's CPU implementation of the path on the host cores,
-    each step one bounded row block of the workload. Rank 0 only."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    each step one bounded sample of the workload. Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     import torch
     dev = "cuda" if torch.cuda.is_available() else "cpu"
-    ops = make_operands(args.workload, 0, dev, rows_scale=args.cpu_rows_scale)
-    ops_np = [row_block(t, ops[0][0]) for t in ops]
-    base, nbytes = cpu_baseline(args.workload, ops_np, steps=args.steps, warmup=args.warmup)
-    sample = f"first {ops_np[0].rows} rows of {args.workload} ({sum(len(m.col) for m in ops_np)} operand entries)"
+    spec = WORKLOADS[args.workload]
+    scale = cpu_sample_scale(args.workload, args.cpu_scale)
+    ops = make_operands(args.workload, 0, dev, scale=scale, rmat_scale=min(args.rmat_scale, 14))
+    ops_np = [to_oracle(spec, t) for t in ops]
+    base = cpu_baseline(args.workload, ops_np, steps=args.steps, warmup=args.warmup)
+    sample = f"{args.workload} at scale {scale:g} of its rows/entries"
     line = {
-        "impl": "reference", "metric": f"{WORKLOADS[args.workload]['op']} effective HBM GB/s (operand + result bytes)",
+        "impl": "reference", "metric": f"{spec['op']} effective HBM GB/s (operand + result bytes)",
         "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": base["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": {"workload": args.workload, "sample": sample},
@@ -206,6 +281,45 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------------- main ----
+
+def build_device_operands(spec, ops, dev):
+    """Synth tuples -> the mirror's tensor objects on `dev`, plus metas for the byte count."""
+    import torch
+    from nacho_b200 import nacho
+    if spec["fmt"] == "csr":
+        tensors = [nacho.CSR_gpu(rp.to(dev), col.to(dev), val.to(dev), torch.tensor([rows, cols], dtype=torch.int32))
+                   for rows, cols, rp, col, val in ops]
+        metas = [(t[0], t[3].numel()) for t in ops]
+    elif spec["fmt"] == "coo3":
+        tensors = [nacho.COO3_gpu(i.to(dev), j.to(dev), k.to(dev), v.to(dev), torch.tensor(list(dims), dtype=torch.int32))
+                   for dims, i, j, k, v in ops]
+        metas = [t[4].numel() for t in ops]
+    else:
+        tensors, metas = [], []
+        for t in ops:
+            dims, arrays = csf3_arrays(t, dev)
+            tensors.append(nacho.CSF3_gpu(*arrays, torch.tensor(list(dims), dtype=torch.int32)))
+            metas.append(sum(a.numel() * 4 for a in arrays))
+    return tensors, metas
+
+
+def buffers_of(t):
+    """The device arrays of a mirror tensor, in constructor order."""
+    names = {"CSR_gpu": ("dim_j_offsets", "dim_j_indices", "values"),
+             "COO3_gpu": ("dim_i_indices", "dim_j_indices", "dim_k_indices", "values"),
+             "CSF3_gpu": ("dim_i_indices", "dim_j_offsets", "dim_j_indices", "dim_k_offsets", "dim_k_indices", "values")}
+    return [getattr(t, n) for n in names[type(t).__name__]]
+
+
+def result_meta(spec, z):
+    if spec["fmt"] == "csr":
+        return (int(z.shape[0]), z.values.numel())
+    if spec["fmt"] == "coo3":
+        return z.values.numel()
+    return sum(b.numel() * 4 for b in buffers_of(z))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -213,25 +327,26 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c3_csr_add_sigma0", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-rows-scale", type=float, default=0.125,
-                    help="fraction of the workload's rows in the CPU-baseline sample")
+    ap.add_argument("--cpu-scale", type=float, default=0.125,
+                    help="fraction of the workload's rows/entries in the CPU-baseline sample")
     ap.add_argument("--rows-scale", type=float, default=1.0,
-                    help="shrink the workload's rows and entries by this factor (profiling captures only; "
-                         "a line printed with a factor other than 1 is not a benchmark result)")
+                    help="shrink the workload by this factor (profiling captures only; a line printed with a "
+                         "factor other than 1 is not a benchmark result)")
+    ap.add_argument("--rmat-scale", type=int, default=16,
+                    help="log2 of the rows of the R-MAT SpGEMM operand (configuration 4a names 18)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "ours":
-        args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    args.warmup = max(args.warmup, 3)
 
     import torch
     import torch.distributed as dist
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
-    from nacho_b200 import _capi, nacho
+    from nacho_b200 import _capi, nacho, shard
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -242,21 +357,22 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     spec = WORKLOADS[args.workload]
-    op_fn = {"csr_add": nacho.gpu_csr_add_f32, "csr_mul": nacho.gpu_csr_mul_f32}[spec["op"]]
-    ops = make_operands(args.workload, rank, dev, rows_scale=args.rows_scale)
-    tensors = [nacho.CSR_gpu(rp, col, val, torch.tensor([rows, cols], dtype=torch.int32))
-               for rows, cols, rp, col, val in ops]
-    rows = ops[0][0]
+    op_fn = getattr(nacho, f"gpu_{spec['op']}_f32")
+    ops = make_operands(args.workload, rank, dev, scale=args.rows_scale, rmat_scale=args.rmat_scale)
+    if spec["op"] == "spgemm" and world > 1:
+        # B is replicated: rank 0's B goes to every rank (A stays a per-rank row block)
+        rows_b, cols_b, rp_b, col_b, val_b = ops[1]
+        rp_b, col_b, val_b, shape_b = shard.broadcast_csr(rp_b if rank == 0 else None, col_b if rank == 0 else None,
+                                                          val_b if rank == 0 else None, (rows_b, cols_b), 0)
+        ops[1] = (shape_b[0], shape_b[1], rp_b, col_b, val_b)
+    tensors, metas = build_device_operands(spec, ops, dev)
     nnz_in = sum(t.values.numel() for t in tensors)
-    stitch_in = torch.zeros(2, dtype=torch.int64, device=dev)
-    stitch_out = torch.zeros(2 * world, dtype=torch.int64, device=dev)
+    rows_local = int(tensors[0].shape[0])
 
     def step():
         z = op_fn(*tensors)
         if world > 1:  # stitch: every block's (rows, nnz) -> global row-offset bases
-            stitch_in[0] = rows
-            stitch_in[1] = z.values.numel()
-            dist.all_gather_into_tensor(stitch_out, stitch_in)
+            shard.stitch(rows_local, z.values.numel(), device=dev)
         return z
 
     def barrier():
@@ -267,30 +383,35 @@ def main():
     z = None
     for _ in range(args.warmup):
         z = step()
+    zmeta = result_meta(spec, z)
+    nbytes = algorithmic_bytes(spec, metas, zmeta)
     nnz_out = z.values.numel()
-    nbytes = algorithmic_bytes(rows, nnz_in, nnz_out, len(tensors))
 
+    # keep the timed region long enough for the clock sampler (about half a second at least)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.15)
     stream = torch.cuda.current_stream()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     launches0 = _capi.launch_count()
+    t_wall0 = time.perf_counter()
     start.record(stream)
     for _ in range(args.steps):
         z = step()
     stop.record(stream)
     barrier()
+    t_wall1 = time.perf_counter()
     launches = _capi.launch_count() - launches0
     elapsed_ms = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
 
-    # ---- per-kernel timing of the dominant kernel, same workload, events on the launching stream
-    fill_name = spec["op"] + "_fused"
+    # ---- per-kernel timing, same workload, events on the launching stream
+    prof_steps = max(3, min(args.steps, 10))
     _capi.profile_reset()
     _capi.profile_enable(True)
-    for _ in range(max(3, min(args.steps, 10))):
+    for _ in range(prof_steps):
         step()
     torch.cuda.synchronize()
     _capi.profile_enable(False)
@@ -298,19 +419,22 @@ def main():
     for kname in _capi.profile_names():
         n, ms = _capi.profile_read(kname)
         if n:
-            kernels[kname] = {"launches": n, "avg_ms": ms / n}
+            kernels[kname] = {"launches_per_step": n / prof_steps, "avg_ms": ms / n, "ms_per_step": ms / prof_steps}
 
-    # ---- end to end with host operands
+    # ---- end to end with host operands (pinned), result back into pinned host buffers
     e2e = None
     if not args.no_e2e:
-        host = [[x.cpu().pin_memory() for x in (t.dim_j_offsets, t.dim_j_indices, t.values)] for t in tensors]
+        host_in = [[b.cpu().pin_memory() for b in buffers_of(t)] for t in tensors]
         shapes = [t.shape for t in tensors]
+        cls = type(tensors[0])
+        host_out = [torch.empty(b.numel(), dtype=b.dtype).pin_memory() for b in buffers_of(z)]
 
         def e2e_step():
-            dev_ops = [nacho.CSR_gpu(*[x.to(dev, non_blocking=True) for x in h], s) for h, s in zip(host, shapes)]
+            dev_ops = [cls(*[b.to(dev, non_blocking=True) for b in h], s) for h, s in zip(host_in, shapes)]
             zz = op_fn(*dev_ops)
-            out = [x.cpu() for x in (zz.dim_j_offsets, zz.dim_j_indices, zz.values)]
-            return out
+            for dst, src in zip(host_out, buffers_of(zz)):
+                dst[: src.numel()].copy_(src, non_blocking=True)
+            torch.cuda.synchronize()
 
         for _ in range(2):
             e2e_step()
@@ -320,53 +444,63 @@ def main():
         for _ in range(k):
             e2e_step()
         barrier()
-        e2e_s = (time.perf_counter() - t0) / k
-        h2d = sum(x.numel() * x.element_size() for h in host for x in h)
-        d2h = 4 * (rows + 1) + 8 * nnz_out
-        e2e = {"seconds": e2e_s, "h2d": h2d, "d2h": d2h}
+        e2e = {"seconds": (time.perf_counter() - t0) / k,
+               "h2d": sum(b.numel() * b.element_size() for h in host_in for b in h),
+               "d2h": sum(b.numel() * b.element_size() for b in buffers_of(z))}
 
     # ---- reduce over ranks: max time, summed bytes
     if world > 1:
         t = torch.tensor([elapsed_ms, e2e["seconds"] if e2e else 0.0], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_s_max = float(t[0]), float(t[1])
+        elapsed_ms, e2e_s = float(t[0]), float(t[1])
         b = torch.tensor([nbytes, nnz_in, launches], dtype=torch.int64, device=dev)
         dist.all_reduce(b, op=dist.ReduceOp.SUM)
         total_bytes, total_nnz_in, launches = int(b[0]), int(b[1]), int(b[2])
     else:
-        e2e_s_max = e2e["seconds"] if e2e else 0.0
+        e2e_s = e2e["seconds"] if e2e else 0.0
         total_bytes, total_nnz_in = nbytes, nnz_in
 
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
-        value = total_bytes / (ms_per_step * 1e-3) / 1e9
         peak, peak_kind = measured_peaks()
-        roof = None
-        if fill_name in kernels:
-            achieved = nbytes / (kernels[fill_name]["avg_ms"] * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": fill_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
-                    "avg_launch_ms": kernels[fill_name]["avg_ms"]}
+        roof, extra = None, {}
+        if kernels:
+            top = max(kernels, key=lambda k: kernels[k]["ms_per_step"])
+            roof_bytes = nbytes
+            if spec["op"] == "spgemm":
+                # expand-sort-compress model: A once, 8 bytes of B per product, C once
+                b_len = (ops[1][2][1:] - ops[1][2][:-1]).to(torch.int64)
+                products = int(b_len[ops[0][3].to(torch.int64)].sum())
+                roof_bytes = bytes_csr(*metas[0]) + 8 * products + bytes_csr(*zmeta)
+                extra = {"products": products, "esc_model_bytes": roof_bytes}
+            achieved = roof_bytes / (kernels[top]["ms_per_step"] * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
+                    "kernel_ms_per_step": kernels[top]["ms_per_step"], "frac_of_nominal_8TBs": achieved / 8000.0}
         base = None
         if not args.no_cpu_baseline:
-            keep = max(1, int(rows * args.cpu_rows_scale))
-            ops_np = [row_block(t, keep) for t in ops]
-            base, _ = cpu_baseline(args.workload, ops_np)
-            base["sample"] = (f"first {keep} rows of {args.workload} "
-                              f"({sum(len(m.col) for m in ops_np)} operand entries), mean of 3 runs")
+            scale = cpu_sample_scale(args.workload, args.cpu_scale) * args.rows_scale
+            cpu_rmat = min(args.rmat_scale, 14)  # the CPU port sorts every product; keep its sample bounded
+            same = scale == args.rows_scale and (args.workload != "c4a_spgemm_rmat" or cpu_rmat == args.rmat_scale)
+            cpu_ops = ops if same else make_operands(args.workload, 0, dev, scale=scale, rmat_scale=cpu_rmat)
+            base = cpu_baseline(args.workload, [to_oracle(spec, t) for t in cpu_ops])
+            base["sample"] = (f"{args.workload} at scale {scale:g} of its rows/entries"
+                              + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" else "")
+                              + ", mean of 3 runs")
         line = {
             "metric": f"{spec['op']} effective HBM GB/s (operand + result bytes)",
-            "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "rows_scale": args.rows_scale, "rows_per_gpu": rows, "operand_nnz_per_gpu": nnz_in,
-                       "result_nnz_per_gpu": nnz_out, "algorithmic_bytes_per_gpu": nbytes,
-                       "l2_policy": "inputs_larger_than_L2" if nbytes > 2 * 126e6 else "inputs fit L2 (latency-bound case)",
-                       "parallelism": f"row blocks x{world}, all-gather of (rows, nnz) per step"},
+            "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict({"workload": args.workload, "rows_scale": args.rows_scale, "rows_per_gpu": rows_local,
+                            "operand_nnz_per_gpu": nnz_in, "result_nnz_per_gpu": nnz_out,
+                            "algorithmic_bytes_per_gpu": nbytes,
+                            "l2_policy": "inputs_larger_than_L2" if nbytes > 2 * 126e6 else "inputs fit L2 (latency-bound case)",
+                            "parallelism": f"row blocks x{world}, all-gather of (rows, nnz) per step"}, **extra),
             "nnz_per_s": total_nnz_in / (ms_per_step * 1e-3),
             "roofline": roof, "kernels": kernels, "cpu_baseline": base,
-            "e2e": ({"value": total_bytes / e2e_s_max / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"],
-                     "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e_s_max * 1e3} if e2e else None),
+            "e2e": ({"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"],
+                     "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e_s * 1e3} if e2e else None),
             "gpu_launches": launches, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -1,0 +1,110 @@
+"""CPU suite: the multi-GPU host logic -- nnz-balanced row cuts, product-balanced cuts,
+merge-path coordinate cuts and the all-gather stitch -- with gloo ranks on CPU. Each rank
+computes its block with the C oracle (the CUDA operator takes that place on GPUs); the
+stitched blocks must equal the unsharded result bit-for-bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import assert_same, synth_csr
+from nacho_b200 import shard, synth
+from oracle.cpu_oracle import COO3, CSR, Oracle
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_row_block_cuts_balance_and_edges():
+    a = synth_csr(synth.c3_csr(0, 3, rows=4096, cols=1 << 16, nnz=1 << 16))
+    b = synth_csr(synth.c3_csr(1, 3, rows=4096, cols=1 << 16, nnz=1 << 16))
+    for parts in (1, 2, 4, 8):
+        cuts = shard.row_block_cuts([a.row_ptr, b.row_ptr], parts)
+        assert cuts[0] == 0 and cuts[-1] == a.rows and len(cuts) == parts + 1
+        assert all(x <= y for x, y in zip(cuts, cuts[1:]))
+        work = (a.row_ptr.astype(np.int64) + b.row_ptr)[cuts]
+        per = np.diff(work)
+        biggest_row = int((np.diff(a.row_ptr) + np.diff(b.row_ptr)).max())
+        assert per.max() <= work[-1] / parts + biggest_row + 1  # off by at most one row's work
+    empty = np.zeros(11, np.int32)
+    assert shard.row_block_cuts([empty, empty], 4) == [0, 0, 0, 0, 10]
+
+
+def test_product_balanced_cuts():
+    a = synth_csr(synth.rmat_csr(scale=10, seed=4010))
+    b = synth_csr(synth.transpose_csr(synth.rmat_csr(scale=10, seed=4010)))
+    cuts = shard.product_balanced_cuts(a.row_ptr, a.col, b.row_ptr, 4)
+    per_entry = np.diff(b.row_ptr)[a.col]
+    prefix = np.concatenate([[0], np.cumsum(per_entry)])[a.row_ptr]
+    per = np.diff(prefix[cuts])
+    row_max = np.diff(prefix).max()
+    assert per.sum() == prefix[-1] and per.max() <= prefix[-1] / 4 + row_max + 1
+
+
+def test_coo3_cuts_never_split_a_pair():
+    rng = np.random.default_rng(1)
+    a = np.unique(rng.integers(0, 5000, 3000))
+    b = np.unique(np.concatenate([a[rng.random(len(a)) < 0.5], rng.integers(0, 5000, 2000)]))
+    for parts in (2, 3, 8):
+        cuts = shard.coo3_cuts(a, b, parts)
+        assert cuts[0] == (0, 0) and cuts[-1] == (len(a), len(b))
+        merged = []
+        for (x0, y0), (x1, y1) in zip(cuts, cuts[1:]):
+            assert x0 <= x1 and y0 <= y1
+            part = np.union1d(a[x0:x1], b[y0:y1])
+            if merged and len(part):
+                assert merged[-1] < part[0]  # ranges are disjoint and ordered: no key on both sides
+            merged.extend(part.tolist())
+        assert np.array_equal(np.array(merged), np.union1d(a, b))
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        oracle = Oracle()
+        ta = synth.c3_csr(0, 2, rows=2048, cols=1 << 14, nnz=1 << 15)
+        tb = synth.c3_csr(1, 2, rows=2048, cols=1 << 14, nnz=1 << 15)
+        cuts = shard.row_block_cuts([ta[2], tb[2]], world)
+        r0, r1 = cuts[rank], cuts[rank + 1]
+        blocks = []
+        for t in (ta, tb):
+            rp, col, val = shard.csr_row_block(t[2], t[3], t[4], r0, r1)
+            blocks.append(CSR(r1 - r0, t[1], rp.numpy(), col.numpy(), val.numpy()))
+        z = oracle.csr_add(blocks[0], blocks[1], 2)
+        row_base, nnz_base, rows_all, nnz_all = shard.stitch(z.rows, len(z.col))
+        assert row_base == r0 and sum(rows_all) == 2048
+        np.savez(os.path.join(out_dir, f"block{rank}.npz"), rp=z.row_ptr, col=z.col, val=z.val,
+                 row_base=row_base, nnz_base=nnz_base)
+        # SpGEMM's replication step: rank 0 owns B, everyone ends up with it
+        if rank == 0:
+            rp_b, col_b, val_b, shape = shard.broadcast_csr(tb[2], tb[3], tb[4], (tb[0], tb[1]), 0)
+        else:
+            rp_b, col_b, val_b, shape = shard.broadcast_csr(None, None, None, None, 0)
+        assert shape == (tb[0], tb[1]) and torch.equal(col_b, tb[3]) and torch.equal(val_b, tb[4])
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_add_equals_unsharded(tmp_path, oracle, world):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    blocks, bases = [], []
+    for r in range(world):
+        f = np.load(tmp_path / f"block{r}.npz")
+        blocks.append((f["rp"], f["col"], f["val"]))
+        bases.append(int(f["nnz_base"]))
+    rp, col, val = shard.concat_csr_blocks(blocks)
+    a = synth_csr(synth.c3_csr(0, 2, rows=2048, cols=1 << 14, nnz=1 << 15))
+    b = synth_csr(synth.c3_csr(1, 2, rows=2048, cols=1 << 14, nnz=1 << 15))
+    want = oracle.csr_add(a, b, 4)
+    assert_same(CSR(want.rows, want.cols, rp, col, val), want, "stitched blocks")
+    assert bases == [int(x) for x in np.concatenate([[0], np.cumsum([b[0][-1] for b in blocks])])[:-1]]
