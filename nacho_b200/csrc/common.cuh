@@ -34,7 +34,9 @@ struct Workspace {
     int64_t *host = nullptr;  // pinned, 64 int64 slots
 };
 
-int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out);
+// `slot` selects one of several independent blocks per (device, stream): a driver that keeps an
+// intermediate alive across calls into other drivers takes slot 1 for it.
+int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out, int slot = 0);
 
 // Carves 256-byte-aligned sub-blocks out of a Workspace.
 class Carver {

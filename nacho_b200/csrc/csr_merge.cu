@@ -882,22 +882,31 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
 // (src/backend/compute.cpp:426-432 builds a + b first), so running the two-operand union twice
 // gives bit-identical values to the reference's fused three-way merge: positions present in A
 // and C only hold a + c, in B and C only b + c, in all three (a + b) + c, and explicit zeros
-// stay. The intermediate A + B lives in stream-ordered allocations that are released before
-// the call returns; it costs one extra write and read of that intermediate compared with a
-// single three-way pass.
+// stay. The intermediate A + B lives in the scratch pool; it costs one extra write and read of
+// that intermediate compared with a single three-way pass.
 int csr_add3_run(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z, bool alloc,
                  int64_t capacity, void *stream_v) {
     int st;
     if ((st = check_csr(c, true))) return st;
     if (!a || !b || a->rows != c->rows || a->cols != c->cols) return NB200_E_BADARG;
-    nb200_csr t{};
-    if ((st = csr2_run<OP_UNION>(a, b, &t, true, 0, stream_v))) return st;
-    st = csr2_run<OP_UNION>(&t, c, z, alloc, capacity, stream_v);
+    if ((st = check_csr(a, true)) || (st = check_csr(b, true))) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (t.row_ptr) cudaFreeAsync(t.row_ptr, stream);
-    if (t.col) cudaFreeAsync(t.col, stream);
-    if (t.val) cudaFreeAsync(t.val, stream);
-    return st;
+    // the intermediate lives in its own pool block (slot 1), so it survives the two calls below,
+    // which use slot 0, and costs no allocation after the first call
+    const int64_t bound = (int64_t)a->nnz + b->nnz;
+    Carver sizes;
+    sizes.take<int32_t>((size_t)a->rows + 1);
+    sizes.take<int32_t>((size_t)bound);
+    sizes.take<float>((size_t)bound);
+    Workspace *ws = nullptr;
+    if ((st = acquire_workspace(stream, sizes.used(), &ws, 1))) return st;
+    Carver carve(ws->dev);
+    nb200_csr t{};
+    t.row_ptr = carve.take<int32_t>((size_t)a->rows + 1);
+    t.col = carve.take<int32_t>((size_t)bound);
+    t.val = carve.take<float>((size_t)bound);
+    if ((st = csr2_run<OP_UNION>(a, b, &t, false, bound, stream_v))) return st;
+    return csr2_run<OP_UNION>(&t, c, z, alloc, capacity, stream_v);
 }
 
 // ------------------------------------------------------- entry point that allocates nothing ----

@@ -63,4 +63,45 @@ static __global__ void __launch_bounds__(1024) k_scan_tiles(int32_t *counts, int
     if (threadIdx.x == 0) *total_out = carry_s;
 }
 
+// Device-wide exclusive prefix of n int32 counts, in place, in one pass: 2048 counts per CTA,
+// CTA totals chained by bounded look-back. `state` holds one zeroed 8-byte word per CTA and
+// `ctl` is zeroed; the grand total lands in ctl->total. A give-up of a bounded wait is
+// recorded in ctl->status and leaves the tail of the array unscanned.
+constexpr int SCAN_NT = 256, SCAN_VT = 8;
+
+static __global__ void __launch_bounds__(SCAN_NT) k_scan_lookback(int32_t *data, int32_t n, uint64_t *state_raw, FusedCtl *ctl) {
+    __shared__ int scan_tmp[40];
+    __shared__ int s_tile;
+    __shared__ long long s_base;
+    volatile uint64_t *state = state_raw;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_tile = atomicAdd(&ctl->ticket, 1);
+    __syncthreads();
+    const int t = s_tile;
+    const int64_t p0 = ((int64_t)t * SCAN_NT + tid) * SCAN_VT;
+    int v[SCAN_VT];
+    int mine = 0;
+#pragma unroll
+    for (int q = 0; q < SCAN_VT; ++q) {
+        v[q] = p0 + q < n ? data[p0 + q] : 0;
+        mine += v[q];
+    }
+    int total;
+    int run = block_excl_sum<SCAN_NT>(mine, scan_tmp, total);
+    if (warp_id() == 0) {
+        const int64_t b = lookback_exclusive(state, t, total, &ctl->status);
+        if (lane_id() == 0) s_base = b;
+    }
+    __syncthreads();
+    const long long base = s_base;
+    if (base < 0) return;
+    long long acc = base + run;
+#pragma unroll
+    for (int q = 0; q < SCAN_VT; ++q) {
+        if (p0 + q < n) data[p0 + q] = (int32_t)min(acc, (long long)INT32_MAX);
+        acc += v[q];
+    }
+    if (t == (int)gridDim.x - 1 && tid == SCAN_NT - 1) ctl->total = acc;
+}
+
 }  // namespace nb200

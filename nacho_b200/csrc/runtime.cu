@@ -20,7 +20,7 @@ std::atomic<uint64_t> g_launches{0};
 std::atomic<int> g_profile_on{0};
 
 std::mutex g_ws_mutex;
-std::map<std::pair<int, cudaStream_t>, Workspace> g_workspaces;
+std::map<std::pair<std::pair<int, int>, cudaStream_t>, Workspace> g_workspaces;
 
 struct TimedLaunch {
     cudaEvent_t start, stop;
@@ -68,11 +68,11 @@ int note_cuda_error(cudaError_t e, const char *what) {
     return e == cudaErrorMemoryAllocation ? NB200_E_NOMEM : NB200_E_CUDA;
 }
 
-int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out) {
+int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out, int slot) {
     int dev = 0;
     NB200_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> g(g_ws_mutex);
-    Workspace &ws = g_workspaces[{dev, stream}];
+    Workspace &ws = g_workspaces[{{dev, slot}, stream}];
     if (!ws.host) NB200_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&ws.host), 64 * sizeof(int64_t), cudaHostAllocDefault));
     if (bytes > ws.dev_bytes) {
         if (ws.dev) {
@@ -142,7 +142,7 @@ int nb200_release_workspaces(void) {
     int prev = 0;
     cudaGetDevice(&prev);
     for (auto &kv : g_workspaces) {
-        cudaSetDevice(kv.first.first);
+        cudaSetDevice(kv.first.first.first);
         if (kv.second.dev) {
             cudaDeviceSynchronize();
             cudaFree(kv.second.dev);

@@ -290,11 +290,11 @@ __global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, cons
 }
 
 // Turns the exclusive prefix of the per-row counts into row offsets (rows + 1 entries).
-__global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restrict__ excl, const int64_t *__restrict__ total,
+__global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restrict__ excl, const long long *__restrict__ total,
                                                          int32_t rows, int32_t *__restrict__ c_rp) {
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i < rows) c_rp[i] = excl[i];
-    if (i == rows) c_rp[rows] = (int32_t)min(*total, (int64_t)INT32_MAX);
+    if (i == rows) c_rp[rows] = (int32_t)min(*total, (long long)INT32_MAX);
 }
 
 // ------------------------------------------------------------------------ host driver ----
@@ -311,7 +311,8 @@ struct EscPlan {
     Workspace *ws;
     RowLists lists;
     int32_t *row_count;  // rows entries (symbolic pass)
-    int64_t *d_total;
+    uint64_t *scan_block;  // FusedCtl + one word per scan CTA
+    int scan_ctas;
     EscCtl *ctl;
     LongSlots slots;
     int n_slots;
@@ -329,7 +330,8 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     sizes.take<int32_t>((size_t)rows);
     sizes.take<int32_t>((size_t)rows);
     sizes.take<int32_t>((size_t)rows + 1);
-    sizes.take<int64_t>(1);
+    const int scan_ctas = (rows + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT);
+    sizes.take<uint64_t>((size_t)scan_ctas + 8);
     sizes.take<EscCtl>(1);
     const size_t fixed = sizes.used();
     // the slots are only needed if there are long rows, which is known after the row-work
@@ -345,7 +347,8 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     plan->lists.medium_rows = carve.take<int32_t>((size_t)rows);
     plan->lists.long_rows = carve.take<int32_t>((size_t)rows);
     plan->row_count = carve.take<int32_t>((size_t)rows + 1);
-    plan->d_total = carve.take<int64_t>(1);
+    plan->scan_block = carve.take<uint64_t>((size_t)scan_ctas + 8);
+    plan->scan_ctas = scan_ctas;
     plan->ctl = carve.take<EscCtl>(1);
     plan->slots.words = words;
     plan->slots.cols = b->cols;
@@ -415,19 +418,24 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
     if ((st = esc_prepare(a, b, false, stream, &plan))) return st;
     if (products) *products = (int64_t)plan.host.products;
     if ((st = esc_run_bins<false>(a, b, plan, nullptr, stream))) return st;
+    FusedCtl *scan_ctl = reinterpret_cast<FusedCtl *>(plan.scan_block);
+    NB200_CUDA(cudaMemsetAsync(plan.scan_block, 0, sizeof(uint64_t) * ((size_t)plan.scan_ctas + 4), stream));
     {
-        LaunchScope scope("scan_tiles", stream);
-        k_scan_tiles<<<1, 1024, 0, stream>>>(plan.row_count, a->rows, plan.d_total);
+        LaunchScope scope("scan_lookback", stream);
+        k_scan_lookback<<<plan.scan_ctas, SCAN_NT, 0, stream>>>(plan.row_count, a->rows, plan.scan_block + 4, scan_ctl);
         NB200_CUDA(cudaGetLastError());
     }
     {
         LaunchScope scope("esc_row_offsets", stream);
-        k_esc_row_offsets<<<(a->rows + 256) / 256, 256, 0, stream>>>(plan.row_count, plan.d_total, a->rows, c->row_ptr);
+        k_esc_row_offsets<<<(a->rows + 256) / 256, 256, 0, stream>>>(plan.row_count, &scan_ctl->total, a->rows, c->row_ptr);
         NB200_CUDA(cudaGetLastError());
     }
-    NB200_CUDA(cudaMemcpyAsync(plan.ws->host, plan.d_total, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaMemcpyAsync(plan.ws->host, scan_ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
     NB200_CUDA(cudaStreamSynchronize(stream));
-    const int64_t nnz = plan.ws->host[0];
+    FusedCtl h;
+    std::memcpy(&h, plan.ws->host, sizeof(h));
+    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    const int64_t nnz = h.total;
     if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
     c->nnz = (int32_t)nnz;
     return NB200_OK;
