@@ -18,6 +18,7 @@
 #include <cstring>
 
 #include "merge_common.cuh"
+#include "tma.cuh"
 
 namespace nb200 {
 
@@ -28,6 +29,9 @@ namespace {
 #endif
 #ifndef COO3_VT
 #define COO3_VT 11
+#endif
+#ifndef COO3_MIN_CTAS
+#define COO3_MIN_CTAS 4
 #endif
 constexpr int NT = COO3_NT;
 constexpr int VT = COO3_VT;
@@ -93,60 +97,129 @@ __global__ void __launch_bounds__(NT) k_coo3_partition(Coo3In A, Coo3In B, Packi
     }
 }
 
+constexpr int RAW_SLOTS = CAP + 16;  // words per staged raw array (i, j, k, value)
+static_assert(RAW_SLOTS >= KEY_SLOTS, "packed keys reuse the raw i and j arrays");
+constexpr int MBAR_POLL_LIMIT = 1 << 24;
+constexpr int ERR_COPY_TIMEOUT = 2;
+
+// Number of 4-byte elements from `p` up to the next 16-byte boundary (0..3).
+__device__ __forceinline__ int head_elems(const void *p) {
+    return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
+}
+
 template <int MODE>
-__global__ void __launch_bounds__(NT) k_coo3_tile(Coo3In A, Coo3In B, Packing pk, Cuts2 cuts, int32_t *tile_count,
-                                                  uint64_t *tile_state_raw, FusedCtl *ctl, Coo3Out Z) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3In B, Packing pk, Cuts2 cuts, int32_t *tile_count,
+                                                                 uint64_t *tile_state_raw, FusedCtl *ctl, Coo3Out Z) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
     __shared__ int s_tile;
     __shared__ long long s_base;
+    __shared__ __align__(8) uint64_t mbar;
     constexpr bool WRITES = MODE != MODE_COUNT;
     volatile uint64_t *tile_state = tile_state_raw;
     const int tid = threadIdx.x;
     int t = blockIdx.x;
-    if (MODE == MODE_FUSED) {
+    if (tid == 0) {
         // number tiles in the order CTAs start, so a tile only waits on running CTAs
-        if (tid == 0) s_tile = atomicAdd(&ctl->ticket, 1);
-        __syncthreads();
-        t = s_tile;
+        if (MODE == MODE_FUSED) s_tile = atomicAdd(&ctl->ticket, 1);
+        mbar_init(&mbar, 1);
+        mbar_fence_init();
     }
+    __syncthreads();
+    if (MODE == MODE_FUSED) t = s_tile;
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
     const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
     const int n = na + nb;
 
-    // Shared layout: keys of A, a sentinel, keys of B, sentinels and slack; values mirror the
-    // positions; the value staging array of the result follows (key staging reuses the keys).
+    // Shared layout, in 4-byte words: four raw arrays of RAW_SLOTS words each (i, j, k, value),
+    // where A's entry e sits at word oa + e and B's at word ob + e, chosen so that 16-byte
+    // boundaries of global memory fall on 16-byte boundaries here (what a bulk copy needs).
+    // Once the coordinates are packed, the 64-bit keys take the place of the raw i and j arrays,
+    // and the value staging array of the result takes the place of the raw k array.
+    uint32_t *raw = reinterpret_cast<uint32_t *>(smem_raw);
     uint64_t *kx = reinterpret_cast<uint64_t *>(smem_raw);
     uint64_t *ky = kx + na + 1;
-    float *vx = reinterpret_cast<float *>(smem_raw + sizeof(uint64_t) * KEY_SLOTS);
-    float *vy = vx + na + 1;
-    float *out_val = vx + KEY_SLOTS;
+    float *out_val = reinterpret_cast<float *>(raw + 2 * RAW_SLOTS);
     uint64_t *out_key = kx;
+    const int ha = head_elems(A.i + a0), hb = head_elems(B.i + b0);
+    const int oa = (4 - ha) & 3;
+    const int ob = ((oa + na + 3) & ~3) + ((4 - hb) & 3);
+    const float *vx = reinterpret_cast<const float *>(raw + 3 * RAW_SLOTS) + oa;
+    const float *vy = reinterpret_cast<const float *>(raw + 3 * RAW_SLOTS) + ob;
 
-    // ---- stage: every load of a thread is issued before the first use, so that their
-    // latencies overlap; coordinates are packed on the way into shared memory
+    // ---- stage the eight operand arrays: aligned interiors by bulk copy, ragged ends (at most
+    // three entries each side) and arrays whose alignment differs from their i array's by
+    // plain loads
     {
-        uint64_t hi[VT];
+        const void *src[8] = {A.i + a0, A.j + a0, A.k + a0, A.val + a0, B.i + b0, B.j + b0, B.k + b0, B.val + b0};
+        const int head_a = min(na, ha), head_b = min(nb, hb);
+        const int nva = (na - head_a) >> 2, nvb = (nb - head_b) >> 2;
+        bool bulk[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) bulk[q] = head_elems(src[q]) == (q < 4 ? ha : hb) && (WRITES || (q & 3) != 3);
+        if (tid == 0) {
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) bytes += bulk[q] ? 16u * (q < 4 ? nva : nvb) : 0u;
+            mbar_arrive_expect_tx(&mbar, bytes);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int nv = q < 4 ? nva : nvb, head = q < 4 ? head_a : head_b;
+                if (bulk[q] && nv)
+                    bulk_load(raw + (q & 3) * RAW_SLOTS + (q < 4 ? oa : ob) + head,
+                              static_cast<const uint32_t *>(src[q]) + head, 16u * nv, &mbar);
+            }
+        }
+        if (tid >= 32 && tid < 32 + 48) {  // ragged ends: 8 arrays x (3 head + 3 tail)
+            const int q = (tid - 32) / 6, e = (tid - 32) % 6;
+            const int count = q < 4 ? na : nb, head = q < 4 ? head_a : head_b, nv = q < 4 ? nva : nvb;
+            const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
+            const bool live = (e < 3 ? e < head : idx < count) && (WRITES || (q & 3) != 3);
+            bool is_bulk = false;
+#pragma unroll
+            for (int qq = 0; qq < 8; ++qq) is_bulk = qq == q ? bulk[qq] : is_bulk;
+            if (live && is_bulk) {
+                const uint32_t *g = nullptr;
+#pragma unroll
+                for (int qq = 0; qq < 8; ++qq) g = qq == q ? static_cast<const uint32_t *>(src[qq]) : g;
+                raw[(q & 3) * RAW_SLOTS + (q < 4 ? oa : ob) + idx] = ld_nc(g + idx);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (!bulk[q] && (WRITES || (q & 3) != 3)) {
+                const int count = q < 4 ? na : nb;
+                for (int e = tid; e < count; e += NT)
+                    raw[(q & 3) * RAW_SLOTS + (q < 4 ? oa : ob) + e] = ld_nc(static_cast<const uint32_t *>(src[q]) + e);
+            }
+        }
+    }
+    const bool landed = mbar_wait_bounded(&mbar, 0, MBAR_POLL_LIMIT);
+    if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
+        if (tid == 0) {
+            if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
+            if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;
+            mbar_wait_bounded(&mbar, 0, MBAR_POLL_LIMIT);  // second bounded wait for copies in flight
+        }
+        return;
+    }
+
+    // ---- pack the coordinates into 64-bit keys (registers first: the keys overwrite the raw
+    // i and j arrays)
+    {
+        uint64_t packed[VT];
 #pragma unroll
         for (int q = 0; q < VT; ++q) {
             const int e = tid + q * NT;  // merged staging slot: A's entries first, then B's
-            hi[q] = 0;
-            if (e < na) hi[q] = ((uint64_t)(uint32_t)ld_nc(A.i + a0 + e) << pk.bj) | (uint32_t)ld_nc(A.j + a0 + e);
-            else if (e < n) hi[q] = ((uint64_t)(uint32_t)ld_nc(B.i + b0 + (e - na)) << pk.bj) | (uint32_t)ld_nc(B.j + b0 + (e - na));
+            const int w = e < na ? oa + e : ob + (e - na);
+            packed[q] = e < n ? pk.pack((int32_t)raw[w], (int32_t)raw[RAW_SLOTS + w], (int32_t)raw[2 * RAW_SLOTS + w]) : INF;
         }
+        __syncthreads();
 #pragma unroll
         for (int q = 0; q < VT; ++q) {
             const int e = tid + q * NT;
-            if (e < na) kx[e] = (hi[q] << pk.bk) | (uint32_t)ld_nc(A.k + a0 + e);
-            else if (e < n) ky[e - na] = (hi[q] << pk.bk) | (uint32_t)ld_nc(B.k + b0 + (e - na));
-        }
-        if (WRITES) {
-#pragma unroll
-            for (int q = 0; q < VT; ++q) {
-                const int e = tid + q * NT;
-                if (e < na) vx[e] = ld_nc(A.val + a0 + e);
-                else if (e < n) vy[e - na] = ld_nc(B.val + b0 + (e - na));
-            }
+            if (e < na) kx[e] = packed[q];
+            else if (e < n) ky[e - na] = packed[q];
         }
         if (tid < VT + 1) ky[nb + tid] = INF;
         if (tid == 0) kx[na] = INF;
@@ -245,7 +318,7 @@ __global__ void __launch_bounds__(NT) k_coo3_tile(Coo3In A, Coo3In B, Packing pk
     }
 }
 
-constexpr size_t coo3_smem_bytes() { return (sizeof(uint64_t) + 2 * sizeof(float)) * (size_t)KEY_SLOTS; }
+constexpr size_t coo3_smem_bytes() { return 16 * (size_t)RAW_SLOTS; }
 
 int bits_for(int32_t extent) {
     int b = 1;
