@@ -429,7 +429,19 @@ def main():
         cls = type(tensors[0])
         host_out = [torch.empty(b.numel(), dtype=b.dtype).pin_memory() for b in buffers_of(z)]
 
+        streamed = spec["op"] in ("csr_add", "csr_mul")
+        if streamed:
+            # host-buffer entry point: row blocks streamed through the GPU, copies overlap the merge
+            from nacho_b200 import host as host_api
+            host_fn = host_api.csr_add_host if spec["op"] == "csr_add" else host_api.csr_mul_host
+            host_ops = [(int(s[0]), int(s[1]), *h) for h, s in zip(host_in, shapes)]
+            cap = sum(h[1].numel() for h in host_in) if spec["op"] == "csr_add" else min(h[1].numel() for h in host_in)
+            out_buf = host_api.result_buffers(rows_local, cap)
+
         def e2e_step():
+            if streamed:
+                host_fn(host_ops[0], host_ops[1], out=out_buf, device=dev)
+                return
             dev_ops = [cls(*[b.to(dev, non_blocking=True) for b in h], s) for h, s in zip(host_in, shapes)]
             zz = op_fn(*dev_ops)
             for dst, src in zip(host_out, buffers_of(zz)):

@@ -160,7 +160,18 @@ int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
 int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
                            int64_t capacity, void *stream);
 
-/* Z = (A + B) + C in one pass, left-to-right association. Replaces
+/* Host-buffer forms of add and multiply: every pointer in a, b and z is a HOST pointer (pinned
+ * memory gives full PCIe speed; pageable memory works but copies synchronously). The matrices
+ * are streamed through the current device in row blocks of about 12 M operand entries on three
+ * internal streams, so that the upload of one block, the merge of the previous one and the
+ * download of the one before overlap. z->row_ptr (rows + 1), z->col and z->val (`capacity`
+ * entries each) are the caller's; on return z->nnz is the result length and the arrays are
+ * complete (the call synchronises its own streams). NB200_E_CAPACITY if the result does not fit.
+ * The reference has no counterpart: its operators take device tensors only. */
+int nb200_csr_add_f32_host(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity);
+int nb200_csr_mul_f32_host(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity);
+
+/* Z = (A + B) + C, left-to-right association, in one call. Replaces
  * csr_add_3::csr_add_3_gpu_i32_f32 (compiler.cpp:114; src/backend/compute.cpp:426-432).
  * Capacity that always suffices: nnz(A) + nnz(B) + nnz(C). */
 int nb200_csr_add_3_f32(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c,

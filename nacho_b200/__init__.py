@@ -15,7 +15,7 @@ import sys
 
 __all__ = ["nacho", "install_as_nacho"]
 
-_LAZY = ("_capi", "nacho", "shard")
+_LAZY = ("_capi", "nacho", "shard", "host")
 
 
 def __getattr__(name):
