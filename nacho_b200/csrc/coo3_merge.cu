@@ -69,12 +69,27 @@ __device__ __forceinline__ uint64_t key_at(const Coo3In &T, const Packing &pk, i
     return pk.pack(ld_nc(T.i + p), ld_nc(T.j + p), ld_nc(T.k + p));
 }
 
-// One warp per cut. Cut t sits at merged position min(t * tile_step, total); equal
-// coordinates stay on one side of a cut.
-__global__ void __launch_bounds__(NT) k_coo3_partition(Coo3In A, Coo3In B, Packing pk, int64_t total, int32_t tile_step,
-                                                       int32_t num_tiles, Cuts2 cuts) {
-    const int t = (blockIdx.x * NT + threadIdx.x) >> 5;
-    if (t > num_tiles) return;
+// Tile cuts, found in two levels so that the searches read little: every COARSE-th cut by one
+// warp with a 32-ary search over the whole diagonal (few cuts, many probes each), then every
+// other cut by one thread with a binary search between its two coarse neighbours (many cuts,
+// few probes each). Cut t sits at merged position min(t * tile_step, total); equal coordinates
+// stay on one side of a cut.
+constexpr int COARSE = 32;
+
+__device__ __forceinline__ void finish_cut(const Coo3In &A, const Coo3In &B, const Packing &pk, int64_t d, int64_t x,
+                                           int32_t *pa, int32_t *pb) {
+    int64_t y = d - x;
+    if (x > 0 && y < B.nnz && key_at(A, pk, x - 1) == key_at(B, pk, y)) ++y;
+    *pa = (int32_t)x;
+    *pb = (int32_t)y;
+}
+
+__global__ void __launch_bounds__(NT) k_coo3_partition_coarse(Coo3In A, Coo3In B, Packing pk, int64_t total, int32_t tile_step,
+                                                              int32_t num_tiles, Cuts2 cuts) {
+    const int c = (blockIdx.x * NT + threadIdx.x) >> 5;
+    const int64_t t64 = (int64_t)c * COARSE;
+    if (t64 > num_tiles + COARSE - 1) return;
+    const int t = (int)min(t64, (int64_t)num_tiles);  // the last coarse cut is the end of the data
     const int64_t d = (int64_t)t * tile_step;
     int32_t pa, pb;
     if (t == 0) {
@@ -86,15 +101,35 @@ __global__ void __launch_bounds__(NT) k_coo3_partition(Coo3In A, Coo3In B, Packi
         const int64_t x_lo = d - B.nnz > 0 ? d - B.nnz : 0;
         const int64_t x_hi = d < A.nnz ? d : A.nnz;
         const int64_t x = warp_count_true(x_lo, x_hi, [&](int64_t m) { return key_at(A, pk, m) <= key_at(B, pk, d - 1 - m); });
-        int64_t y = d - x;
-        if (x > 0 && y < B.nnz && key_at(A, pk, x - 1) == key_at(B, pk, y)) ++y;
-        pa = (int32_t)x;
-        pb = (int32_t)y;
+        finish_cut(A, B, pk, d, x, &pa, &pb);
     }
     if (lane_id() == 0) {
         cuts.a[t] = pa;
         cuts.b[t] = pb;
     }
+}
+
+__global__ void __launch_bounds__(NT) k_coo3_partition_fine(Coo3In A, Coo3In B, Packing pk, int64_t total, int32_t tile_step,
+                                                            int32_t num_tiles, Cuts2 cuts) {
+    const int t = blockIdx.x * NT + threadIdx.x;
+    if (t >= num_tiles || t % COARSE == 0) return;
+    const int64_t d = (int64_t)t * tile_step;
+    int32_t pa, pb;
+    if (d >= total) {
+        pa = A.nnz;
+        pb = B.nnz;
+    } else {
+        const int c0 = t / COARSE * COARSE, c1 = min(c0 + COARSE, num_tiles);
+        int64_t lo = max((int64_t)cuts.a[c0], d - B.nnz > 0 ? d - B.nnz : 0);
+        int64_t hi = min((int64_t)cuts.a[c1], d < A.nnz ? d : (int64_t)A.nnz);
+        while (lo < hi) {  // first m with key_A(m) > key_B(d - 1 - m)
+            const int64_t mid = (lo + hi) >> 1;
+            if (key_at(A, pk, mid) <= key_at(B, pk, d - 1 - mid)) lo = mid + 1; else hi = mid;
+        }
+        finish_cut(A, B, pk, d, lo, &pa, &pb);
+    }
+    cuts.a[t] = pa;
+    cuts.b[t] = pb;
 }
 
 constexpr int RAW_SLOTS = CAP + 16;  // words per staged raw array (i, j, k, value)
@@ -437,8 +472,9 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     }
     {
         LaunchScope scope("coo3_partition", stream);
-        const int warps = num_tiles + 1;
-        k_coo3_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        const int warps = num_tiles / COARSE + 2;
+        k_coo3_partition_coarse<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        k_coo3_partition_fine<<<(num_tiles + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_coo3_partition"));

@@ -27,24 +27,46 @@ namespace {
 
 constexpr int NT = 256;
 
-// One thread per (i, j) fibre q: its i is the last fibre-list start <= q; the thread then
-// writes (i, j) for every entry of the fibre.
+// One warp per 32 consecutive (i, j) fibres. Each lane looks up its fibre's i (the last
+// fibre-list start <= q, by binary search) and j; the warp then walks the entries of its 32
+// fibres together, each lane finding the fibre of its entry among the 32 starts by shuffles,
+// so that the writes are coalesced however short the fibres are.
 __global__ void __launch_bounds__(NT) k_csf_expand(int32_t n_i, int32_t n_j, const int32_t *__restrict__ i_idx,
                                                    const int32_t *__restrict__ j_ptr, const int32_t *__restrict__ j_idx,
                                                    const int32_t *__restrict__ k_ptr, int32_t *__restrict__ out_i,
                                                    int32_t *__restrict__ out_j) {
-    const int q = blockIdx.x * NT + threadIdx.x;
-    if (q >= n_j) return;
-    int lo = 0, hi = n_i - 1;  // largest r with j_ptr[r] <= q
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (ld_nc(j_ptr + mid) <= q) lo = mid; else hi = mid - 1;
+    const int w = (blockIdx.x * NT + threadIdx.x) >> 5;
+    const int q0 = w * 32;
+    if (q0 >= n_j) return;
+    const int lane = lane_id();
+    const int q = q0 + lane;
+    int32_t start = INT32_MAX, i = 0, j = 0;
+    if (q < n_j) {
+        int lo = 0, hi = n_i - 1;  // largest r with j_ptr[r] <= q
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (ld_nc(j_ptr + mid) <= q) lo = mid; else hi = mid - 1;
+        }
+        i = ld_nc(i_idx + lo);
+        j = ld_nc(j_idx + q);
+        start = ld_nc(k_ptr + q);
     }
-    const int32_t i = ld_nc(i_idx + lo), j = ld_nc(j_idx + q);
-    const int32_t p0 = ld_nc(k_ptr + q), p1 = ld_nc(k_ptr + q + 1);
-    for (int32_t p = p0; p < p1; ++p) {
-        out_i[p] = i;
-        out_j[p] = j;
+    const int32_t p_begin = __shfl_sync(FULL_MASK, start, 0);
+    const int32_t p_end = ld_nc(k_ptr + min(q0 + 32, n_j));
+    for (int32_t base = p_begin; base < p_end; base += 32) {
+        const int32_t p = base + lane;
+        int lo = 0, hi = 31;  // largest lane whose fibre starts at or before p
+#pragma unroll
+        for (int step = 0; step < 5; ++step) {
+            const int mid = (lo + hi + 1) >> 1;
+            const int32_t sm = __shfl_sync(FULL_MASK, start, mid);
+            if (sm <= p) lo = mid; else hi = mid - 1;
+        }
+        const int32_t vi = __shfl_sync(FULL_MASK, i, lo), vj = __shfl_sync(FULL_MASK, j, lo);
+        if (p < p_end) {
+            out_i[p] = vi;
+            out_j[p] = vj;
+        }
     }
 }
 
@@ -213,11 +235,11 @@ int csf_add_run(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, bool al
 
     if (a->n_j > 0) {
         LaunchScope scope("csf_expand", stream);
-        k_csf_expand<<<(a->n_j + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
+        k_csf_expand<<<(int)(((int64_t)a->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
     }
     if (b->n_j > 0) {
         LaunchScope scope("csf_expand", stream);
-        k_csf_expand<<<(b->n_j + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
+        k_csf_expand<<<(int)(((int64_t)b->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csf_expand"));
