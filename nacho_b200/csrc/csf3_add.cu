@@ -94,12 +94,22 @@ __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t 
     const int t = s_tile;
     const int64_t p0 = ((int64_t)t * NT + tid) * CVT;
     int32_t ci[CVT + 1], cj[CVT + 1];
+    ci[0] = p0 > 0 && p0 - 1 < nnz ? ld_nc(zi + p0 - 1) : -1;
+    cj[0] = p0 > 0 && p0 - 1 < nnz ? ld_nc(zj + p0 - 1) : -1;
+    if (p0 + CVT <= nnz) {  // the thread's 8 entries start on a 32-byte boundary: two 16-byte loads per array
+        static_assert(CVT == 8, "vector loads below assume 8 entries per thread");
+        const int4 i0 = __ldg(reinterpret_cast<const int4 *>(zi + p0)), i1 = __ldg(reinterpret_cast<const int4 *>(zi + p0) + 1);
+        const int4 j0 = __ldg(reinterpret_cast<const int4 *>(zj + p0)), j1 = __ldg(reinterpret_cast<const int4 *>(zj + p0) + 1);
+        ci[1] = i0.x, ci[2] = i0.y, ci[3] = i0.z, ci[4] = i0.w, ci[5] = i1.x, ci[6] = i1.y, ci[7] = i1.z, ci[8] = i1.w;
+        cj[1] = j0.x, cj[2] = j0.y, cj[3] = j0.z, cj[4] = j0.w, cj[5] = j1.x, cj[6] = j1.y, cj[7] = j1.z, cj[8] = j1.w;
+    } else {
 #pragma unroll
-    for (int q = 0; q <= CVT; ++q) {
-        const int64_t p = p0 - 1 + q;
-        const bool in = p >= 0 && p < nnz;
-        ci[q] = in ? ld_nc(zi + p) : -1;
-        cj[q] = in ? ld_nc(zj + p) : -1;
+        for (int q = 1; q <= CVT; ++q) {
+            const int64_t p = p0 - 1 + q;
+            const bool in = p < nnz;
+            ci[q] = in ? ld_nc(zi + p) : -1;
+            cj[q] = in ? ld_nc(zj + p) : -1;
+        }
     }
     unsigned head_i = 0, head_ij = 0;
 #pragma unroll
