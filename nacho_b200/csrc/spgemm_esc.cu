@@ -28,7 +28,7 @@ namespace {
 constexpr int SMALL_P = 32;
 constexpr int MEDIUM_P = 2048;
 constexpr int MED_NT = 128;
-constexpr int LONG_NT = 256;
+constexpr int LONG_NT = 1024;
 
 struct CsrView {
     const int32_t *rp;
@@ -132,12 +132,15 @@ __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const i
     }
     float v = __shfl_sync(FULL_MASK, my_val, src);  // value of the product now at this lane
     float acc = v;
-#pragma unroll
-    for (int t = 1; t < 32; ++t) {  // head lanes add their run in sorted (= expansion) order
+    // longest run of equal columns in this row (distance from a head to the next head or to
+    // the end of the valid lanes): the summation loop needs no more steps than that
+    const unsigned later = lane < 31 ? (heads >> (lane + 1)) : 0u;
+    const int n_valid = __popc(__ballot_sync(FULL_MASK, valid));
+    const int my_run = head ? (later ? __ffs(later) : n_valid - lane) : 0;
+    const int longest = __reduce_max_sync(FULL_MASK, my_run);
+    for (int t = 1; t < longest; ++t) {  // head lanes add their run in sorted (= expansion) order
         const float nv = __shfl_down_sync(FULL_MASK, v, t);
-        const uint32_t nc = __shfl_down_sync(FULL_MASK, col, t);
-        const bool nvalid = __shfl_down_sync(FULL_MASK, (int)valid, t) != 0;
-        if (lane + t < 32 && nvalid && nc == col) acc += nv;
+        if (t < my_run) acc += nv;
     }
     if (head) {
         const int pos = ld_nc(c_rp + i) + __popc(heads & ((1u << lane) - 1u));
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, cons
                                                       LongSlots slots, int32_t *__restrict__ row_count,
                                                       const int32_t *__restrict__ c_rp, int32_t *__restrict__ c_col,
                                                       float *__restrict__ c_val) {
-    __shared__ int scan_tmp[40];
+    __shared__ int scan_tmp[72];
     const int tid = threadIdx.x;
     uint32_t *bitmap = slots.bitmap + (size_t)blockIdx.x * slots.words;
     double *acc = NUMERIC ? slots.acc + (size_t)blockIdx.x * slots.cols : nullptr;
@@ -305,7 +308,8 @@ int check_operand(const nb200_csr *m) {
     return NB200_OK;
 }
 
-constexpr size_t LONG_SLOT_BUDGET = size_t(2) << 30;  // bytes of accumulator slots per call
+// Accumulator slots are sized to stay resident in the 126 MB L2, where their atomics are served.
+constexpr size_t LONG_SLOT_BUDGET = size_t(96) << 20;
 
 struct EscPlan {
     Workspace *ws;
