@@ -39,6 +39,11 @@ if ROOT not in sys.path:
 
 FALLBACK_HBM_GBS = 6650.0
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per algorithmic byte of one launch
+# of a kernel, from one ncu capture of a reduced case each (profiles/*.md give the commands);
+# traffic grows in proportion to the entries, so the ratio is applied to the full launch.
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"csr_add_fused": 0.877, "coo3_add_fused": 0.92}
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -487,7 +492,9 @@ def main():
                 extra = {"products": products, "esc_model_bytes": roof_bytes}
             achieved = roof_bytes / (kernels[top]["ms_per_step"] * 1e-3) / 1e9
             roof = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
+                    "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth",
+                    "traffic": (TRAFFIC_PER_ALGORITHMIC_BYTE[top] * roof_bytes / max(kernels[top]["launches_per_step"], 1)
+                                if top in TRAFFIC_PER_ALGORITHMIC_BYTE else None),
                     "kernel_ms_per_step": kernels[top]["ms_per_step"], "frac_of_nominal_8TBs": achieved / 8000.0}
         base = None
         if not args.no_cpu_baseline:
