@@ -162,10 +162,11 @@ __device__ __forceinline__ void st_relaxed_gpu(volatile uint64_t *p, uint64_t v)
 // together, so a round costs one memory round trip however many words it covers.
 constexpr int LOOKBACK_DEPTH = 1;
 
-__device__ __forceinline__ int64_t lookback_exclusive(volatile uint64_t *state, int t, int64_t aggregate,
-                                                      DeviceStatus *status) {
-    if (lane_id() == 0) st_relaxed_gpu(state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)aggregate);
-    if (t == 0) return 0;
+// Sum of the counts of tiles [0, t), read off the tile words of the predecessors; publishes
+// nothing. Polls with `sleep_ns` between rounds. Returns -1 (and records the tile in `status`)
+// if a bounded wait gives up. Called by all 32 lanes of one warp, t > 0.
+__device__ __forceinline__ int64_t lookback_predecessors(volatile uint64_t *state, int t, DeviceStatus *status,
+                                                         unsigned sleep_ns) {
     int64_t exclusive = 0;
     bool failed = false, done = false;
     for (int pos = t - 1; !done; pos -= 32 * LOOKBACK_DEPTH) {
@@ -184,12 +185,12 @@ __device__ __forceinline__ int64_t lookback_exclusive(volatile uint64_t *state, 
             for (int j = 0; j < LOOKBACK_DEPTH; ++j) ready = ready && (s[j] >> 62) != 0;
             // only words up to the nearest prefix matter; waiting for all of them is simpler and
             // they belong to tiles that started earlier still
-            if (ready) break;
+            if (__all_sync(FULL_MASK, ready)) break;
             if (++polls >= LOOKBACK_POLL_LIMIT) {
                 timed_out = true;
                 break;
             }
-            __nanosleep(32);
+            __nanosleep(sleep_ns);
         }
         if (__any_sync(FULL_MASK, timed_out)) {
             failed = true;
@@ -208,13 +209,21 @@ __device__ __forceinline__ int64_t lookback_exclusive(volatile uint64_t *state, 
         }
     }
     if (failed) {
-        if (lane_id() == 0) {
-            if (atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
-            st_relaxed_gpu(state + t, LB_PREFIX);  // unblock successors; the call reports the failure
-        }
+        if (lane_id() == 0 && atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
         return -1;
     }
-    if (lane_id() == 0) st_relaxed_gpu(state + t, LB_PREFIX | (uint64_t)(exclusive + aggregate));
+    return exclusive;
+}
+
+// Publishes the tile's count, walks back, publishes the inclusive prefix. Returns the sum of the
+// counts of tiles [0, t), or -1 after a give-up (the tile then still publishes a prefix so that
+// its successors do not wait on it). Called by all 32 lanes of one warp.
+__device__ __forceinline__ int64_t lookback_exclusive(volatile uint64_t *state, int t, int64_t aggregate,
+                                                      DeviceStatus *status) {
+    if (lane_id() == 0) st_relaxed_gpu(state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)aggregate);
+    if (t == 0) return 0;
+    const int64_t exclusive = lookback_predecessors(state, t, status, 32);
+    if (lane_id() == 0) st_relaxed_gpu(state + t, LB_PREFIX | (uint64_t)(exclusive < 0 ? 0 : exclusive + aggregate));
     return exclusive;
 }
 

@@ -499,12 +499,16 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     CSR2_PHASE_END(1, (int)keys[tid]);
 
     if (scan_warp) {
-        // ---- scan warp: wait for the tile's count, turn it into the output base
+        // ---- scan warp: the output base of the tile is the sum of the counts of all earlier
+        // tiles, which does not depend on this tile's own count. So the walk over the
+        // predecessors' words starts now, while the workers are still merging, and is usually
+        // over by the time they know their count.
         if (MODE != MODE_FUSED) return;
-        CountBar::sync();
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, 256);
+        CountBar::sync();  // the workers have published the tile's count by now
         const int total = s_total;
-        const int64_t bse = lookback_exclusive(tile_state, t, total, &ctl->status);
         if (lane_id() == 0) {
+            if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
             s_base = bse;
             if (bse >= 0 && t == (int)gridDim.x - 1) ctl->total = bse + total;
         }
@@ -619,9 +623,13 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     thread_rank[tid] = rank;
     thread_emit[tid] = emit;
     if (MODE == MODE_FUSED) {
-        if (tid == 0) s_total = total;
+        if (tid == 0) {
+            // successors can add this tile's count from here on
+            st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
+            s_total = total;
+        }
         __threadfence_block();
-        CountBar::arrive();  // the scan warp starts its look-back now
+        CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
     }
     CSR2_PHASE_END(4, rank + (int)r[3]);
 
