@@ -132,6 +132,11 @@ __global__ void __launch_bounds__(NT) k_coo3_partition_fine(Coo3In A, Coo3In B, 
     cuts.b[t] = pb;
 }
 
+// Hardware barriers of the tile kernel: 0 = whole CTA, 1 = the NT worker threads, 2 = workers
+// arrive / the scan warp waits ("the tile's count is known").
+using WorkerBar = NamedBarrier<1, NT>;
+using CountBar = NamedBarrier<2, NT + 32>;
+
 constexpr int RAW_SLOTS = CAP + 16;  // words per staged raw array (i, j, k, value)
 static_assert(RAW_SLOTS >= KEY_SLOTS, "packed keys reuse the raw i and j arrays");
 constexpr int MBAR_POLL_LIMIT = 1 << 24;
@@ -143,16 +148,18 @@ __device__ __forceinline__ int head_elems(const void *p) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3In B, Packing pk, Cuts2 cuts, int32_t *tile_count,
+__global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3In B, Packing pk, Cuts2 cuts, int32_t *tile_count,
                                                                  uint64_t *tile_state_raw, FusedCtl *ctl, Coo3Out Z) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
     __shared__ int s_tile;
     __shared__ long long s_base;
     __shared__ __align__(8) uint64_t mbar;
+    __shared__ int s_total;
     constexpr bool WRITES = MODE != MODE_COUNT;
     volatile uint64_t *tile_state = tile_state_raw;
     const int tid = threadIdx.x;
+    const bool scan_warp = tid >= NT;  // one extra warp: it only turns counts into output bases
     int t = blockIdx.x;
     if (tid == 0) {
         // number tiles in the order CTAs start, so a tile only waits on running CTAs
@@ -224,7 +231,7 @@ __global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3I
         for (int q = 0; q < 8; ++q) {
             if (!bulk[q] && (WRITES || (q & 3) != 3)) {
                 const int count = q < 4 ? na : nb;
-                for (int e = tid; e < count; e += NT)
+                for (int e = tid; e < count && !scan_warp; e += NT)
                     raw[(q & 3) * RAW_SLOTS + (q < 4 ? oa : ob) + e] = ld_nc(static_cast<const uint32_t *>(src[q]) + e);
             }
         }
@@ -239,6 +246,22 @@ __global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3I
         return;
     }
 
+    if (scan_warp) {
+        // the output base is the sum of the counts of all earlier tiles and does not depend on
+        // this tile's count: walk the predecessors' words while the workers merge
+        if (MODE != MODE_FUSED) return;
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, 1000);
+        CountBar::sync();  // the workers have published the tile's count by now
+        const int total = s_total;
+        if (lane_id() == 0) {
+            if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
+            s_base = bse;
+            if (bse >= 0 && t == (int)gridDim.x - 1) ctl->total = bse + total;
+        }
+        __syncthreads();
+        return;
+    }
+
     // ---- pack the coordinates into 64-bit keys (registers first: the keys overwrite the raw
     // i and j arrays)
     {
@@ -249,7 +272,7 @@ __global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3I
             const int w = e < na ? oa + e : ob + (e - na);
             packed[q] = e < n ? pk.pack((int32_t)raw[w], (int32_t)raw[RAW_SLOTS + w], (int32_t)raw[2 * RAW_SLOTS + w]) : INF;
         }
-        __syncthreads();
+        WorkerBar::sync();
 #pragma unroll
         for (int q = 0; q < VT; ++q) {
             const int e = tid + q * NT;
@@ -259,7 +282,7 @@ __global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3I
         if (tid < VT + 1) ky[nb + tid] = INF;
         if (tid == 0) kx[na] = INF;
     }
-    __syncthreads();
+    WorkerBar::sync();
 
     // ---- split the tile among threads: merge-path diagonal tid * VT, ties take A first
     const int diag = min(tid * VT, n);
@@ -303,25 +326,19 @@ __global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3I
     // ---- rank the survivors inside the tile
     int total;
     const int mine = __popc(emit);
-    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // syncs: key reads are done
+    const int rank = block_excl_sum<NT, WorkerBar>(mine, scan_tmp, total);  // syncs: key reads are done
     if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
         return;
     }
-
-    // ---- output base of the tile
-    long long base;
-    if (MODE == MODE_FILL) {
-        base = tile_count[t];
-    } else {
-        if (warp_id() == 0) {
-            const int64_t bse = lookback_exclusive(tile_state, t, total, &ctl->status);
-            if (lane_id() == 0) s_base = bse;
+    if (MODE == MODE_FUSED) {
+        if (tid == 0) {
+            // successors can add this tile's count from here on
+            st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
+            s_total = total;
         }
-        __syncthreads();
-        base = s_base;
-        if (base < 0) return;  // a bounded wait gave up; the host reports it
-        if (t == (int)gridDim.x - 1 && tid == 0) ctl->total = base + total;
+        __threadfence_block();
+        CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
     }
 
     // ---- compact through shared memory, then unpack and store coalesced
@@ -343,7 +360,10 @@ __global__ void __launch_bounds__(NT, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3I
             yi += !tx;
         }
     }
-    __syncthreads();
+    // ---- output base of the tile (from the scan warp, or from the scanned counts)
+    if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
+    const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
+    if (base < 0) return;  // a bounded wait gave up; the host reports it
     for (int i = tid; i < total; i += NT) {
         const uint64_t kq = out_key[i];
         Z.i[base + i] = pk.i_of(kq);
@@ -375,7 +395,7 @@ cudaError_t launch_coo3_tile(const Coo3In &A, const Coo3In &B, const Packing &pk
     }
     static const char *const names[3] = {"coo3_add_count", "coo3_add_fill", "coo3_add_fused"};
     LaunchScope scope(names[MODE], stream);
-    kernel<<<num_tiles, NT, coo3_smem_bytes(), stream>>>(A, B, pk, cuts, tile_count, tile_state, ctl, Z);
+    kernel<<<num_tiles, NT + 32, coo3_smem_bytes(), stream>>>(A, B, pk, cuts, tile_count, tile_state, ctl, Z);
     return cudaGetLastError();
 }
 

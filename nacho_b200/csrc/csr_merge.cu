@@ -37,6 +37,9 @@ namespace {
 #ifndef CSR2_VT
 #define CSR2_VT 19
 #endif
+#ifndef CSR2_LB_SLEEP
+#define CSR2_LB_SLEEP 1000  // nanoseconds between polls of the predecessors' tile words (shorter polls measurably slow the workers)
+#endif
 #ifndef CSR2_MIN_CTAS
 #define CSR2_MIN_CTAS 3
 #endif
@@ -504,7 +507,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         // predecessors' words starts now, while the workers are still merging, and is usually
         // over by the time they know their count.
         if (MODE != MODE_FUSED) return;
-        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, 256);
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, CSR2_LB_SLEEP);
         CountBar::sync();  // the workers have published the tile's count by now
         const int total = s_total;
         if (lane_id() == 0) {
