@@ -188,9 +188,9 @@ int nb200_csr_add_3_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200
  * src/backend/stitch_and_generate_gpu.cpp:14-139,257-363). Unlike the reference, product
  * counts are 64-bit (a product count above 2^31 is fine as long as nnz(C) fits int32) and
  * rows with at most 2048 products sum equal-column products in a fixed order (ascending j);
- * longer rows accumulate in float64 with atomics. Rows longer than 2048 products need a dense
- * per-row accumulator over B's column range; if one such accumulator exceeds 2 GiB the call
- * returns NB200_E_NOMEM / NB200_E_UNSUPPORTED. */
+ * longer rows accumulate with float32 atomics (as the reference does for every row). Rows
+ * longer than 2048 products need a dense per-row accumulator over B's column range (4 bytes
+ * per column, up to 592 of them at once, 4 GiB in total); NB200_E_NOMEM if that cannot be had. */
 int nb200_spgemm_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int32_t num_blocks,
                      int32_t threads_per_block, void *stream);
 /* Two-step form for caller-owned memory: _symbolic fills c->row_ptr (rows + 1, caller-owned)

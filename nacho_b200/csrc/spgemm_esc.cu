@@ -11,11 +11,11 @@
 // keeps its products on chip:
 //   small   P_i <= 32     one warp per row: products in registers, bitonic sort by shuffles
 //   medium  P_i <= 2048   one CTA per row: products in shared memory, bitonic sort there
-//   long    P_i  > 2048   a dense accumulator per row (bitmap + float64 values over the column
-//                         range, L2 resident), filled with atomics, compacted by a bitmap scan
+//   long    P_i  > 2048   a dense accumulator per row (bitmap + float32 values over the column
+//                         range), filled with atomics, compacted by a bitmap scan
 // Two passes: symbolic (unique columns per row -> row offsets by a scan) and numeric (fill).
 // Small and medium rows sum equal-column products in expansion order (ascending j), a fixed
-// order; long rows sum in float64 with atomics.
+// order; long rows sum with float32 atomics, like the reference does for every row.
 #include <algorithm>
 #include <cstring>
 
@@ -28,7 +28,21 @@ namespace {
 constexpr int SMALL_P = 32;
 constexpr int MEDIUM_P = 2048;
 constexpr int MED_NT = 128;
-constexpr int LONG_NT = 1024;
+#ifndef ESC_LONG_NT
+#define ESC_LONG_NT 512
+#endif
+#ifndef ESC_LONG_SLOTS
+#define ESC_LONG_SLOTS (4 * 148)  // with 512 threads each: every SM fully occupied; the path is bound by atomic latency
+#endif
+constexpr int LONG_NT = ESC_LONG_NT;
+// Accumulator type of the long-row path: float32 atomics, as in the reference's compress step
+// (src/backend/stitch_and_generate_gpu.cpp:312-363); -DESC_ACC_DOUBLE switches to float64
+// (about 1.4x slower on configuration 4a).
+#ifdef ESC_ACC_DOUBLE
+typedef double acc_t;
+#else
+typedef float acc_t;
+#endif
 
 struct CsrView {
     const int32_t *rp;
@@ -233,7 +247,7 @@ __global__ void __launch_bounds__(MED_NT) k_esc_medium(CsrView A, CsrView B, con
 // Dense accumulator of one long row: a bit per column, and (numeric pass) a float64 per column.
 struct LongSlots {
     uint32_t *bitmap;  // slots x words
-    double *acc;       // slots x cols (numeric only)
+    acc_t *acc;        // slots x cols (numeric only)
     int32_t words;
     int32_t cols;
 };
@@ -249,7 +263,7 @@ __global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, cons
     __shared__ int scan_tmp[72];
     const int tid = threadIdx.x;
     uint32_t *bitmap = slots.bitmap + (size_t)blockIdx.x * slots.words;
-    double *acc = NUMERIC ? slots.acc + (size_t)blockIdx.x * slots.cols : nullptr;
+    acc_t *acc = NUMERIC ? slots.acc + (size_t)blockIdx.x * slots.cols : nullptr;
     for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
         const int32_t i = ld_nc(row_list + r);
         const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
@@ -260,7 +274,7 @@ __global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, cons
             for (int32_t q = b_lo + lane_id(); q < b_hi; q += 32) {
                 const uint32_t col = (uint32_t)ld_nc(B.col + q);
                 atomicOr(bitmap + (col >> 5), 1u << (col & 31u));
-                if (NUMERIC) atomicAdd(acc + col, (double)(a * ld_nc(B.val + q)));
+                if (NUMERIC) atomicAdd(acc + col, (acc_t)(a * ld_nc(B.val + q)));
             }
         }
         __syncthreads();
@@ -280,7 +294,7 @@ __global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, cons
                         bits &= bits - 1;
                         c_col[pos] = (int32_t)col;
                         c_val[pos] = (float)__ldcg(acc + col);
-                        acc[col] = 0.0;
+                        acc[col] = (acc_t)0;
                         ++pos;
                     }
                 }
@@ -308,8 +322,7 @@ int check_operand(const nb200_csr *m) {
     return NB200_OK;
 }
 
-// Accumulator slots are sized to stay resident in the 126 MB L2, where their atomics are served.
-constexpr size_t LONG_SLOT_BUDGET = size_t(96) << 20;
+constexpr size_t LONG_SLOT_BUDGET = size_t(4) << 30;  // bytes of accumulator slots per call
 
 struct EscPlan {
     Workspace *ws;
@@ -327,8 +340,8 @@ struct EscPlan {
 int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream_t stream, EscPlan *plan) {
     const int32_t rows = a->rows;
     const int32_t words = (b->cols + 31) / 32;
-    const size_t slot_bytes = (size_t)words * 4 + (numeric ? (size_t)b->cols * 8 : 0);
-    int max_slots = (int)std::min<size_t>(2 * 148, std::max<size_t>(1, LONG_SLOT_BUDGET / std::max<size_t>(slot_bytes, 1)));
+    const size_t slot_bytes = (size_t)words * 4 + (numeric ? (size_t)b->cols * sizeof(acc_t) : 0);
+    int max_slots = (int)std::min<size_t>(ESC_LONG_SLOTS, std::max<size_t>(1, LONG_SLOT_BUDGET / std::max<size_t>(slot_bytes, 1)));
     Carver sizes;
     sizes.take<int32_t>((size_t)rows);
     sizes.take<int32_t>((size_t)rows);
@@ -357,7 +370,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     plan->slots.words = words;
     plan->slots.cols = b->cols;
     plan->slots.bitmap = carve.take<uint32_t>((size_t)max_slots * words);
-    plan->slots.acc = numeric ? carve.take<double>((size_t)max_slots * b->cols) : nullptr;
+    plan->slots.acc = numeric ? carve.take<acc_t>((size_t)max_slots * b->cols) : nullptr;
     plan->n_slots = max_slots;
 
     NB200_CUDA(cudaMemsetAsync(plan->ctl, 0, sizeof(EscCtl), stream));
@@ -373,7 +386,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     if (plan->host.n_long > 0) {
         plan->n_slots = std::min(plan->n_slots, plan->host.n_long);
         NB200_CUDA(cudaMemsetAsync(plan->slots.bitmap, 0, (size_t)plan->n_slots * words * 4, stream));
-        if (numeric) NB200_CUDA(cudaMemsetAsync(plan->slots.acc, 0, (size_t)plan->n_slots * b->cols * 8, stream));
+        if (numeric) NB200_CUDA(cudaMemsetAsync(plan->slots.acc, 0, (size_t)plan->n_slots * b->cols * sizeof(acc_t), stream));
     }
     return NB200_OK;
 }
