@@ -44,14 +44,6 @@ namespace {
 #define CSR2_MIN_CTAS 3
 #endif
 constexpr int NT = CSR2_NT;
-// Profiling aid: building with -DCSR2_STOP_AFTER=k makes the fast tile body return after its
-// k-th phase (results are then wrong), so that instruction and shared-memory counters can be
-// attributed to phases by difference. Never defined in a normal build.
-#ifdef CSR2_STOP_AFTER
-#define CSR2_PHASE_END(k, keep) do { if (CSR2_STOP_AFTER == (k)) { if ((keep) == 0x7fff1234) ctl->total = (keep); return; } } while (0)
-#else
-#define CSR2_PHASE_END(k, keep) do { } while (0)
-#endif
 
 
 struct CsrIn {
@@ -499,7 +491,6 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         }
         return;
     }
-    CSR2_PHASE_END(1, (int)keys[tid]);
 
     if (scan_warp) {
         // ---- scan warp: the output base of the tile is the sum of the counts of all earlier
@@ -563,7 +554,6 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         }
     }
     WorkerBar::sync();
-    CSR2_PHASE_END(2, (int)keys[tid]);
 
     // ---- split the tile among threads: merge-path diagonal tid * VT (the operand bit makes
     // an A entry smaller than the B entry at the same position, so ties take A first)
@@ -578,7 +568,6 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         x0 = lo;
     }
     const int y0 = diag - x0;
-    CSR2_PHASE_END(3, x0);
     thread_rank[tid] = x0;  // borrowed to pass every thread's split to its left neighbour
     WorkerBar::sync();
     const int cnt = min(VT, n - diag);
@@ -634,7 +623,6 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         __threadfence_block();
         CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
     }
-    CSR2_PHASE_END(4, rank + (int)r[3]);
 
     // ---- compact columns and values of the survivors into the staging arrays
     {
@@ -655,13 +643,11 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
             yi += !tx;
         }
     }
-    CSR2_PHASE_END(6, out_col[tid]);
 
     // ---- output base of the tile
     if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
     const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
     if (base < 0) return;  // a bounded wait gave up; the host reports it
-    CSR2_PHASE_END(5, (int)base);
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
     // tile those are the survivors among the first d = (A entries before row r) + (B entries
