@@ -76,7 +76,20 @@ struct CompressCtl {
     int n_i, n_j;
 };
 
-constexpr int CVT = 8;  // entries per thread in the compress pass
+constexpr int CVT = 32;  // entries per thread in the compress pass (one bit each in the head masks)
+constexpr int CCH = 8;   // entries per load step: two 16-byte loads per coordinate array
+
+// Loads entries [p, p + CCH) of `z` (-1 beyond the end). p is a multiple of CCH, so the fast
+// path is two aligned 16-byte loads.
+__device__ __forceinline__ void load_chunk(const int32_t *__restrict__ z, int64_t p, int32_t nnz, int32_t (&out)[CCH]) {
+    if (p + CCH <= nnz) {
+        const int4 lo = __ldg(reinterpret_cast<const int4 *>(z + p)), hi = __ldg(reinterpret_cast<const int4 *>(z + p) + 1);
+        out[0] = lo.x, out[1] = lo.y, out[2] = lo.z, out[3] = lo.w, out[4] = hi.x, out[5] = hi.y, out[6] = hi.z, out[7] = hi.w;
+    } else {
+#pragma unroll
+        for (int q = 0; q < CCH; ++q) out[q] = p + q < nnz ? ld_nc(z + p + q) : -1;
+    }
+}
 
 // Head flags + packed scan + scatter. A tile's count is (new i's << 31 | new (i, j)'s).
 __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t *__restrict__ zi,
@@ -93,32 +106,26 @@ __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t 
     __syncthreads();
     const int t = s_tile;
     const int64_t p0 = ((int64_t)t * NT + tid) * CVT;
-    int32_t ci[CVT + 1], cj[CVT + 1];
-    ci[0] = p0 > 0 && p0 - 1 < nnz ? ld_nc(zi + p0 - 1) : -1;
-    cj[0] = p0 > 0 && p0 - 1 < nnz ? ld_nc(zj + p0 - 1) : -1;
-    if (p0 + CVT <= nnz) {  // the thread's 8 entries start on a 32-byte boundary: two 16-byte loads per array
-        static_assert(CVT == 8, "vector loads below assume 8 entries per thread");
-        const int4 i0 = __ldg(reinterpret_cast<const int4 *>(zi + p0)), i1 = __ldg(reinterpret_cast<const int4 *>(zi + p0) + 1);
-        const int4 j0 = __ldg(reinterpret_cast<const int4 *>(zj + p0)), j1 = __ldg(reinterpret_cast<const int4 *>(zj + p0) + 1);
-        ci[1] = i0.x, ci[2] = i0.y, ci[3] = i0.z, ci[4] = i0.w, ci[5] = i1.x, ci[6] = i1.y, ci[7] = i1.z, ci[8] = i1.w;
-        cj[1] = j0.x, cj[2] = j0.y, cj[3] = j0.z, cj[4] = j0.w, cj[5] = j1.x, cj[6] = j1.y, cj[7] = j1.z, cj[8] = j1.w;
-    } else {
-#pragma unroll
-        for (int q = 1; q <= CVT; ++q) {
-            const int64_t p = p0 - 1 + q;
-            const bool in = p < nnz;
-            ci[q] = in ? ld_nc(zi + p) : -1;
-            cj[q] = in ? ld_nc(zj + p) : -1;
-        }
-    }
     unsigned head_i = 0, head_ij = 0;
+    {
+        int32_t prev_i = p0 > 0 && p0 - 1 < nnz ? ld_nc(zi + p0 - 1) : -1;
+        int32_t prev_j = p0 > 0 && p0 - 1 < nnz ? ld_nc(zj + p0 - 1) : -1;
 #pragma unroll
-    for (int q = 0; q < CVT; ++q) {
-        const bool live = p0 + q < nnz;
-        const bool ni = live && ci[q + 1] != ci[q];
-        const bool nij = live && (ni || cj[q + 1] != cj[q]);
-        head_i |= (unsigned)ni << q;
-        head_ij |= (unsigned)nij << q;
+        for (int c = 0; c < CVT / CCH; ++c) {
+            int32_t ci[CCH], cj[CCH];
+            load_chunk(zi, p0 + c * CCH, nnz, ci);
+            load_chunk(zj, p0 + c * CCH, nnz, cj);
+#pragma unroll
+            for (int q = 0; q < CCH; ++q) {
+                const bool live = p0 + c * CCH + q < nnz;
+                const bool ni = live && ci[q] != prev_i;
+                const bool nij = live && (ni || cj[q] != prev_j);
+                head_i |= (unsigned)ni << (c * CCH + q);
+                head_ij |= (unsigned)nij << (c * CCH + q);
+                prev_i = ci[q];
+                prev_j = cj[q];
+            }
+        }
     }
     int tot_i, tot_ij;
     int rank_i = block_excl_sum<NT>(__popc(head_i), scan_tmp, tot_i);
@@ -134,21 +141,28 @@ __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t 
     int r = (int)(base >> 31) + rank_i;
     int f = (int)(base & 0x7fffffff) + rank_ij;
 #pragma unroll
-    for (int q = 0; q < CVT; ++q) {
-        const int64_t p = p0 + q;
-        if ((head_ij >> q) & 1u) {
-            if (f < cap_j) {
-                j_idx[f] = cj[q + 1];
-                k_ptr[f] = (int32_t)p;
-            }
-            if ((head_i >> q) & 1u) {
-                if (r < cap_i) {
-                    i_idx[r] = ci[q + 1];
-                    j_ptr[r] = f;
+    for (int c = 0; c < CVT / CCH; ++c) {
+        if (((head_ij >> (c * CCH)) & 0xffu) == 0) continue;  // no fibre starts in this chunk
+        int32_t ci[CCH], cj[CCH];
+        load_chunk(zi, p0 + c * CCH, nnz, ci);  // second read, from cache
+        load_chunk(zj, p0 + c * CCH, nnz, cj);
+#pragma unroll
+        for (int q = 0; q < CCH; ++q) {
+            const int bit = c * CCH + q;
+            if ((head_ij >> bit) & 1u) {
+                if (f < cap_j) {
+                    j_idx[f] = cj[q];
+                    k_ptr[f] = (int32_t)(p0 + bit);
                 }
-                ++r;
+                if ((head_i >> bit) & 1u) {
+                    if (r < cap_i) {
+                        i_idx[r] = ci[q];
+                        j_ptr[r] = f;
+                    }
+                    ++r;
+                }
+                ++f;
             }
-            ++f;
         }
     }
     if (t == (int)gridDim.x - 1 && tid == NT - 1) {  // last thread of the last tile holds the totals
