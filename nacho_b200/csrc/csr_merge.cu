@@ -421,10 +421,12 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     const int n = na + nb;
     const uint32_t cmask = (1u << cbits) - 1u;
 
-    uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw);
-    float *vals = reinterpret_cast<float *>(keys + P::SLOTS);
-    int32_t *out_col = reinterpret_cast<int32_t *>(keys);
-    float *out_val = reinterpret_cast<float *>(vals + P::SLOTS);
+    // layout: values | keys | extra words. The (column, value) staging pairs of the result
+    // reuse the keys (in registers by then) and run on into the extra words.
+    float *vals = reinterpret_cast<float *>(smem_raw);
+    uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw) + P::SLOTS;
+    uint2 *out_pair = reinterpret_cast<uint2 *>(keys);
+    static_assert(P::SLOTS % 2 == 0 && P::SLOTS + P::OUT >= 2 * P::OUT, "staging pairs must fit keys + extra words, 8-byte aligned");
 
     const int32_t *ga_col = A.col + a0, *gb_col = B.col + b0;
     const float *ga_val = A.val + a0, *gb_val = B.val + b0;
@@ -595,7 +597,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     unsigned from_a = 0, same = 0;
 #pragma unroll
     for (int i = 0; i < VT; ++i) {
-        from_a |= (unsigned)((r[i] & 1u) == 0u) << i;
+        from_a |= (~r[i] & 1u) << i;
         same |= (unsigned)((r[i] ^ r[i + 1]) == 1u) << i;
     }
     const unsigned live = (1u << cnt) - 1u;
@@ -624,23 +626,27 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
     }
 
-    // ---- compact columns and values of the survivors into the staging arrays
+    // ---- compact (column, value) pairs of the survivors into the staging array. Entry i of the
+    // thread came from A iff its key's operand bit is clear; its value sits at A's start + (A
+    // entries before it) or B's start + (B entries before it), and an A entry's twin is the
+    // next B entry.
     {
-        int o = rank, xi = x0, yi = y0;
+        const float *pa = vals + oa + x0, *pb = vals + obv + y0;
+        uint2 *po = out_pair + rank;
+        int ca = 0;  // A entries among the thread's first i entries
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
-            const bool tx = (from_a >> i) & 1u;
-            const bool both = (twin >> i) & 1u;
-            const bool out = (emit >> i) & 1u;
-            float v = vals[tx ? oa + xi : obv + yi];
-            if (both) v = OP == OP_UNION ? v + vy[yi] : v * vy[yi];
-            if (out) {
-                out_col[o] = (int32_t)((r[i] >> 1) & cmask);
-                out_val[o] = v;
+            const bool tx = (r[i] & 1u) == 0u;
+            float v = *(tx ? pa + ca : pb + (i - ca));
+            if ((twin >> i) & 1u) {  // an A entry whose twin is the next B entry
+                const float vb = pb[i - ca];
+                v = OP == OP_UNION ? v + vb : v * vb;
             }
-            o += out;
-            xi += tx;
-            yi += !tx;
+            if ((emit >> i) & 1u) {
+                *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(v));
+                ++po;
+            }
+            ca += tx;
         }
     }
 
@@ -667,8 +673,9 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     int32_t *gz_col = Z.col + base;
     float *gz_val = Z.val + base;
     for (int i = tid; i < total; i += NT) {
-        gz_col[i] = out_col[i];
-        gz_val[i] = out_val[i];
+        const uint2 p = out_pair[i];
+        gz_col[i] = (int32_t)p.x;
+        gz_val[i] = __uint_as_float(p.y);
     }
 }
 

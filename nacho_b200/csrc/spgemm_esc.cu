@@ -107,9 +107,24 @@ __device__ __forceinline__ uint64_t warp_bitonic_sort(uint64_t key) {
     return key;
 }
 
+__device__ __forceinline__ uint32_t warp_bitonic_sort32(uint32_t key) {
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const uint32_t other = __shfl_xor_sync(FULL_MASK, key, j);
+            const bool take_min = ((lane_id() & k) == 0) == ((lane_id() & j) == 0);
+            key = take_min ? min(key, other) : max(key, other);
+        }
+    }
+    return key;
+}
+
 // One warp per row with at most 32 products. Lane l holds product l of the row's expansion
 // order; the sort key is (column << 32 | l), so equal columns stay in expansion order.
-template <bool NUMERIC>
+// NARROW: B has fewer than 2^27 columns, so (column << 5 | lane) fits 32 bits and the sort
+// moves half as much through the shuffles.
+template <bool NUMERIC, bool NARROW>
 __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const int32_t *__restrict__ row_list, int n_rows,
                                                    int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
                                                    int32_t *__restrict__ c_col, float *__restrict__ c_val) {
@@ -132,11 +147,22 @@ __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const i
         }
         base += len;
     }
-    uint64_t key = have ? (((uint64_t)my_col << 32) | (uint32_t)lane) : ~0ull;
-    key = warp_bitonic_sort(key);
-    const uint32_t col = (uint32_t)(key >> 32);
-    const int src = (int)(key & 31u);
-    const bool valid = key != ~0ull;
+    uint32_t col;
+    int src;
+    bool valid;
+    if (NARROW) {
+        uint32_t key = have ? ((my_col << 5) | (uint32_t)lane) : ~0u;
+        key = warp_bitonic_sort32(key);
+        col = key >> 5;
+        src = (int)(key & 31u);
+        valid = key != ~0u;
+    } else {
+        uint64_t key = have ? (((uint64_t)my_col << 32) | (uint32_t)lane) : ~0ull;
+        key = warp_bitonic_sort(key);
+        col = (uint32_t)(key >> 32);
+        src = (int)(key & 31u);
+        valid = key != ~0ull;
+    }
     const uint32_t prev_col = __shfl_up_sync(FULL_MASK, col, 1);
     const bool head = valid && (lane == 0 || prev_col != col);
     const unsigned heads = __ballot_sync(FULL_MASK, head);
@@ -401,7 +427,10 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
     if (plan.host.n_small > 0) {
         LaunchScope scope(NUMERIC ? "esc_small_numeric" : "esc_small_symbolic", stream);
         const int warps = plan.host.n_small;
-        k_esc_small<NUMERIC><<<(warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
+        if (b->cols < (1 << 27))
+            k_esc_small<NUMERIC, true><<<(warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
+        else
+            k_esc_small<NUMERIC, false><<<(warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
         NB200_CUDA(cudaGetLastError());
     }
     if (plan.host.n_medium > 0) {

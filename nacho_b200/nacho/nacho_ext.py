@@ -46,16 +46,17 @@ class CSR_gpu:
     """CSR matrix on the GPU: ``CSR_gpu(dim_j_offsets, dim_j_indices, values, shape)``
     (attribute names as emitted by src/backend/generate_bindings.cpp:84-154)."""
 
-    __slots__ = ("_offsets", "_indices", "_values", "_shape")
+    __slots__ = ("_offsets", "_indices", "_values", "_shape", "_rows", "_cols")
 
     def __init__(self, dim_j_offsets, dim_j_indices, values, shape):
         self._offsets = _dev_array(dim_j_offsets, torch.int32, "dim_j_offsets")
         self._indices = _dev_array(dim_j_indices, torch.int32, "dim_j_indices")
         self._values = _dev_array(values, torch.float32, "values")
         self._shape = _shape_array(shape, 2)
+        self._rows, self._cols = (int(x) for x in self._shape)
         if self._indices.numel() != self._values.numel():
             raise ValueError("dim_j_indices and values differ in length")
-        if self._offsets.numel() != int(self._shape[0]) + 1:
+        if self._offsets.numel() != self._rows + 1:
             raise ValueError("dim_j_offsets must hold rows + 1 entries")
         if not (self._offsets.device == self._indices.device == self._values.device):
             raise ValueError("all buffers of a tensor must live on one device")
@@ -70,11 +71,11 @@ class CSR_gpu:
         return self._values.device
 
     def _struct(self) -> CsrStruct:
-        return CsrStruct(int(self._shape[0]), int(self._shape[1]), self._values.numel(),
+        return CsrStruct(self._rows, self._cols, self._values.numel(),
                          self._offsets.data_ptr(), self._indices.data_ptr(), self._values.data_ptr())
 
     def __repr__(self):
-        return f"CSR_gpu(shape=({int(self._shape[0])}, {int(self._shape[1])}), nnz={self._values.numel()})"
+        return f"CSR_gpu(shape=({self._rows}, {self._cols}), nnz={self._values.numel()})"
 
 
 def _same_device(*tensors):
