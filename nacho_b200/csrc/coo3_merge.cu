@@ -162,13 +162,12 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
     const bool scan_warp = tid >= NT;  // one extra warp: it only turns counts into output bases
     int t = blockIdx.x;
     if (tid == 0) {
-        // number tiles in the order CTAs start, so a tile only waits on running CTAs
-        if (MODE == MODE_FUSED) s_tile = atomicAdd(&ctl->ticket, 1);
         mbar_init(&mbar, 1);
         mbar_fence_init();
     }
     __syncthreads();
-    if (MODE == MODE_FUSED) t = s_tile;
+    // tiles are numbered by CTA index: CTAs are dispatched in increasing index order, so a tile
+    // only waits on CTAs dispatched before it (and every such wait is bounded)
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
     const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
     const int n = na + nb;

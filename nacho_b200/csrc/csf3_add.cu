@@ -102,9 +102,7 @@ __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t 
     __shared__ long long s_base;
     volatile uint64_t *tile_state = tile_state_raw;
     const int tid = threadIdx.x;
-    if (tid == 0) s_tile = atomicAdd(&ctl->ticket, 1);
-    __syncthreads();
-    const int t = s_tile;
+    const int t = blockIdx.x;  // CTAs are dispatched in index order; waits on earlier tiles are bounded
     const int64_t p0 = ((int64_t)t * NT + tid) * CVT;
     unsigned head_i = 0, head_ij = 0;
     {

@@ -688,15 +688,21 @@ __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, C
     __shared__ unsigned thread_emit[NT];
     __shared__ __align__(8) uint64_t mbar;
     __shared__ int s_tile;
+    // Tiles are numbered by CTA index: CTAs are dispatched in increasing index order, so a tile
+    // only ever waits on CTAs that were dispatched before it (and every such wait is bounded).
+    // Set CSR2_TICKET to number tiles with an atomic ticket taken at CTA start instead.
     int t = blockIdx.x;
     if (threadIdx.x == 0) {
-        // number tiles in the order CTAs start, so a tile only waits on running CTAs
+#ifdef CSR2_TICKET
         if (MODE == MODE_FUSED) s_tile = atomicAdd(&ctl->ticket, 1);
+#endif
         mbar_init(&mbar, 1);
         mbar_fence_init();
     }
     __syncthreads();
+#ifdef CSR2_TICKET
     if (MODE == MODE_FUSED) t = s_tile;
+#endif
     // 32-bit composite keys hold ((row in tile << cbits | column) << 1 | operand) when that
     // fits; tiles that span too many rows for that (long runs of empty rows) use 64-bit keys.
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;

@@ -75,9 +75,7 @@ static __global__ void __launch_bounds__(SCAN_NT) k_scan_lookback(int32_t *data,
     __shared__ long long s_base;
     volatile uint64_t *state = state_raw;
     const int tid = threadIdx.x;
-    if (tid == 0) s_tile = atomicAdd(&ctl->ticket, 1);
-    __syncthreads();
-    const int t = s_tile;
+    const int t = blockIdx.x;  // CTAs are dispatched in index order; waits on earlier tiles are bounded
     const int64_t p0 = ((int64_t)t * SCAN_NT + tid) * SCAN_VT;
     int v[SCAN_VT];
     int mine = 0;
