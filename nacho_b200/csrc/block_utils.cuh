@@ -135,8 +135,9 @@ __device__ __forceinline__ int64_t warp_count_true(int64_t lo, int64_t hi, Pred 
 // soon as it knows it, then walks back over its predecessors' words, 32 at a time, adding
 // aggregates until it meets a tile that already knows its inclusive prefix. A word carries a
 // 2-bit state and a 62-bit value and is written with one 8-byte store, so no fence is needed
-// between the two. Tiles must be numbered in the order their CTAs start (take the number from
-// an atomic ticket) so that a tile only ever waits on CTAs that are already running.
+// between the two. A tile waits only on tiles with lower numbers, so tiles must be numbered in
+// an order in which their CTAs start: the CTA index (the hardware hands CTAs out in index
+// order, the numbering the kernels here use) or an atomic ticket taken at CTA start.
 //
 // Every wait is bounded: after LOOKBACK_POLL_LIMIT polls of one word the walk gives up,
 // records the tile in `status` and returns -1; the caller then skips its writes. The tile
