@@ -59,6 +59,37 @@ __device__ __forceinline__ int block_excl_sum(int v, int *tmp, int &total) {
     return tmp[warp_id()] + incl - v;
 }
 
+// Two exclusive sums at once (va, vb) over the first NT threads; `ta` / `tb` receive the totals.
+// `tmp` is >= 66 ints of shared memory.
+template <int NT, typename Bar = WholeCta>
+__device__ __forceinline__ void block_excl_sum2(int va, int vb, int *tmp, int &ea, int &eb, int &ta, int &tb) {
+    constexpr int NW = NT / 32;
+    const int ia = warp_incl_sum(va), ib = warp_incl_sum(vb);
+    Bar::sync();
+    if (lane_id() == 31) {
+        tmp[warp_id()] = ia;
+        tmp[33 + warp_id()] = ib;
+    }
+    Bar::sync();
+    if (warp_id() == 0) {
+        const int wa = lane_id() < NW ? tmp[lane_id()] : 0, wb = lane_id() < NW ? tmp[33 + lane_id()] : 0;
+        const int sa = warp_incl_sum(wa), sb = warp_incl_sum(wb);
+        if (lane_id() < NW) {
+            tmp[lane_id()] = sa - wa;
+            tmp[33 + lane_id()] = sb - wb;
+        }
+        if (lane_id() == NW - 1) {
+            tmp[32] = sa;
+            tmp[65] = sb;
+        }
+    }
+    Bar::sync();
+    ta = tmp[32];
+    tb = tmp[65];
+    ea = tmp[warp_id()] + ia - va;
+    eb = tmp[33 + warp_id()] + ib - vb;
+}
+
 // Exclusive running maximum over the CTA for two independent sequences at once (va, vb).
 // `tmp` is >= 64 unsigned of shared memory.
 template <int NT, typename Bar = WholeCta>
@@ -156,6 +187,16 @@ __device__ __forceinline__ uint64_t ld_relaxed_gpu(const volatile uint64_t *p) {
 
 __device__ __forceinline__ void st_relaxed_gpu(volatile uint64_t *p, uint64_t v) {
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ int ld_relaxed_gpu_i32(const int *p) {
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_relaxed_gpu_i32(int *p, int v) {
+    asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Called by all 32 lanes of one warp. Returns the sum of the aggregates of tiles [0, t).

@@ -71,7 +71,6 @@ constexpr int SCAN_NT = 256, SCAN_VT = 8;
 
 static __global__ void __launch_bounds__(SCAN_NT) k_scan_lookback(int32_t *data, int32_t n, uint64_t *state_raw, FusedCtl *ctl) {
     __shared__ int scan_tmp[40];
-    __shared__ int s_tile;
     __shared__ long long s_base;
     volatile uint64_t *state = state_raw;
     const int tid = threadIdx.x;

@@ -11,12 +11,16 @@
 // keeps its products on chip:
 //   small   P_i <= 32     one warp per row: products in registers, bitonic sort by shuffles
 //   medium  P_i <= 2048   one CTA per row: products in shared memory, bitonic sort there
-//   long    P_i  > 2048   a dense accumulator per row (bitmap + float32 values over the column
-//                         range), filled with atomics, compacted by a bitmap scan
+//   long    P_i  > 2048   a dense accumulator per row in global memory (bitmap + float32 values
+//                         over the column range), filled with atomics, compacted by a bitmap scan
+//   huge    P_i  > 1024 per window of 16384 columns: the row is cut into column windows and
+//                         each (row, window) unit accumulates in shared memory (float32 atomics
+//                         there), so the products of the heaviest rows never reach L2 or HBM
 // Two passes: symbolic (unique columns per row -> row offsets by a scan) and numeric (fill).
 // Small and medium rows sum equal-column products in expansion order (ascending j), a fixed
-// order; long rows sum with float32 atomics, like the reference does for every row.
+// order; long and huge rows sum with float32 atomics, like the reference does for every row.
 #include <algorithm>
+#include <climits>
 #include <cstring>
 
 #include "merge_common.cuh"
@@ -54,17 +58,22 @@ struct CsrView {
 struct EscCtl {
     unsigned long long products;
     int n_small, n_medium, n_long;
+    int n_giant, n_huge;  // huge rows with more / at most GIANT_P products
     int pad;
 };
 
+// huge_rows holds the giant rows from its front and the other huge rows from its back, so
+// that the heaviest units are handed out first.
 struct RowLists {
-    int32_t *small_rows, *medium_rows, *long_rows;
+    int32_t *small_rows, *medium_rows, *long_rows, *huge_rows;
 };
+
+constexpr unsigned long long GIANT_P = 1ull << 20;
 
 // Expand phase 1 (src/backend/compute.cpp:541-611): per-row product counts, and the bins.
 // Rows without products get their count (0) written here.
 __global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32_t rows, int32_t *__restrict__ row_count,
-                                                     RowLists lists, EscCtl *ctl) {
+                                                     RowLists lists, unsigned long long huge_p, EscCtl *ctl) {
     const int i = blockIdx.x * 256 + threadIdx.x;
     unsigned long long p = 0;
     if (i < rows) {
@@ -79,8 +88,13 @@ __global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32
             lists.small_rows[atomicAdd(&ctl->n_small, 1)] = i;
         } else if (p <= MEDIUM_P) {
             lists.medium_rows[atomicAdd(&ctl->n_medium, 1)] = i;
-        } else {
+        } else if (p <= huge_p) {
             lists.long_rows[atomicAdd(&ctl->n_long, 1)] = i;
+        } else {
+            if (p > GIANT_P)
+                lists.huge_rows[atomicAdd(&ctl->n_giant, 1)] = i;
+            else
+                lists.huge_rows[rows - 1 - atomicAdd(&ctl->n_huge, 1)] = i;
         }
     }
     // one atomic per warp for the product total
@@ -332,6 +346,226 @@ __global__ void __launch_bounds__(LONG_NT) k_esc_long(CsrView A, CsrView B, cons
     }
 }
 
+// -------------------------------------------------------------------------- huge rows ----
+
+constexpr int WIN_NT = 512;
+constexpr int WIN_BYTES = 64 * 1024;                // shared-memory accumulator of one window
+constexpr int WIN_COLS_NUMERIC = WIN_BYTES / 4;     // float32 sums: 16384 columns per window
+constexpr int WIN_COLS_SYMBOLIC = WIN_BYTES;        // flag bytes: 65536 columns per window
+constexpr int WIN_MAX_WINDOWS = 256;                // wider matrices keep every long row on the global accumulator
+constexpr size_t WIN_PTR_BUDGET = size_t(1) << 30;  // bytes of the window pointer table
+#ifndef ESC_WIN_P
+#define ESC_WIN_P 1024                              // a row is huge when it has more products than this per window
+#endif
+#ifndef ESC_WIN_ITEMS
+#define ESC_WIN_ITEMS 4                             // 32-product blocks a warp keeps in flight
+#endif
+constexpr uint32_t NEG_ZERO_BITS = 0x80000000u;
+
+// Window pointer table of B: ptr[j * (n_win + 1) + w] = first position of row j whose column is
+// >= w * win_cols (w = 0 .. n_win), so that window w of row j is [ptr[w], ptr[w + 1]).
+__global__ void __launch_bounds__(256) k_esc_window_ptr(CsrView B, int32_t b_rows, int n_win, int win_cols, int32_t *__restrict__ ptr) {
+    const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int per = n_win + 1;
+    if (t >= (int64_t)b_rows * per) return;
+    const int32_t j = (int32_t)(t / per);
+    const int w = (int)(t - (int64_t)j * per);
+    int32_t lo = ld_nc(B.rp + j), hi = ld_nc(B.rp + j + 1);
+    if (w == n_win) {
+        lo = hi;
+    } else if (w > 0) {
+        const int32_t key = w * win_cols;
+        while (lo < hi) {
+            const int32_t mid = lo + ((hi - lo) >> 1);
+            if (ld_nc(B.col + mid) < key)
+                lo = mid + 1;
+            else
+                hi = mid;
+        }
+    }
+    ptr[t] = lo;
+}
+
+// Persistent CTAs take huge rows from a ticket and walk the row's column windows in order. In
+// window w every entry (i, j) of the row contributes the slice [ptr[j][w], ptr[j][w + 1]) of B's
+// row j; the non-empty slices of up to WIN_NT entries form one flat product range that the warps
+// walk ESC_WIN_ITEMS x 32 products at a time, accumulating into shared memory. The window is
+// then read off in column order behind the row's earlier windows.
+//
+// Numeric: the sums start at -0.0f and every product is added as (product + 0.0f), which is
+// never -0.0f, so a word that still holds -0.0f was not touched and no separate flag is needed
+// (-0.0f + x == x for every x that is not -0.0f). Symbolic: one flag byte per column, plain
+// stores, four times as many columns per window.
+template <bool NUMERIC>
+__global__ void __launch_bounds__(WIN_NT, 2)
+    k_esc_window(CsrView A, CsrView B, const int32_t *__restrict__ win_ptr, const int32_t *__restrict__ huge_rows, int32_t rows,
+                 int n_giant, int n_rows, int n_win, int *ticket, int32_t *__restrict__ row_count,
+                 const int32_t *__restrict__ c_rp, int32_t *__restrict__ c_col, float *__restrict__ c_val) {
+    constexpr int WCOLS = NUMERIC ? WIN_COLS_NUMERIC : WIN_COLS_SYMBOLIC;
+    extern __shared__ __align__(16) unsigned char win_smem[];
+    float *acc = reinterpret_cast<float *>(win_smem);
+    unsigned char *flags = win_smem;
+    __shared__ int seg_off[WIN_NT + 1];
+    __shared__ int seg_start[WIN_NT];
+    __shared__ float seg_a[NUMERIC ? WIN_NT : 1];
+    __shared__ int scan_tmp[72];
+    __shared__ int s_row;
+    const int tid = threadIdx.x;
+    const int per = n_win + 1;
+
+    if (NUMERIC) {
+        for (int c = tid; c < WCOLS; c += WIN_NT) acc[c] = __uint_as_float(NEG_ZERO_BITS);
+    } else {
+        for (int c = tid; c < WIN_BYTES / 16; c += WIN_NT) reinterpret_cast<uint4 *>(flags)[c] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    for (;;) {
+        __syncthreads();  // the previous row is fully read off; s_row may be overwritten
+        if (tid == 0) s_row = atomicAdd(ticket, 1);
+        __syncthreads();
+        const int r = s_row;
+        if (r >= n_rows) break;
+        const int32_t i = ld_nc(huge_rows + (r < n_giant ? r : rows - 1 - (r - n_giant)));
+        const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
+        const bool one_chunk = hi - lo <= WIN_NT;  // then every thread keeps its entry across the windows
+        int64_t my_ptr = -1;
+        float my_a = 0.f;
+        if (one_chunk && lo + tid < hi) {
+            my_ptr = (int64_t)ld_nc(A.col + lo + tid) * per;
+            if (NUMERIC) my_a = ld_nc(A.val + lo + tid);
+        }
+        int64_t out = NUMERIC ? (int64_t)ld_nc(c_rp + i) : 0;  // next free position of the row (count so far, symbolic)
+
+        for (int w = 0; w < n_win; ++w) {
+            bool any = false;
+            for (int32_t chunk = lo; chunk < hi; chunk += WIN_NT) {
+                int32_t s = 0, len = 0;
+                float a = my_a;
+                int64_t pp = my_ptr;
+                if (!one_chunk) {
+                    pp = -1;
+                    if (chunk + tid < hi) {
+                        pp = (int64_t)ld_nc(A.col + chunk + tid) * per;
+                        if (NUMERIC) a = ld_nc(A.val + chunk + tid);
+                    }
+                }
+                if (pp >= 0) {
+                    s = ld_nc(win_ptr + pp + w);
+                    len = ld_nc(win_ptr + pp + w + 1) - s;
+                }
+                int k_idx, off, n_seg, total;
+                block_excl_sum2<WIN_NT>(len > 0 ? 1 : 0, len, scan_tmp, k_idx, off, n_seg, total);
+                if (total == 0) continue;  // uniform; the scan synchronises before it reuses scan_tmp
+                any = true;
+                if (len > 0) {
+                    seg_off[k_idx] = off;
+                    seg_start[k_idx] = s;
+                    if (NUMERIC) seg_a[k_idx] = a;
+                }
+                if (tid == 0) seg_off[n_seg] = total;
+                __syncthreads();
+                int k = 0;  // segment holding the warp's current 32-product block (warp-uniform)
+                for (int p0 = warp_id() * (32 * ESC_WIN_ITEMS); p0 < total; p0 += WIN_NT * ESC_WIN_ITEMS) {
+                    int32_t q[ESC_WIN_ITEMS];
+                    float av[ESC_WIN_ITEMS];
+#pragma unroll
+                    for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
+                        const int pb = p0 + 32 * it;
+                        q[it] = -1;
+                        av[it] = 0.f;
+                        if (pb < total) {
+                            const int probe = k + 1 + lane_id();
+                            const unsigned ahead = __ballot_sync(FULL_MASK, probe < n_seg && seg_off[probe] <= pb);
+                            if (ahead == FULL_MASK) {
+                                int l = k + 32, h = n_seg - 1;
+                                while (l < h) {
+                                    const int mid = (l + h + 1) >> 1;
+                                    if (seg_off[mid] <= pb)
+                                        l = mid;
+                                    else
+                                        h = mid - 1;
+                                }
+                                k = l;
+                            } else {
+                                k += __popc(ahead);
+                            }
+                            const int p = pb + lane_id();
+                            if (p < total) {
+                                int kk = k;
+                                while (seg_off[kk + 1] <= p) ++kk;  // ends: seg_off[n_seg] == total > p
+                                q[it] = seg_start[kk] + (p - seg_off[kk]);
+                                if (NUMERIC) av[it] = seg_a[kk];
+                            }
+                        }
+                    }
+                    int32_t c[ESC_WIN_ITEMS];
+                    float bv[ESC_WIN_ITEMS];
+#pragma unroll
+                    for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
+                        c[it] = q[it] >= 0 ? ld_nc(B.col + q[it]) : 0;
+                        bv[it] = NUMERIC && q[it] >= 0 ? ld_nc(B.val + q[it]) : 0.f;
+                    }
+#pragma unroll
+                    for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
+                        if (q[it] >= 0) {
+                            const int32_t cw = c[it] - w * WCOLS;
+                            if (NUMERIC)
+                                atomicAdd(acc + cw, __fadd_rn(av[it] * bv[it], 0.0f));
+                            else
+                                flags[cw] = 1;
+                        }
+                    }
+                }
+                __syncthreads();  // the segment arrays are rewritten by the next chunk
+            }
+            if (!any) continue;  // uniform
+
+            if (!NUMERIC) {
+                uint4 *f4 = reinterpret_cast<uint4 *>(flags);
+                int mine = 0;
+#pragma unroll
+                for (int k = 0; k < WIN_BYTES / 16 / WIN_NT; ++k) {
+                    const uint4 x = f4[k * WIN_NT + tid];
+                    const int n = __popc(x.x) + __popc(x.y) + __popc(x.z) + __popc(x.w);
+                    if (n) f4[k * WIN_NT + tid] = make_uint4(0u, 0u, 0u, 0u);
+                    mine += n;
+                }
+                int cnt;
+                block_excl_sum<WIN_NT>(mine, scan_tmp, cnt);
+                out += cnt;
+                continue;
+            }
+
+            // numeric read-off: thread t looks after columns [32 t, 32 t + 32) of the window; the
+            // rotation by t keeps the 32 lanes of a warp on 32 different banks
+            uint32_t mask = 0u;
+            const int wbase = tid * 32;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                const int idx = (k + tid) & 31;
+                if (__float_as_uint(acc[wbase + idx]) != NEG_ZERO_BITS) mask |= 1u << idx;
+            }
+            int cnt;
+            const int rank = block_excl_sum<WIN_NT>(__popc(mask), scan_tmp, cnt);
+            if (mask) {
+                const int64_t first = out + rank;
+                const int32_t col0 = w * WCOLS + wbase;
+#pragma unroll
+                for (int k = 0; k < 32; ++k) {
+                    const int idx = (k + tid) & 31;
+                    if ((mask >> idx) & 1u) {
+                        const int64_t pos = first + __popc(mask & ((1u << idx) - 1u));
+                        c_col[pos] = col0 + idx;
+                        c_val[pos] = acc[wbase + idx];
+                        acc[wbase + idx] = __uint_as_float(NEG_ZERO_BITS);
+                    }
+                }
+            }
+            out += cnt;
+        }
+        if (!NUMERIC && tid == 0) row_count[i] = (int32_t)out;
+    }
+}
+
 // Turns the exclusive prefix of the per-row counts into row offsets (rows + 1 entries).
 __global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restrict__ excl, const long long *__restrict__ total,
                                                          int32_t rows, int32_t *__restrict__ c_rp) {
@@ -359,8 +593,21 @@ struct EscPlan {
     EscCtl *ctl;
     LongSlots slots;
     int n_slots;
+    int n_win;    // column windows per huge row (0: the window path is off for this B)
     EscCtl host;  // counters read back after the row-work kernel
 };
+
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
 
 // Bins the rows (kernel + one read-back) and carves the scratch of one pass.
 int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream_t stream, EscPlan *plan) {
@@ -369,9 +616,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     const size_t slot_bytes = (size_t)words * 4 + (numeric ? (size_t)b->cols * sizeof(acc_t) : 0);
     int max_slots = (int)std::min<size_t>(ESC_LONG_SLOTS, std::max<size_t>(1, LONG_SLOT_BUDGET / std::max<size_t>(slot_bytes, 1)));
     Carver sizes;
-    sizes.take<int32_t>((size_t)rows);
-    sizes.take<int32_t>((size_t)rows);
-    sizes.take<int32_t>((size_t)rows);
+    for (int q = 0; q < 4; ++q) sizes.take<int32_t>((size_t)rows);
     sizes.take<int32_t>((size_t)rows + 1);
     const int scan_ctas = (rows + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT);
     sizes.take<uint64_t>((size_t)scan_ctas + 8);
@@ -389,6 +634,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     plan->lists.small_rows = carve.take<int32_t>((size_t)rows);
     plan->lists.medium_rows = carve.take<int32_t>((size_t)rows);
     plan->lists.long_rows = carve.take<int32_t>((size_t)rows);
+    plan->lists.huge_rows = carve.take<int32_t>((size_t)rows);
     plan->row_count = carve.take<int32_t>((size_t)rows + 1);
     plan->scan_block = carve.take<uint64_t>((size_t)scan_ctas + 8);
     plan->scan_ctas = scan_ctas;
@@ -398,12 +644,17 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     plan->slots.bitmap = carve.take<uint32_t>((size_t)max_slots * words);
     plan->slots.acc = numeric ? carve.take<acc_t>((size_t)max_slots * b->cols) : nullptr;
     plan->n_slots = max_slots;
+    const int win_cols = numeric ? WIN_COLS_NUMERIC : WIN_COLS_SYMBOLIC;
+    const int64_t n_win = std::max<int64_t>(1, ((int64_t)b->cols + win_cols - 1) / win_cols);
+    const bool windows_on = n_win <= WIN_MAX_WINDOWS && (size_t)b->rows * (size_t)(n_win + 1) * 4 <= WIN_PTR_BUDGET;
+    plan->n_win = windows_on ? (int)n_win : 0;
+    const unsigned long long huge_p = plan->n_win ? (unsigned long long)ESC_WIN_P * (unsigned long long)plan->n_win : ULLONG_MAX;
 
     NB200_CUDA(cudaMemsetAsync(plan->ctl, 0, sizeof(EscCtl), stream));
     const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val};
     if (rows > 0) {
         LaunchScope scope("esc_rowwork", stream);
-        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, numeric ? nullptr : plan->row_count, plan->lists, plan->ctl);
+        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, numeric ? nullptr : plan->row_count, plan->lists, huge_p, plan->ctl);
         NB200_CUDA(cudaGetLastError());
     }
     NB200_CUDA(cudaMemcpyAsync(plan->ws->host, plan->ctl, sizeof(EscCtl), cudaMemcpyDeviceToHost, stream));
@@ -442,6 +693,38 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
         LaunchScope scope(NUMERIC ? "esc_long_numeric" : "esc_long_symbolic", stream);
         k_esc_long<NUMERIC><<<plan.n_slots, LONG_NT, 0, stream>>>(A, B, plan.lists.long_rows, plan.host.n_long, plan.slots, count, c_rp,
                                                                  c_col, c_val);
+        NB200_CUDA(cudaGetLastError());
+    }
+    const int64_t n_huge = (int64_t)plan.host.n_giant + plan.host.n_huge;
+    if (n_huge > 0) {
+        constexpr int WCOLS = NUMERIC ? WIN_COLS_NUMERIC : WIN_COLS_SYMBOLIC;
+        const int64_t ptr_entries = (int64_t)b->rows * (plan.n_win + 1);
+        Carver sizes;
+        sizes.take<int>(1);
+        sizes.take<int32_t>((size_t)ptr_entries);
+        Workspace *ws = nullptr;
+        int st;
+        if ((st = acquire_workspace(stream, sizes.used(), &ws, 3))) return st;
+        Carver carve(ws->dev);
+        int *ticket = carve.take<int>(1);
+        int32_t *win_ptr = carve.take<int32_t>((size_t)ptr_entries);
+        NB200_CUDA(cudaMemsetAsync(ticket, 0, sizeof(int), stream));
+        {
+            LaunchScope scope("esc_window_ptr", stream);
+            k_esc_window_ptr<<<(unsigned)((ptr_entries + 255) / 256), 256, 0, stream>>>(B, b->rows, plan.n_win, WCOLS, win_ptr);
+            NB200_CUDA(cudaGetLastError());
+        }
+        static bool attr_set[2] = {false, false};
+        if (!attr_set[NUMERIC]) {
+            NB200_CUDA(cudaFuncSetAttribute(k_esc_window<NUMERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, WIN_BYTES));
+            attr_set[NUMERIC] = true;
+        }
+        int per_sm = 0;
+        NB200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_esc_window<NUMERIC>, WIN_NT, WIN_BYTES));
+        const int grid = (int)std::min<int64_t>(n_huge, (int64_t)sm_count() * std::max(per_sm, 1));
+        LaunchScope scope(NUMERIC ? "esc_window_numeric" : "esc_window_symbolic", stream);
+        k_esc_window<NUMERIC><<<grid, WIN_NT, WIN_BYTES, stream>>>(A, B, win_ptr, plan.lists.huge_rows, a->rows, plan.host.n_giant, (int)n_huge,
+                                                                  plan.n_win, ticket, count, c_rp, c_col, c_val);
         NB200_CUDA(cudaGetLastError());
     }
     return NB200_OK;

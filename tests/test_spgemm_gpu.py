@@ -85,6 +85,45 @@ def test_medium_and_long_rows(nacho, oracle):
     check(nacho, oracle, a, b)
 
 
+def test_long_huge_and_giant_rows(nacho, oracle):
+    """100000 columns = 7 windows of 16384: rows of 2049 .. 7168 products stay on the global
+    accumulator, heavier rows go through the shared-memory windows, one row has more than 2^20
+    products. A row of explicit zeros against negative values makes every product -0.0: its
+    entries must still be stored (as 0.0 sums)."""
+    from nacho_b200 import synth
+    rng = np.random.default_rng(11)
+    rows, inner, cols = 48, 3000, 100_000
+    tb = synth.random_csr(inner, cols, 0.005, 12)          # about 500 entries per row of B
+    lens = rng.integers(0, 4, rows)
+    lens[3], lens[4], lens[5] = 6, 9, 13                   # long: about 3000 / 4500 / 6500 products
+    lens[8], lens[9], lens[10] = 20, 64, 700               # huge
+    lens[11] = 600                                         # huge, all-zero values
+    lens[20] = 2600                                        # giant: about 1.3 M products
+    rp = np.zeros(rows + 1, np.int32)
+    rp[1:] = np.cumsum(lens)
+    col = np.concatenate([np.sort(rng.choice(inner, int(n), replace=False)) for n in lens]).astype(np.int32)
+    val = rng.uniform(-1, 1, len(col)).astype(np.float32)
+    val[rp[11]:rp[12]] = 0.0
+    val[rp[10]:rp[11]:7] = 0.0
+    a = CSR(rows, inner, rp, col, val)
+    b = synth_csr(tb)
+    b = CSR(b.rows, b.cols, b.row_ptr, b.col, -np.abs(b.val))
+    got, products = check(nacho, oracle, a, b)
+    assert products > (1 << 20)
+    row11 = got.val[got.row_ptr[11]:got.row_ptr[12]]
+    assert len(row11) > 0 and not row11.any()
+
+
+def test_single_window_and_partial_last_window(nacho, oracle):
+    """Column counts around the window width: 16384 (one full window), 16385 and 40000 (last
+    window partial), with rows heavy enough to take the window path."""
+    from nacho_b200 import synth
+    for n, cols in enumerate((16384, 16385, 40000)):
+        a = synth_csr(synth.random_csr(40, 600, 0.3, 30 + n))
+        b = synth_csr(synth.random_csr(600, cols, 0.02, 40 + n))
+        check(nacho, oracle, a, b)
+
+
 def test_laplacian_squared_reduced(nacho, oracle):
     """Configuration 4b on a 96 x 96 grid: 13-point stencil, at most 13 entries per row."""
     from nacho_b200 import synth
