@@ -59,13 +59,13 @@ struct EscCtl {
     unsigned long long products;
     int n_small, n_medium, n_long;
     int n_giant, n_huge;  // huge rows with more / at most GIANT_P products
-    int pad;
+    int n_ranked;
 };
 
 // huge_rows holds the giant rows from its front and the other huge rows from its back, so
 // that the heaviest units are handed out first.
 struct RowLists {
-    int32_t *small_rows, *medium_rows, *long_rows, *huge_rows;
+    int32_t *small_rows, *medium_rows, *long_rows, *huge_rows, *ranked_rows;
 };
 
 constexpr unsigned long long GIANT_P = 1ull << 20;
@@ -73,7 +73,7 @@ constexpr unsigned long long GIANT_P = 1ull << 20;
 // Expand phase 1 (src/backend/compute.cpp:541-611): per-row product counts, and the bins.
 // Rows without products get their count (0) written here.
 __global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32_t rows, int32_t *__restrict__ row_count,
-                                                     RowLists lists, unsigned long long huge_p, EscCtl *ctl) {
+                                                     RowLists lists, unsigned long long huge_p, unsigned long long ranked_p, EscCtl *ctl) {
     const int i = blockIdx.x * 256 + threadIdx.x;
     unsigned long long p = 0;
     if (i < rows) {
@@ -89,7 +89,10 @@ __global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32
         } else if (p <= MEDIUM_P) {
             lists.medium_rows[atomicAdd(&ctl->n_medium, 1)] = i;
         } else if (p <= huge_p) {
-            lists.long_rows[atomicAdd(&ctl->n_long, 1)] = i;
+            if (p <= ranked_p)
+                lists.ranked_rows[atomicAdd(&ctl->n_ranked, 1)] = i;
+            else
+                lists.long_rows[atomicAdd(&ctl->n_long, 1)] = i;
         } else {
             if (p > GIANT_P)
                 lists.huge_rows[atomicAdd(&ctl->n_giant, 1)] = i;
@@ -362,6 +365,61 @@ constexpr size_t WIN_PTR_BUDGET = size_t(1) << 30;  // bytes of the window point
 #endif
 constexpr uint32_t NEG_ZERO_BITS = 0x80000000u;
 
+// Walks a flat product range cut into segments: segment k covers the products
+// [seg_off[k], seg_off[k + 1]) and they are the entries seg_start[k] ... of B, each multiplied
+// by seg_a[k]; every segment is non-empty and seg_off[n_seg] == total. Called by all NT threads
+// of the CTA; warp v takes the 32-product blocks v, v + NT/32, ... in groups of ESC_WIN_ITEMS with
+// all of a group's loads in flight together, and hands every product to f(column, value).
+template <int NT, bool WITH_VALUES, typename F>
+__device__ __forceinline__ void walk_segments(const int *seg_off, const int *seg_start, const float *seg_a, int n_seg, int total,
+                                              const CsrView &B, F f) {
+    int k = 0;  // segment holding the warp's current 32-product block (warp-uniform)
+    for (int p0 = warp_id() * (32 * ESC_WIN_ITEMS); p0 < total; p0 += NT * ESC_WIN_ITEMS) {
+        int32_t q[ESC_WIN_ITEMS];
+        float av[ESC_WIN_ITEMS];
+#pragma unroll
+        for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
+            const int pb = p0 + 32 * it;
+            q[it] = -1;
+            av[it] = 0.f;
+            if (pb < total) {
+                const int probe = k + 1 + lane_id();
+                const unsigned ahead = __ballot_sync(FULL_MASK, probe < n_seg && seg_off[probe] <= pb);
+                if (ahead == FULL_MASK) {
+                    int l = k + 32, h = n_seg - 1;
+                    while (l < h) {
+                        const int mid = (l + h + 1) >> 1;
+                        if (seg_off[mid] <= pb)
+                            l = mid;
+                        else
+                            h = mid - 1;
+                    }
+                    k = l;
+                } else {
+                    k += __popc(ahead);
+                }
+                const int p = pb + lane_id();
+                if (p < total) {
+                    int kk = k;
+                    while (seg_off[kk + 1] <= p) ++kk;  // ends: seg_off[n_seg] == total > p
+                    q[it] = seg_start[kk] + (p - seg_off[kk]);
+                    if (WITH_VALUES) av[it] = seg_a[kk];
+                }
+            }
+        }
+        int32_t c[ESC_WIN_ITEMS];
+        float bv[ESC_WIN_ITEMS];
+#pragma unroll
+        for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
+            c[it] = q[it] >= 0 ? ld_nc(B.col + q[it]) : 0;
+            bv[it] = WITH_VALUES && q[it] >= 0 ? ld_nc(B.val + q[it]) : 0.f;
+        }
+#pragma unroll
+        for (int it = 0; it < ESC_WIN_ITEMS; ++it)
+            if (q[it] >= 0) f(c[it], av[it] * bv[it]);
+    }
+}
+
 // Window pointer table of B: ptr[j * (n_win + 1) + w] = first position of row j whose column is
 // >= w * win_cols (w = 0 .. n_win), so that window w of row j is [ptr[w], ptr[w + 1]).
 __global__ void __launch_bounds__(256) k_esc_window_ptr(CsrView B, int32_t b_rows, int n_win, int win_cols, int32_t *__restrict__ ptr) {
@@ -463,58 +521,13 @@ __global__ void __launch_bounds__(WIN_NT, 2)
                 }
                 if (tid == 0) seg_off[n_seg] = total;
                 __syncthreads();
-                int k = 0;  // segment holding the warp's current 32-product block (warp-uniform)
-                for (int p0 = warp_id() * (32 * ESC_WIN_ITEMS); p0 < total; p0 += WIN_NT * ESC_WIN_ITEMS) {
-                    int32_t q[ESC_WIN_ITEMS];
-                    float av[ESC_WIN_ITEMS];
-#pragma unroll
-                    for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
-                        const int pb = p0 + 32 * it;
-                        q[it] = -1;
-                        av[it] = 0.f;
-                        if (pb < total) {
-                            const int probe = k + 1 + lane_id();
-                            const unsigned ahead = __ballot_sync(FULL_MASK, probe < n_seg && seg_off[probe] <= pb);
-                            if (ahead == FULL_MASK) {
-                                int l = k + 32, h = n_seg - 1;
-                                while (l < h) {
-                                    const int mid = (l + h + 1) >> 1;
-                                    if (seg_off[mid] <= pb)
-                                        l = mid;
-                                    else
-                                        h = mid - 1;
-                                }
-                                k = l;
-                            } else {
-                                k += __popc(ahead);
-                            }
-                            const int p = pb + lane_id();
-                            if (p < total) {
-                                int kk = k;
-                                while (seg_off[kk + 1] <= p) ++kk;  // ends: seg_off[n_seg] == total > p
-                                q[it] = seg_start[kk] + (p - seg_off[kk]);
-                                if (NUMERIC) av[it] = seg_a[kk];
-                            }
-                        }
-                    }
-                    int32_t c[ESC_WIN_ITEMS];
-                    float bv[ESC_WIN_ITEMS];
-#pragma unroll
-                    for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
-                        c[it] = q[it] >= 0 ? ld_nc(B.col + q[it]) : 0;
-                        bv[it] = NUMERIC && q[it] >= 0 ? ld_nc(B.val + q[it]) : 0.f;
-                    }
-#pragma unroll
-                    for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
-                        if (q[it] >= 0) {
-                            const int32_t cw = c[it] - w * WCOLS;
-                            if (NUMERIC)
-                                atomicAdd(acc + cw, __fadd_rn(av[it] * bv[it], 0.0f));
-                            else
-                                flags[cw] = 1;
-                        }
-                    }
-                }
+                const int32_t c_first = w * WCOLS;
+                walk_segments<WIN_NT, NUMERIC>(seg_off, seg_start, seg_a, n_seg, total, B, [&](int32_t col, float v) {
+                    if (NUMERIC)
+                        atomicAdd(acc + (col - c_first), __fadd_rn(v, 0.0f));
+                    else
+                        flags[col - c_first] = 1;
+                });
                 __syncthreads();  // the segment arrays are rewritten by the next chunk
             }
             if (!any) continue;  // uniform
@@ -535,35 +548,134 @@ __global__ void __launch_bounds__(WIN_NT, 2)
                 continue;
             }
 
-            // numeric read-off: thread t looks after columns [32 t, 32 t + 32) of the window; the
-            // rotation by t keeps the 32 lanes of a warp on 32 different banks
+            // numeric read-off: warp v looks after columns [1024 v, 1024 v + 1024) of the window in 32
+            // groups of 32; lane g keeps the touched mask of group g, every group is read and
+            // written with lane = column, so shared-memory reads and the result stores coalesce
+            const int wbase = warp_id() * 1024;
             uint32_t mask = 0u;
-            const int wbase = tid * 32;
-#pragma unroll
-            for (int k = 0; k < 32; ++k) {
-                const int idx = (k + tid) & 31;
-                if (__float_as_uint(acc[wbase + idx]) != NEG_ZERO_BITS) mask |= 1u << idx;
+#pragma unroll 8
+            for (int g = 0; g < 32; ++g) {
+                const uint32_t m = __ballot_sync(FULL_MASK, __float_as_uint(acc[wbase + g * 32 + lane_id()]) != NEG_ZERO_BITS);
+                if (lane_id() == g) mask = m;
             }
             int cnt;
             const int rank = block_excl_sum<WIN_NT>(__popc(mask), scan_tmp, cnt);
-            if (mask) {
-                const int64_t first = out + rank;
-                const int32_t col0 = w * WCOLS + wbase;
-#pragma unroll
-                for (int k = 0; k < 32; ++k) {
-                    const int idx = (k + tid) & 31;
-                    if ((mask >> idx) & 1u) {
-                        const int64_t pos = first + __popc(mask & ((1u << idx) - 1u));
-                        c_col[pos] = col0 + idx;
-                        c_val[pos] = acc[wbase + idx];
-                        acc[wbase + idx] = __uint_as_float(NEG_ZERO_BITS);
-                    }
+            const uint32_t below = (1u << lane_id()) - 1u;
+            const int32_t col0 = w * WCOLS + wbase + lane_id();
+#pragma unroll 4
+            for (int g = 0; g < 32; ++g) {
+                const uint32_t m = __shfl_sync(FULL_MASK, mask, g);
+                const int base = __shfl_sync(FULL_MASK, rank, g);
+                if (m == 0u) continue;
+                if ((m >> lane_id()) & 1u) {
+                    const int64_t pos = out + base + __popc(m & below);
+                    c_col[pos] = col0 + g * 32;
+                    c_val[pos] = acc[wbase + g * 32 + lane_id()];
+                    acc[wbase + g * 32 + lane_id()] = __uint_as_float(NEG_ZERO_BITS);
                 }
             }
             out += cnt;
         }
         if (!NUMERIC && tid == 0) row_count[i] = (int32_t)out;
     }
+}
+
+// ------------------------------------------------------------------------ ranked rows ----
+
+constexpr int RK_NT = 256;
+constexpr int RK_WORDS = 8192;                    // bitmap of the whole column range in shared memory
+constexpr int RK_MAX_COLS = RK_WORDS * 32;        // 262144: wider matrices use the global accumulator
+constexpr unsigned long long RK_MAX_P = 65535;    // ranks are kept in 16 bits
+constexpr size_t RK_SMEM = RK_WORDS * 4 + RK_WORDS * 2;
+
+// One CTA per row whose products exceed the sort in shared memory but not the window path.
+// Pass 1 sets a bit per produced column in a shared-memory bitmap; a popcount scan turns the
+// bitmap into the rank of every column within the result row; pass 2 walks the products again
+// and adds each one straight into its final position of C (float32 reductions in L2 on the row's
+// own compact output range, which pass 2 zeroes first). Symbolic: pass 1 and the count only.
+template <bool NUMERIC>
+__global__ void __launch_bounds__(RK_NT) k_esc_ranked(CsrView A, CsrView B, const int32_t *__restrict__ row_list,
+                                                      int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
+                                                      int32_t *__restrict__ c_col, float *__restrict__ c_val) {
+    extern __shared__ __align__(16) unsigned char rk_smem[];
+    uint32_t *bitmap = reinterpret_cast<uint32_t *>(rk_smem);
+    uint16_t *rank16 = reinterpret_cast<uint16_t *>(rk_smem + RK_WORDS * 4);
+    __shared__ int seg_off[RK_NT + 1];
+    __shared__ int seg_start[RK_NT];
+    __shared__ float seg_a[NUMERIC ? RK_NT : 1];
+    __shared__ int scan_tmp[72];
+    const int tid = threadIdx.x;
+    const int32_t i = ld_nc(row_list + blockIdx.x);
+    const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
+    const bool one_chunk = hi - lo <= RK_NT;  // then the segments of pass 1 serve pass 2 as well
+
+    for (int c = tid; c < RK_WORDS / 4; c += RK_NT) reinterpret_cast<uint4 *>(bitmap)[c] = make_uint4(0u, 0u, 0u, 0u);
+
+    // builds the segments of one chunk of the row's entries (whole rows of B) and walks them
+    auto pass = [&](bool build, auto f) {
+        for (int32_t chunk = lo; chunk < hi; chunk += RK_NT) {
+            int n_seg, total;
+            if (build) {
+                int32_t s = 0, len = 0;
+                float a = 0.f;
+                if (chunk + tid < hi) {
+                    const int32_t j = ld_nc(A.col + chunk + tid);
+                    s = ld_nc(B.rp + j);
+                    len = ld_nc(B.rp + j + 1) - s;
+                    if (NUMERIC) a = ld_nc(A.val + chunk + tid);
+                }
+                int k_idx, off;
+                block_excl_sum2<RK_NT>(len > 0 ? 1 : 0, len, scan_tmp, k_idx, off, n_seg, total);
+                if (len > 0) {
+                    seg_off[k_idx] = off;
+                    seg_start[k_idx] = s;
+                    if (NUMERIC) seg_a[k_idx] = a;
+                }
+                if (tid == 0) {
+                    seg_off[n_seg] = total;
+                    scan_tmp[70] = n_seg;
+                }
+                __syncthreads();
+            } else {
+                n_seg = scan_tmp[70];
+                total = seg_off[n_seg];
+            }
+            walk_segments<RK_NT, NUMERIC>(seg_off, seg_start, seg_a, n_seg, total, B, f);
+            __syncthreads();
+        }
+    };
+
+    __syncthreads();
+    pass(true, [&](int32_t col, float) { atomicOr(bitmap + (col >> 5), 1u << (col & 31)); });
+
+    // warp v looks after the words [1024 v, 1024 v + 1024), lane = word within groups of 32
+    const int wbase = warp_id() * (RK_WORDS / (RK_NT / 32));
+    int mine = 0;
+#pragma unroll 8
+    for (int g = 0; g < RK_WORDS / RK_NT; ++g) mine += __popc(bitmap[wbase + g * 32 + lane_id()]);
+    int cnt;
+    const int excl = block_excl_sum<RK_NT>(mine, scan_tmp, cnt);
+    if (!NUMERIC) {
+        if (tid == 0) row_count[i] = cnt;
+        return;
+    }
+    int running = __shfl_sync(FULL_MASK, excl, 0);  // columns before this warp's words
+#pragma unroll 4
+    for (int g = 0; g < RK_WORDS / RK_NT; ++g) {
+        const int c = __popc(bitmap[wbase + g * 32 + lane_id()]);
+        const int incl = warp_incl_sum(c);
+        rank16[wbase + g * 32 + lane_id()] = (uint16_t)(running + incl - c);
+        running += __shfl_sync(FULL_MASK, incl, 31);
+    }
+    const int64_t out = ld_nc(c_rp + i);
+    for (int k = tid; k < cnt; k += RK_NT) c_val[out + k] = 0.f;
+    __syncthreads();  // ranks complete, output zeroed (the reductions below come from this CTA only)
+    pass(!one_chunk, [&](int32_t col, float v) {
+        const uint32_t bits = bitmap[col >> 5];
+        const int64_t pos = out + rank16[col >> 5] + __popc(bits & ((1u << (col & 31)) - 1u));
+        c_col[pos] = col;
+        atomicAdd(c_val + pos, v);
+    });
 }
 
 // Turns the exclusive prefix of the per-row counts into row offsets (rows + 1 entries).
@@ -616,7 +728,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     const size_t slot_bytes = (size_t)words * 4 + (numeric ? (size_t)b->cols * sizeof(acc_t) : 0);
     int max_slots = (int)std::min<size_t>(ESC_LONG_SLOTS, std::max<size_t>(1, LONG_SLOT_BUDGET / std::max<size_t>(slot_bytes, 1)));
     Carver sizes;
-    for (int q = 0; q < 4; ++q) sizes.take<int32_t>((size_t)rows);
+    for (int q = 0; q < 5; ++q) sizes.take<int32_t>((size_t)rows);
     sizes.take<int32_t>((size_t)rows + 1);
     const int scan_ctas = (rows + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT);
     sizes.take<uint64_t>((size_t)scan_ctas + 8);
@@ -635,6 +747,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     plan->lists.medium_rows = carve.take<int32_t>((size_t)rows);
     plan->lists.long_rows = carve.take<int32_t>((size_t)rows);
     plan->lists.huge_rows = carve.take<int32_t>((size_t)rows);
+    plan->lists.ranked_rows = carve.take<int32_t>((size_t)rows);
     plan->row_count = carve.take<int32_t>((size_t)rows + 1);
     plan->scan_block = carve.take<uint64_t>((size_t)scan_ctas + 8);
     plan->scan_ctas = scan_ctas;
@@ -654,7 +767,8 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val};
     if (rows > 0) {
         LaunchScope scope("esc_rowwork", stream);
-        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, numeric ? nullptr : plan->row_count, plan->lists, huge_p, plan->ctl);
+        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, numeric ? nullptr : plan->row_count, plan->lists, huge_p,
+                                                         b->cols <= RK_MAX_COLS ? RK_MAX_P : 0ull, plan->ctl);
         NB200_CUDA(cudaGetLastError());
     }
     NB200_CUDA(cudaMemcpyAsync(plan->ws->host, plan->ctl, sizeof(EscCtl), cudaMemcpyDeviceToHost, stream));
@@ -693,6 +807,16 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
         LaunchScope scope(NUMERIC ? "esc_long_numeric" : "esc_long_symbolic", stream);
         k_esc_long<NUMERIC><<<plan.n_slots, LONG_NT, 0, stream>>>(A, B, plan.lists.long_rows, plan.host.n_long, plan.slots, count, c_rp,
                                                                  c_col, c_val);
+        NB200_CUDA(cudaGetLastError());
+    }
+    if (plan.host.n_ranked > 0) {
+        static bool attr_set[2] = {false, false};
+        if (!attr_set[NUMERIC]) {
+            NB200_CUDA(cudaFuncSetAttribute(k_esc_ranked<NUMERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RK_SMEM));
+            attr_set[NUMERIC] = true;
+        }
+        LaunchScope scope(NUMERIC ? "esc_ranked_numeric" : "esc_ranked_symbolic", stream);
+        k_esc_ranked<NUMERIC><<<plan.host.n_ranked, RK_NT, RK_SMEM, stream>>>(A, B, plan.lists.ranked_rows, count, c_rp, c_col, c_val);
         NB200_CUDA(cudaGetLastError());
     }
     const int64_t n_huge = (int64_t)plan.host.n_giant + plan.host.n_huge;

@@ -114,6 +114,22 @@ def test_long_huge_and_giant_rows(nacho, oracle):
     assert len(row11) > 0 and not row11.any()
 
 
+def test_wider_than_the_shared_bitmap(nacho, oracle):
+    """300000 columns: rows of 2049 .. 19456 products cannot rank their columns in the
+    shared-memory bitmap (262144 columns) and take the global accumulator; heavier rows still
+    take the windows (19 of them, the last one partial)."""
+    from nacho_b200 import synth
+    rng = np.random.default_rng(17)
+    rows, inner, cols = 32, 2000, 300_000
+    lens = rng.integers(0, 3, rows)
+    lens[2], lens[3], lens[4], lens[5] = 6, 12, 25, 60
+    rp = np.zeros(rows + 1, np.int32)
+    rp[1:] = np.cumsum(lens)
+    col = np.concatenate([np.sort(rng.choice(inner, int(n), replace=False)) for n in lens]).astype(np.int32)
+    a = CSR(rows, inner, rp, col, rng.uniform(-1, 1, len(col)).astype(np.float32))
+    check(nacho, oracle, a, synth_csr(synth.random_csr(inner, cols, 0.002, 18)))
+
+
 def test_single_window_and_partial_last_window(nacho, oracle):
     """Column counts around the window width: 16384 (one full window), 16385 and 40000 (last
     window partial), with rows heavy enough to take the window path."""
