@@ -30,7 +30,10 @@ namespace nb200 {
 namespace {
 
 constexpr int SMALL_P = 32;
-constexpr int MEDIUM_P = 2048;
+#ifndef ESC_MEDIUM_P
+#define ESC_MEDIUM_P 2048
+#endif
+constexpr int MEDIUM_P = ESC_MEDIUM_P;
 constexpr int MED_NT = 128;
 #ifndef ESC_LONG_NT
 #define ESC_LONG_NT 512
@@ -74,36 +77,45 @@ constexpr unsigned long long GIANT_P = 1ull << 20;
 // Rows without products get their count (0) written here.
 __global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32_t rows, int32_t *__restrict__ row_count,
                                                      RowLists lists, unsigned long long huge_p, unsigned long long ranked_p, EscCtl *ctl) {
-    const int i = blockIdx.x * 256 + threadIdx.x;
+    __shared__ unsigned long long warp_p[8];
+    const int i = blockIdx.x * 8 + warp_id();  // one warp per row, lanes stride over the row's entries
     unsigned long long p = 0;
     if (i < rows) {
         const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
-        for (int32_t e = lo; e < hi; ++e) {
+        for (int32_t e = lo + lane_id(); e < hi; e += 32) {
             const int32_t j = ld_nc(A.col + e);
             p += (unsigned long long)(ld_nc(B.rp + j + 1) - ld_nc(B.rp + j));
         }
-        if (p == 0) {
-            if (row_count) row_count[i] = 0;
-        } else if (p <= SMALL_P) {
-            lists.small_rows[atomicAdd(&ctl->n_small, 1)] = i;
-        } else if (p <= MEDIUM_P) {
-            lists.medium_rows[atomicAdd(&ctl->n_medium, 1)] = i;
-        } else if (p <= huge_p) {
-            if (p <= ranked_p)
-                lists.ranked_rows[atomicAdd(&ctl->n_ranked, 1)] = i;
-            else
-                lists.long_rows[atomicAdd(&ctl->n_long, 1)] = i;
-        } else {
-            if (p > GIANT_P)
-                lists.huge_rows[atomicAdd(&ctl->n_giant, 1)] = i;
-            else
-                lists.huge_rows[rows - 1 - atomicAdd(&ctl->n_huge, 1)] = i;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL_MASK, p, o);
+        if (lane_id() == 0) {
+            if (p == 0) {
+                if (row_count) row_count[i] = 0;
+            } else if (p <= SMALL_P) {
+                lists.small_rows[atomicAdd(&ctl->n_small, 1)] = i;
+            } else if (p <= MEDIUM_P) {
+                lists.medium_rows[atomicAdd(&ctl->n_medium, 1)] = i;
+            } else if (p <= huge_p) {
+                if (p <= ranked_p)
+                    lists.ranked_rows[atomicAdd(&ctl->n_ranked, 1)] = i;
+                else
+                    lists.long_rows[atomicAdd(&ctl->n_long, 1)] = i;
+            } else {
+                if (p > GIANT_P)
+                    lists.huge_rows[atomicAdd(&ctl->n_giant, 1)] = i;
+                else
+                    lists.huge_rows[rows - 1 - atomicAdd(&ctl->n_huge, 1)] = i;
+            }
         }
     }
-    // one atomic per warp for the product total
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL_MASK, p, o);
-    if (lane_id() == 0 && p) atomicAdd(&ctl->products, p);
+    // one atomic per CTA for the product total
+    if (lane_id() == 0) warp_p[warp_id()] = p;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long sum = 0;
+        for (int v = 0; v < 8; ++v) sum += warp_p[v];
+        if (sum) atomicAdd(&ctl->products, sum);
+    }
 }
 
 // ------------------------------------------------------------------------- small rows ----
@@ -368,38 +380,53 @@ constexpr uint32_t NEG_ZERO_BITS = 0x80000000u;
 // Walks a flat product range cut into segments: segment k covers the products
 // [seg_off[k], seg_off[k + 1]) and they are the entries seg_start[k] ... of B, each multiplied
 // by seg_a[k]; every segment is non-empty and seg_off[n_seg] == total. Called by all NT threads
-// of the CTA; warp v takes the 32-product blocks v, v + NT/32, ... in groups of ESC_WIN_ITEMS with
-// all of a group's loads in flight together, and hands every product to f(column, value).
+// of the CTA. Every warp takes one contiguous share of the range (a multiple of 32 products) and
+// moves through it 32 products at a time, lane = product, so the loads from B coalesce; the
+// segment of the current block is warp-uniform state that only moves forward, and a block that
+// lies inside one segment (the common case for long rows of B) needs no per-lane search.
+// ESC_WIN_ITEMS blocks have their loads in flight together. f(column, value) gets every product.
 template <int NT, bool WITH_VALUES, typename F>
 __device__ __forceinline__ void walk_segments(const int *seg_off, const int *seg_start, const float *seg_a, int n_seg, int total,
                                               const CsrView &B, F f) {
-    int k = 0;  // segment holding the warp's current 32-product block (warp-uniform)
-    for (int p0 = warp_id() * (32 * ESC_WIN_ITEMS); p0 < total; p0 += NT * ESC_WIN_ITEMS) {
+    constexpr int NW = NT / 32;
+    const int share = ((total + NW * 32 - 1) / (NW * 32)) * 32;
+    int pb = warp_id() * share;
+    const int pe = min(pb + share, total);
+    if (pb >= pe) return;
+    int k = 0;
+    {  // largest k with seg_off[k] <= pb
+        int h = n_seg - 1;
+        while (k < h) {
+            const int mid = (k + h + 1) >> 1;
+            if (seg_off[mid] <= pb)
+                k = mid;
+            else
+                h = mid - 1;
+        }
+    }
+    int k_end = seg_off[k + 1];
+    int delta = seg_start[k] - seg_off[k];  // position in B = delta + product index
+    float k_a = WITH_VALUES ? seg_a[k] : 0.f;
+    for (; pb < pe; pb += 32 * ESC_WIN_ITEMS) {
         int32_t q[ESC_WIN_ITEMS];
         float av[ESC_WIN_ITEMS];
 #pragma unroll
         for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
-            const int pb = p0 + 32 * it;
+            const int b = pb + 32 * it;
             q[it] = -1;
             av[it] = 0.f;
-            if (pb < total) {
-                const int probe = k + 1 + lane_id();
-                const unsigned ahead = __ballot_sync(FULL_MASK, probe < n_seg && seg_off[probe] <= pb);
-                if (ahead == FULL_MASK) {
-                    int l = k + 32, h = n_seg - 1;
-                    while (l < h) {
-                        const int mid = (l + h + 1) >> 1;
-                        if (seg_off[mid] <= pb)
-                            l = mid;
-                        else
-                            h = mid - 1;
-                    }
-                    k = l;
-                } else {
-                    k += __popc(ahead);
+            if (b < pe) {
+                while (b >= k_end) {
+                    ++k;
+                    k_end = seg_off[k + 1];
+                    delta = seg_start[k] - seg_off[k];
+                    if (WITH_VALUES) k_a = seg_a[k];
                 }
-                const int p = pb + lane_id();
-                if (p < total) {
+                const int p = b + lane_id();
+                if (b + 32 <= k_end) {
+                    q[it] = delta + p;
+                    av[it] = k_a;
+                } else if (p < pe) {
                     int kk = k;
                     while (seg_off[kk + 1] <= p) ++kk;  // ends: seg_off[n_seg] == total > p
                     q[it] = seg_start[kk] + (p - seg_off[kk]);
@@ -586,7 +613,7 @@ constexpr int RK_NT = 256;
 constexpr int RK_WORDS = 8192;                    // bitmap of the whole column range in shared memory
 constexpr int RK_MAX_COLS = RK_WORDS * 32;        // 262144: wider matrices use the global accumulator
 constexpr unsigned long long RK_MAX_P = 65535;    // ranks are kept in 16 bits
-constexpr size_t RK_SMEM = RK_WORDS * 4 + RK_WORDS * 2;
+constexpr size_t RK_SMEM = RK_WORDS * 4 + RK_WORDS * 2;  // bitmap + ranks at the full width
 
 // One CTA per row whose products exceed the sort in shared memory but not the window path.
 // Pass 1 sets a bit per produced column in a shared-memory bitmap; a popcount scan turns the
@@ -595,11 +622,13 @@ constexpr size_t RK_SMEM = RK_WORDS * 4 + RK_WORDS * 2;
 // own compact output range, which pass 2 zeroes first). Symbolic: pass 1 and the count only.
 template <bool NUMERIC>
 __global__ void __launch_bounds__(RK_NT) k_esc_ranked(CsrView A, CsrView B, const int32_t *__restrict__ row_list,
-                                                      int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
-                                                      int32_t *__restrict__ c_col, float *__restrict__ c_val) {
+                                                      int words, int32_t *__restrict__ row_count,
+                                                      const int32_t *__restrict__ c_rp, int32_t *__restrict__ c_col,
+                                                      float *__restrict__ c_val) {
+    // `words`: bitmap words in use, a multiple of RK_NT that covers B's columns
     extern __shared__ __align__(16) unsigned char rk_smem[];
     uint32_t *bitmap = reinterpret_cast<uint32_t *>(rk_smem);
-    uint16_t *rank16 = reinterpret_cast<uint16_t *>(rk_smem + RK_WORDS * 4);
+    uint16_t *rank16 = reinterpret_cast<uint16_t *>(rk_smem + (size_t)words * 4);
     __shared__ int seg_off[RK_NT + 1];
     __shared__ int seg_start[RK_NT];
     __shared__ float seg_a[NUMERIC ? RK_NT : 1];
@@ -609,7 +638,7 @@ __global__ void __launch_bounds__(RK_NT) k_esc_ranked(CsrView A, CsrView B, cons
     const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
     const bool one_chunk = hi - lo <= RK_NT;  // then the segments of pass 1 serve pass 2 as well
 
-    for (int c = tid; c < RK_WORDS / 4; c += RK_NT) reinterpret_cast<uint4 *>(bitmap)[c] = make_uint4(0u, 0u, 0u, 0u);
+    for (int c = tid; c < words / 4; c += RK_NT) reinterpret_cast<uint4 *>(bitmap)[c] = make_uint4(0u, 0u, 0u, 0u);
 
     // builds the segments of one chunk of the row's entries (whole rows of B) and walks them
     auto pass = [&](bool build, auto f) {
@@ -648,11 +677,12 @@ __global__ void __launch_bounds__(RK_NT) k_esc_ranked(CsrView A, CsrView B, cons
     __syncthreads();
     pass(true, [&](int32_t col, float) { atomicOr(bitmap + (col >> 5), 1u << (col & 31)); });
 
-    // warp v looks after the words [1024 v, 1024 v + 1024), lane = word within groups of 32
-    const int wbase = warp_id() * (RK_WORDS / (RK_NT / 32));
+    // warp v looks after an eighth of the words, lane = word within groups of 32
+    const int groups = words / RK_NT;
+    const int wbase = warp_id() * groups * 32;
     int mine = 0;
-#pragma unroll 8
-    for (int g = 0; g < RK_WORDS / RK_NT; ++g) mine += __popc(bitmap[wbase + g * 32 + lane_id()]);
+#pragma unroll 4
+    for (int g = 0; g < groups; ++g) mine += __popc(bitmap[wbase + g * 32 + lane_id()]);
     int cnt;
     const int excl = block_excl_sum<RK_NT>(mine, scan_tmp, cnt);
     if (!NUMERIC) {
@@ -661,7 +691,7 @@ __global__ void __launch_bounds__(RK_NT) k_esc_ranked(CsrView A, CsrView B, cons
     }
     int running = __shfl_sync(FULL_MASK, excl, 0);  // columns before this warp's words
 #pragma unroll 4
-    for (int g = 0; g < RK_WORDS / RK_NT; ++g) {
+    for (int g = 0; g < groups; ++g) {
         const int c = __popc(bitmap[wbase + g * 32 + lane_id()]);
         const int incl = warp_incl_sum(c);
         rank16[wbase + g * 32 + lane_id()] = (uint16_t)(running + incl - c);
@@ -705,7 +735,7 @@ struct EscPlan {
     EscCtl *ctl;
     LongSlots slots;
     int n_slots;
-    int n_win;    // column windows per huge row (0: the window path is off for this B)
+    int n_win_numeric, n_win_symbolic;  // column windows per huge row in either pass (0: the window path is off for this B)
     EscCtl host;  // counters read back after the row-work kernel
 };
 
@@ -722,11 +752,21 @@ int sm_count() {
 }
 
 // Bins the rows (kernel + one read-back) and carves the scratch of one pass.
-int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream_t stream, EscPlan *plan) {
+// `numeric`: the global accumulator slots carry values (needed by the numeric pass);
+// `counts`: rows without products get their count written (needed by the symbolic pass).
+// A plan prepared with both serves a symbolic pass followed by a numeric pass.
+int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, bool counts, cudaStream_t stream, EscPlan *plan) {
     const int32_t rows = a->rows;
     const int32_t words = (b->cols + 31) / 32;
     const size_t slot_bytes = (size_t)words * 4 + (numeric ? (size_t)b->cols * sizeof(acc_t) : 0);
+    // both passes bin the rows alike: the thresholds come from the numeric pass's windows
+    const int64_t n_win_num = std::max<int64_t>(1, ((int64_t)b->cols + WIN_COLS_NUMERIC - 1) / WIN_COLS_NUMERIC);
+    const int64_t n_win_sym = std::max<int64_t>(1, ((int64_t)b->cols + WIN_COLS_SYMBOLIC - 1) / WIN_COLS_SYMBOLIC);
+    const bool windows_on = n_win_num <= WIN_MAX_WINDOWS && (size_t)b->rows * (size_t)(n_win_num + 1) * 4 <= WIN_PTR_BUDGET;
+    const bool ranked_on = b->cols <= RK_MAX_COLS;
+    const bool no_long_rows = windows_on && ranked_on && (unsigned long long)ESC_WIN_P * n_win_num <= RK_MAX_P;
     int max_slots = (int)std::min<size_t>(ESC_LONG_SLOTS, std::max<size_t>(1, LONG_SLOT_BUDGET / std::max<size_t>(slot_bytes, 1)));
+    if (no_long_rows) max_slots = 0;
     Carver sizes;
     for (int q = 0; q < 5; ++q) sizes.take<int32_t>((size_t)rows);
     sizes.take<int32_t>((size_t)rows + 1);
@@ -738,7 +778,7 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     // kernel; reserve them up front so that the pool block does not move in between
     int st;
     if ((st = acquire_workspace(stream, fixed + (size_t)max_slots * (slot_bytes + 512) + 1024, &plan->ws))) {
-        if (st != NB200_E_NOMEM || max_slots == 1) return st;
+        if (st != NB200_E_NOMEM || max_slots <= 1) return st;
         max_slots = 1;
         if ((st = acquire_workspace(stream, fixed + slot_bytes + 2048, &plan->ws))) return st;
     }
@@ -757,18 +797,16 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool numeric, cudaStream
     plan->slots.bitmap = carve.take<uint32_t>((size_t)max_slots * words);
     plan->slots.acc = numeric ? carve.take<acc_t>((size_t)max_slots * b->cols) : nullptr;
     plan->n_slots = max_slots;
-    const int win_cols = numeric ? WIN_COLS_NUMERIC : WIN_COLS_SYMBOLIC;
-    const int64_t n_win = std::max<int64_t>(1, ((int64_t)b->cols + win_cols - 1) / win_cols);
-    const bool windows_on = n_win <= WIN_MAX_WINDOWS && (size_t)b->rows * (size_t)(n_win + 1) * 4 <= WIN_PTR_BUDGET;
-    plan->n_win = windows_on ? (int)n_win : 0;
-    const unsigned long long huge_p = plan->n_win ? (unsigned long long)ESC_WIN_P * (unsigned long long)plan->n_win : ULLONG_MAX;
+    plan->n_win_numeric = windows_on ? (int)n_win_num : 0;
+    plan->n_win_symbolic = windows_on ? (int)n_win_sym : 0;
+    const unsigned long long huge_p = windows_on ? (unsigned long long)ESC_WIN_P * (unsigned long long)n_win_num : ULLONG_MAX;
 
     NB200_CUDA(cudaMemsetAsync(plan->ctl, 0, sizeof(EscCtl), stream));
     const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val};
     if (rows > 0) {
         LaunchScope scope("esc_rowwork", stream);
-        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, numeric ? nullptr : plan->row_count, plan->lists, huge_p,
-                                                         b->cols <= RK_MAX_COLS ? RK_MAX_P : 0ull, plan->ctl);
+        k_esc_rowwork<<<(rows + 7) / 8, 256, 0, stream>>>(A, B, rows, counts ? plan->row_count : nullptr, plan->lists, huge_p,
+                                                         ranked_on ? RK_MAX_P : 0ull, plan->ctl);
         NB200_CUDA(cudaGetLastError());
     }
     NB200_CUDA(cudaMemcpyAsync(plan->ws->host, plan->ctl, sizeof(EscCtl), cudaMemcpyDeviceToHost, stream));
@@ -816,13 +854,16 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
             attr_set[NUMERIC] = true;
         }
         LaunchScope scope(NUMERIC ? "esc_ranked_numeric" : "esc_ranked_symbolic", stream);
-        k_esc_ranked<NUMERIC><<<plan.host.n_ranked, RK_NT, RK_SMEM, stream>>>(A, B, plan.lists.ranked_rows, count, c_rp, c_col, c_val);
+        const int rk_words = (((b->cols + 31) / 32 + RK_NT - 1) / RK_NT) * RK_NT;
+        k_esc_ranked<NUMERIC><<<plan.host.n_ranked, RK_NT, (size_t)rk_words * 6, stream>>>(A, B, plan.lists.ranked_rows, rk_words, count, c_rp,
+                                                                                        c_col, c_val);
         NB200_CUDA(cudaGetLastError());
     }
     const int64_t n_huge = (int64_t)plan.host.n_giant + plan.host.n_huge;
     if (n_huge > 0) {
         constexpr int WCOLS = NUMERIC ? WIN_COLS_NUMERIC : WIN_COLS_SYMBOLIC;
-        const int64_t ptr_entries = (int64_t)b->rows * (plan.n_win + 1);
+        const int n_win = NUMERIC ? plan.n_win_numeric : plan.n_win_symbolic;
+        const int64_t ptr_entries = (int64_t)b->rows * (n_win + 1);
         Carver sizes;
         sizes.take<int>(1);
         sizes.take<int32_t>((size_t)ptr_entries);
@@ -835,7 +876,7 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
         NB200_CUDA(cudaMemsetAsync(ticket, 0, sizeof(int), stream));
         {
             LaunchScope scope("esc_window_ptr", stream);
-            k_esc_window_ptr<<<(unsigned)((ptr_entries + 255) / 256), 256, 0, stream>>>(B, b->rows, plan.n_win, WCOLS, win_ptr);
+            k_esc_window_ptr<<<(unsigned)((ptr_entries + 255) / 256), 256, 0, stream>>>(B, b->rows, n_win, WCOLS, win_ptr);
             NB200_CUDA(cudaGetLastError());
         }
         static bool attr_set[2] = {false, false};
@@ -848,13 +889,15 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
         const int grid = (int)std::min<int64_t>(n_huge, (int64_t)sm_count() * std::max(per_sm, 1));
         LaunchScope scope(NUMERIC ? "esc_window_numeric" : "esc_window_symbolic", stream);
         k_esc_window<NUMERIC><<<grid, WIN_NT, WIN_BYTES, stream>>>(A, B, win_ptr, plan.lists.huge_rows, a->rows, plan.host.n_giant, (int)n_huge,
-                                                                  plan.n_win, ticket, count, c_rp, c_col, c_val);
+                                                                  n_win, ticket, count, c_rp, c_col, c_val);
         NB200_CUDA(cudaGetLastError());
     }
     return NB200_OK;
 }
 
-int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_t *products, void *stream_v) {
+// `keep`: if given, the plan is prepared for both passes and handed back, so that a numeric
+// pass that follows at once (nothing else touching the stream's scratch) skips the binning.
+int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_t *products, void *stream_v, EscPlan *keep = nullptr) {
     int st;
     if ((st = check_operand(a)) || (st = check_operand(b))) return st;
     if (!c || !c->row_ptr || a->cols != b->rows) return NB200_E_BADARG;
@@ -868,7 +911,8 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
         return NB200_OK;
     }
     EscPlan plan{};
-    if ((st = esc_prepare(a, b, false, stream, &plan))) return st;
+    if ((st = esc_prepare(a, b, keep != nullptr, true, stream, &plan))) return st;
+    if (keep) *keep = plan;
     if (products) *products = (int64_t)plan.host.products;
     if ((st = esc_run_bins<false>(a, b, plan, nullptr, stream))) return st;
     FusedCtl *scan_ctl = reinterpret_cast<FusedCtl *>(plan.scan_block);
@@ -894,15 +938,16 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
     return NB200_OK;
 }
 
-int spgemm_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, void *stream_v) {
+int spgemm_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, void *stream_v, const EscPlan *kept = nullptr) {
     int st;
     if ((st = check_operand(a)) || (st = check_operand(b))) return st;
     if (!c || !c->row_ptr || a->cols != b->rows || c->nnz < 0) return NB200_E_BADARG;
     if (c->nnz > 0 && (!c->col || !c->val)) return NB200_E_BADARG;
     if (a->rows == 0 || c->nnz == 0) return NB200_OK;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (kept) return esc_run_bins<true>(a, b, *kept, c, stream);
     EscPlan plan{};
-    if ((st = esc_prepare(a, b, true, stream, &plan))) return st;
+    if ((st = esc_prepare(a, b, true, false, stream, &plan))) return st;
     return esc_run_bins<true>(a, b, plan, c, stream);
 }
 
@@ -929,12 +974,13 @@ int nb200_spgemm_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int32
     c->col = nullptr;
     c->val = nullptr;
     NB200_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&c->row_ptr), sizeof(int32_t) * ((size_t)std::max(a->rows, 0) + 1), stream));
-    int st = spgemm_symbolic(a, b, c, nullptr, stream_v);
+    EscPlan plan{};
+    int st = spgemm_symbolic(a, b, c, nullptr, stream_v, &plan);
     if (st == NB200_OK && c->nnz > 0) {
         cudaError_t e = cudaMallocAsync(reinterpret_cast<void **>(&c->col), sizeof(int32_t) * (size_t)c->nnz, stream);
         if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&c->val), sizeof(float) * (size_t)c->nnz, stream);
         if (e != cudaSuccess) st = note_cuda_error(e, "cudaMallocAsync");
-        else st = spgemm_numeric(a, b, c, stream_v);
+        else st = spgemm_numeric(a, b, c, stream_v, &plan);
     }
     if (st != NB200_OK) {
         if (c->row_ptr) cudaFreeAsync(c->row_ptr, stream);
