@@ -333,6 +333,26 @@ __device__ __forceinline__ void walk_segments(const int *seg_off, const int *seg
     int delta = seg_start[k] - seg_off[k];  // position in B = delta + product index
     float k_a = WITH_VALUES ? seg_a[k] : 0.f;
     for (; pb < pe; pb += 32 * ESC_WIN_ITEMS) {
+        while (pb >= k_end) {
+            ++k;
+            k_end = seg_off[k + 1];
+            delta = seg_start[k] - seg_off[k];
+            if (WITH_VALUES) k_a = seg_a[k];
+        }
+        if (pb + 32 * ESC_WIN_ITEMS <= min(k_end, pe)) {  // uniform: all the blocks lie inside segment k
+            const int32_t *bc = B.col + (delta + pb + lane_id());
+            const float *bvp = B.val + (delta + pb + lane_id());
+            int32_t c[ESC_WIN_ITEMS];
+            float bv[ESC_WIN_ITEMS];
+#pragma unroll
+            for (int it = 0; it < ESC_WIN_ITEMS; ++it) {
+                c[it] = ld_nc(bc + 32 * it);
+                bv[it] = WITH_VALUES ? ld_nc(bvp + 32 * it) : 0.f;
+            }
+#pragma unroll
+            for (int it = 0; it < ESC_WIN_ITEMS; ++it) f(c[it], k_a * bv[it]);
+            continue;
+        }
         int32_t q[ESC_WIN_ITEMS];
         float av[ESC_WIN_ITEMS];
 #pragma unroll
@@ -441,7 +461,7 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
     int64_t out = NUMERIC ? (int64_t)ld_nc(c_rp + i) : 0;  // next free position of the row (count so far, symbolic)
 
     for (int w = 0; w < n_win; ++w) {
-        const int64_t c_first = (int64_t)w * RK_WINDOW_COLS;
+        const int32_t c_first = w * RK_WINDOW_COLS;  // below 2^31: it is a column of B
 
         // builds the segments of one chunk of the row's entries (their rows of B inside the window)
         // and walks them; returns whether the window holds any product
@@ -470,7 +490,7 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
                         } else {
                             const int32_t b_lo = ld_nc(B.rp + j), b_hi = ld_nc(B.rp + j + 1);
                             s = w == 0 ? b_lo : first_col_at_least(B.col, b_lo, b_hi, c_first);
-                            len = (w == n_win - 1 ? b_hi : first_col_at_least(B.col, s, b_hi, c_first + RK_WINDOW_COLS)) - s;
+                            len = (w == n_win - 1 ? b_hi : first_col_at_least(B.col, s, b_hi, (int64_t)c_first + RK_WINDOW_COLS)) - s;
                         }
                     }
                     int k_idx, off;
@@ -527,17 +547,18 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
             rank[idx] = (RankT)first;
             int64_t pos = out + first;
             while (bits) {
-                c_col[pos++] = (int32_t)(c_first + (int64_t)idx * 32 + (__ffs(bits) - 1));
+                c_col[pos++] = c_first + idx * 32 + (__ffs(bits) - 1);
                 bits &= bits - 1u;
             }
             running += __shfl_sync(FULL_MASK, incl, 31);
         }
         for (int k = tid; k < cnt; k += NT) c_val[out + k] = 0.f;
         __syncthreads();  // ranks complete, output zeroed (the reductions below come from this CTA only)
+        float *row_val = c_val + out;  // the window's part of the row; its length fits 32 bits
         pass(!one_chunk, [&](int32_t col, float v) {
             const uint32_t cw = (uint32_t)(col - c_first);
             const uint32_t bits = bitmap[cw >> 5];
-            atomicAdd(c_val + (out + (int64_t)rank[cw >> 5] + __popc(bits & ((1u << (cw & 31u)) - 1u))), v);
+            atomicAdd(row_val + ((uint32_t)rank[cw >> 5] + __popc(bits & ((1u << (cw & 31u)) - 1u))), v);
         });
         out += cnt;
     }

@@ -69,13 +69,14 @@ def test_exact_cancellation_is_kept(nacho, oracle):
 
 
 def test_medium_and_long_rows(nacho, oracle):
-    """Rows in every bin: <= 32, <= 2048 and > 2048 products, next to empty rows."""
+    """Rows in the warp, sorted-CTA and ranked bins (<= 32, <= 256, more products), next to empty rows."""
     rng = np.random.default_rng(3)
     rows, inner, cols = 300, 4000, 6000
     lens = rng.integers(0, 6, rows)
-    lens[10] = 200      # medium: 200 entries x ~8 = 1600 products
-    lens[20] = 900      # long
-    lens[21] = 3000     # long, most of the inner dimension
+    lens[9] = 25       # sorted in shared memory: about 200 products
+    lens[10] = 200      # ranked: 200 entries x ~8 = 1600 products
+    lens[20] = 900      # ranked
+    lens[21] = 3000     # ranked, most of the inner dimension
     lens[50:60] = 0
     rp = np.zeros(rows + 1, np.int32)
     rp[1:] = np.cumsum(lens)
@@ -87,18 +88,17 @@ def test_medium_and_long_rows(nacho, oracle):
 
 
 def test_long_huge_and_giant_rows(nacho, oracle):
-    """100000 columns = 7 windows of 16384: rows of 2049 .. 7168 products stay on the global
-    accumulator, heavier rows go through the shared-memory windows, one row has more than 2^20
-    products. A row of explicit zeros against negative values makes every product -0.0: its
-    entries must still be stored (as 0.0 sums)."""
+    """Rows on both sides of 65535 products (16-bit and 32-bit column ranks) and one row with more
+    than 2^20 products (handed out first). A row of explicit zeros against negative values makes
+    every product -0.0: its entries must still be stored (as 0.0 sums)."""
     from nacho_b200 import synth
     rng = np.random.default_rng(11)
     rows, inner, cols = 48, 3000, 100_000
     tb = synth.random_csr(inner, cols, 0.005, 12)          # about 500 entries per row of B
     lens = rng.integers(0, 4, rows)
-    lens[3], lens[4], lens[5] = 6, 9, 13                   # long: about 3000 / 4500 / 6500 products
-    lens[8], lens[9], lens[10] = 20, 64, 700               # huge
-    lens[11] = 600                                         # huge, all-zero values
+    lens[3], lens[4], lens[5] = 6, 9, 13                   # ranked: about 3000 / 4500 / 6500 products
+    lens[8], lens[9], lens[10] = 20, 64, 700               # ranked, ranked, heavy (about 350000 products)
+    lens[11] = 600                                         # heavy, all-zero values
     lens[20] = 2600                                        # giant: about 1.3 M products
     rp = np.zeros(rows + 1, np.int32)
     rp[1:] = np.cumsum(lens)
@@ -116,14 +116,14 @@ def test_long_huge_and_giant_rows(nacho, oracle):
 
 
 def test_wider_than_the_shared_bitmap(nacho, oracle):
-    """300000 columns: rows of 2049 .. 19456 products cannot rank their columns in the
-    shared-memory bitmap (262144 columns) and take the global accumulator; heavier rows still
-    take the windows (19 of them, the last one partial)."""
+    """300000 columns: wider than the shared-memory bitmap (262144 columns), so every ranked row
+    is walked in two column windows through the window pointer table of B, the second window
+    partial."""
     from nacho_b200 import synth
     rng = np.random.default_rng(17)
     rows, inner, cols = 32, 2000, 300_000
     lens = rng.integers(0, 3, rows)
-    lens[2], lens[3], lens[4], lens[5] = 6, 12, 25, 60
+    lens[2], lens[3], lens[4], lens[5], lens[6] = 6, 12, 25, 60, 200   # the last one heavy: about 120000 products
     rp = np.zeros(rows + 1, np.int32)
     rp[1:] = np.cumsum(lens)
     col = np.concatenate([np.sort(rng.choice(inner, int(n), replace=False)) for n in lens]).astype(np.int32)
@@ -131,9 +131,28 @@ def test_wider_than_the_shared_bitmap(nacho, oracle):
     check(nacho, oracle, a, synth_csr(synth.random_csr(inner, cols, 0.002, 18)))
 
 
+def test_hyper_wide_b_without_pointer_table(nacho, oracle):
+    """2^30 columns and 70000 rows of B: the window pointer table (70000 x 4097 entries) would
+    exceed its budget, so the 4096 column windows of every ranked row are located by binary
+    search instead. Almost all windows of a row are empty."""
+    rng = np.random.default_rng(23)
+    inner, cols, per_row = 70_000, 1 << 30, 100
+    keys = np.unique(np.repeat(np.arange(inner, dtype=np.int64), per_row) * cols + rng.integers(0, cols, inner * per_row))
+    b_rows, b_col = keys // cols, (keys % cols).astype(np.int32)
+    b_rp = np.zeros(inner + 1, np.int32)
+    b_rp[1:] = np.cumsum(np.bincount(b_rows, minlength=inner))
+    b = CSR(inner, cols, b_rp, b_col, rng.uniform(-1, 1, len(b_col)).astype(np.float32))
+    lens = np.array([0, 4, 30, 0, 700, 2])
+    rp = np.zeros(len(lens) + 1, np.int32)
+    rp[1:] = np.cumsum(lens)
+    col = np.concatenate([np.sort(rng.choice(inner, int(n), replace=False)) for n in lens]).astype(np.int32)
+    a = CSR(len(lens), inner, rp, col, rng.uniform(-1, 1, len(col)).astype(np.float32))
+    check(nacho, oracle, a, b)
+
+
 def test_single_window_and_partial_last_window(nacho, oracle):
-    """Column counts around the window width: 16384 (one full window), 16385 and 40000 (last
-    window partial), with rows heavy enough to take the window path."""
+    """Column counts around multiples of the bitmap granularity (8192 columns per 256 words),
+    with rows heavy enough to be ranked."""
     from nacho_b200 import synth
     for n, cols in enumerate((16384, 16385, 40000)):
         a = synth_csr(synth.random_csr(40, 600, 0.3, 30 + n))
@@ -152,7 +171,7 @@ def test_laplacian_squared_reduced(nacho, oracle):
 
 
 def test_rmat_reduced(nacho, oracle):
-    """Configuration 4a at scale 12 (4096 rows, B = A^T): skewed rows, some in the long bin."""
+    """Configuration 4a at scale 12 (4096 rows, B = A^T): skewed rows in every bin."""
     from nacho_b200 import synth
     ta = synth.rmat_csr(scale=12, seed=4012)
     tb = synth.transpose_csr(ta)
