@@ -16,6 +16,10 @@ entries per operand, uniform rows). Rank 0 prints one JSON line:
              kernel (CUDA events on the launching stream), against the measured HBM copy peak
   cpu_baseline  the reference's own CPU kernels (the C oracle port where the reference has
              none, i.e. SpGEMM) timed on the host cores on a bounded sample of the workload
+  ref_gpu_baseline  at N = 1: the reference's own GPU kernels (emitted by its compiler, recompiled
+             unchanged for sm_100a) on the same device operands, whole driver call, default grid;
+             null where that library was not built, "unavailable" where the input exceeds the
+             reference's int32 product counters
 
 With N > 1 (launched by torch.distributed.run) every rank holds its own row block of the same
 size (weak scaling); the only exchange is the all-gather of (rows, nnz) per block that stitches
@@ -253,6 +257,38 @@ def cpu_baseline(name: str, operands, steps: int = 3, warmup: int = 1):
             "nnz_per_s": nnz_in / t, "ms": t * 1e3}
 
 
+def ref_gpu_baseline(spec, tensors, nbytes, products=None, runs: int = 3):
+    """Times the reference's own GPU kernels (emitted by its compiler, recompiled unchanged for
+    sm_100a into oracle/_ref/libnacho_ref_gpu.so) on the device operands of this run, default grid
+    256 x 256, whole driver call (its allocations and its length read-back included). Returns None
+    where that library was not built, and skips SpGEMM inputs whose product count would overflow
+    the reference's int32 counters."""
+    from oracle.gpu_reference import DEFAULT_GRID, ReferenceGpu
+    if not ReferenceGpu.available():
+        return None
+    op = spec["op"]
+    if op == "spgemm" and (products is None or products >= (1 << 31) - (1 << 24)):
+        return {"unavailable": f"{products} products do not fit the reference's int32 product counters"}
+    ref = ReferenceGpu()
+    if spec["fmt"] == "csr":
+        tup = [(int(t.shape[0]), int(t.shape[1]), t.dim_j_offsets, t.dim_j_indices, t.values) for t in tensors]
+    elif spec["fmt"] == "coo3":
+        tup = [(tuple(int(x) for x in t.shape), t.dim_i_indices, t.dim_j_indices, t.dim_k_indices, t.values) for t in tensors]
+    else:
+        tup = [(tuple(int(x) for x in t.shape), t.dim_i_indices, t.dim_j_offsets, t.dim_j_indices, t.dim_k_offsets,
+                t.dim_k_indices, t.values) for t in tensors]
+    fn = {"csr_add": ref.csr_add, "csr_mul": ref.csr_mul, "csr_add_3": ref.csr_add_3, "spgemm": ref.spgemm,
+          "coo3d_add": ref.coo3_add, "csf_add": ref.csf3_add}[op]
+    times = []
+    for k in range(runs + 1):  # the first call is the warm-up
+        fn(*tup, keep=False)
+        if k:
+            times.append(ref.last_ms)
+    ms = statistics.mean(times)
+    return {"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms, "grid": list(DEFAULT_GRID), "runs": runs,
+            "kind": "reference GPU kernels as emitted by its compiler, recompiled for sm_100a; whole driver call"}
+
+
 def cpu_sample_scale(name: str, requested: float) -> float:
     """Fraction of the workload used for CPU timing: about 10-30 s of CPU work in total."""
     if name == "c1_csr_add" or name.startswith("c4"):
@@ -341,6 +377,7 @@ def main():
                     help="log2 of the rows of the R-MAT SpGEMM operand (configuration 4a names 18)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own GPU kernels beside ours")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -506,6 +543,9 @@ def main():
             base["sample"] = (f"{args.workload} at scale {scale:g} of its rows/entries"
                               + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" else "")
                               + ", mean of 3 runs")
+        ref_gpu = None
+        if world == 1 and not args.no_ref_gpu:
+            ref_gpu = ref_gpu_baseline(spec, tensors, nbytes, extra.get("products"))
         line = {
             "metric": f"{spec['op']} effective HBM GB/s (operand + result bytes)",
             "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -517,7 +557,7 @@ def main():
                             "l2_policy": "inputs_larger_than_L2" if nbytes > 2 * 126e6 else "inputs fit L2 (latency-bound case)",
                             "parallelism": f"row blocks x{world}, all-gather of (rows, nnz) per step"}, **extra),
             "nnz_per_s": total_nnz_in / (ms_per_step * 1e-3),
-            "roofline": roof, "kernels": kernels, "cpu_baseline": base,
+            "roofline": roof, "kernels": kernels, "cpu_baseline": base, "ref_gpu_baseline": ref_gpu,
             "e2e": ({"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"],
                      "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e_s * 1e3} if e2e else None),
             "gpu_launches": launches, "clocks": clocks,
