@@ -138,6 +138,8 @@ struct KeyTraits<uint64_t> {
 // Generic tile body: any key width, plain loads and stores. Used for the tiles whose rows do not
 // fit a 32-bit composite key; the common case takes csr2_tile_fast below.
 template <typename KeyT, int VT, int OP, int MODE>
+// (Not inlined, so the structs are taken by address: the kernel declares them __grid_constant__,
+// which lets that address point at the parameter space instead of a per-thread stack copy.)
 __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits,
                                                const int t, int32_t *tile_count, volatile uint64_t *tile_state,
                                                FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
@@ -680,8 +682,10 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
 }
 
 template <int VT, int OP, int MODE>
-__global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(CsrIn A, CsrIn B, Cuts cuts, int cbits, int32_t *tile_count,
-                                                       uint64_t *tile_state, FusedCtl *ctl, CsrOut Z) {
+__global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __grid_constant__ CsrIn A, const __grid_constant__ CsrIn B,
+                                                                         const __grid_constant__ Cuts cuts, int cbits, int32_t *tile_count,
+                                                                         uint64_t *tile_state, FusedCtl *ctl,
+                                                                         const __grid_constant__ CsrOut Z) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
     __shared__ int thread_rank[NT];
