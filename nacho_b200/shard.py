@@ -10,6 +10,9 @@ of the operands only, so the path shards with no data-path collective:
 * SpGEMM: A in row blocks of balanced product counts, B replicated with a broadcast.
 * COO3 add: merge-path diagonal cuts of the flat merged coordinate sequence that never
   split an equal pair (src/backend/partition.cpp:964-983).
+* CSF3 add: the same cuts on the innermost (k) level. A cut may fall inside a fibre, so a block
+  can start or end with a partial ``i`` slice / ``(i, j)`` fibre; the same node then closes one
+  result block and opens the next, and the stitch counts it once.
 
 The one exchange is ``stitch``: an all-gather of (rows, nnz) per block, whose exclusive prefix
 gives each block's global row base and the base to add to its row offsets.
@@ -86,6 +89,116 @@ def coo3_cuts(a_keys, b_keys, parts: int) -> list[tuple[int, int]]:
         cuts.append((x, y))
     cuts.append((na, nb))
     return cuts
+
+
+def csf3_keys(levels, dims) -> np.ndarray:
+    """int64 key ``(i * dims[1] + j) * dims[2] + k`` of every stored entry of a CSF3 tensor given
+    as (i_idx, j_ptr, j_idx, k_ptr, k_idx): the order the k level is stored in."""
+    i_idx, j_ptr, j_idx, k_ptr, k_idx = (_np(x).astype(np.int64) for x in levels)
+    i_of_j = np.repeat(i_idx, np.diff(j_ptr))
+    fibre = i_of_j * int(dims[1]) + j_idx
+    return np.repeat(fibre, np.diff(k_ptr)) * int(dims[2]) + k_idx
+
+
+def csf3_block(levels, val, k0: int, k1: int):
+    """The sub-tensor holding the k-level positions [k0, k1) of a CSF3 tensor, as
+    (i_idx, j_ptr, j_idx, k_ptr, k_idx, val) with offsets rebased to 0. The first and last
+    fibre (and slice) are clipped where the range cuts through them."""
+    i_idx, j_ptr, j_idx, k_ptr, k_idx = (_np(x) for x in levels)
+    val = _np(val)
+    if k1 <= k0:
+        z = np.zeros(0, np.int32)
+        return z, np.zeros(1, np.int32), z, np.zeros(1, np.int32), z, np.zeros(0, np.float32)
+    kp, jp = k_ptr.astype(np.int64), j_ptr.astype(np.int64)
+    j0 = int(np.searchsorted(kp, k0, side="right")) - 1          # fibre holding position k0
+    j1 = int(np.searchsorted(kp, k1 - 1, side="right"))           # one past the fibre holding k1 - 1
+    i0 = int(np.searchsorted(jp, j0, side="right")) - 1
+    i1 = int(np.searchsorted(jp, j1 - 1, side="right"))
+    new_kp = (np.clip(kp[j0:j1 + 1], k0, k1) - k0).astype(np.int32)
+    new_jp = (np.clip(jp[i0:i1 + 1], j0, j1) - j0).astype(np.int32)
+    return (i_idx[i0:i1].astype(np.int32), new_jp, j_idx[j0:j1].astype(np.int32), new_kp,
+            k_idx[k0:k1].astype(np.int32), val[k0:k1].astype(np.float32))
+
+
+def csf3_cuts(a_levels, b_levels, dims, parts: int) -> list[tuple[int, int]]:
+    """Cuts (x, y) of the k levels of two CSF3 tensors into ``parts`` ranges of about equal merged
+    length; a coordinate stored in both stays on one side of a cut."""
+    return coo3_cuts(csf3_keys(a_levels, dims), csf3_keys(b_levels, dims), parts)
+
+
+def csf3_seam(prev_block, block) -> tuple[int, int]:
+    """(shared_i, shared_j): 1 where ``block`` opens with the slice / fibre that ``prev_block``
+    closed with (that node is one node of the whole tensor), else 0."""
+    pi, _, pj = prev_block[0], prev_block[1], prev_block[2]
+    bi, _, bj = block[0], block[1], block[2]
+    if len(pi) == 0 or len(bi) == 0 or int(pi[-1]) != int(bi[0]):
+        return 0, 0
+    return 1, int(len(pj) > 0 and len(bj) > 0 and int(pj[-1]) == int(bj[0]))
+
+
+def concat_csf3_blocks(blocks):
+    """Host-side reassembly of the result blocks of a CSF3 add (each a tuple
+    (i_idx, j_ptr, j_idx, k_ptr, k_idx, val) over consecutive coordinate ranges) into one CSF3
+    tree: offsets are rebased and a slice / fibre cut by a block boundary is stored once."""
+    blocks = [tuple(_np(x) for x in b) for b in blocks if len(b[4])]
+    if not blocks:
+        z = np.zeros(0, np.int32)
+        return z, np.zeros(1, np.int32), z, np.zeros(1, np.int32), z, np.zeros(0, np.float32)
+    i_idx = np.zeros(0, np.int64)
+    j_cnt = np.zeros(0, np.int64)   # fibres per stitched slice
+    j_idx = np.zeros(0, np.int64)
+    k_cnt = np.zeros(0, np.int64)   # entries per stitched fibre
+    for n, b in enumerate(blocks):
+        bi, bj = b[0].astype(np.int64), b[2].astype(np.int64)
+        jc, kc = np.diff(b[1].astype(np.int64)), np.diff(b[3].astype(np.int64))
+        si, sj = csf3_seam(blocks[n - 1], b) if n else (0, 0)
+        if sj:   # the first fibre continues the previous block's last one
+            k_cnt[-1] += kc[0]
+            kc, bj = kc[1:], bj[1:]
+            jc[0] -= 1
+        if si:   # the first slice continues the previous block's last one
+            j_cnt[-1] += jc[0]
+            jc, bi = jc[1:], bi[1:]
+        i_idx, j_cnt = np.concatenate([i_idx, bi]), np.concatenate([j_cnt, jc])
+        j_idx, k_cnt = np.concatenate([j_idx, bj]), np.concatenate([k_cnt, kc])
+    ptr = lambda counts: np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    return (i_idx.astype(np.int32), ptr(j_cnt), j_idx.astype(np.int32), ptr(k_cnt),
+            np.concatenate([b[4] for b in blocks]).astype(np.int32), np.concatenate([b[5] for b in blocks]).astype(np.float32))
+
+
+def stitch_csf3(block, group=None, device=None):
+    """All-gathers, per result block of a CSF3 add, its node counts and its first and last
+    (i, j): returns (i_base, j_base, k_base, shared_i, shared_j) for this rank -- where its nodes
+    start in the stitched tree and whether its first slice / fibre is the previous block's last
+    one (then that node is not counted again) -- plus the stitched totals (n_i, n_j, n_k)."""
+    i_idx, _, j_idx, _, k_idx = (_np(x) for x in block[:5])
+    has = len(k_idx) > 0
+    mine = [len(i_idx), len(j_idx), len(k_idx),
+            int(i_idx[0]) if has else -1, int(j_idx[0]) if has else -1,
+            int(i_idx[-1]) if has else -1, int(j_idx[-1]) if has else -1]
+    if not dist.is_available() or not dist.is_initialized():
+        return (0, 0, 0, 0, 0), tuple(mine[:3])
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else "cpu"
+    t = torch.tensor(mine, dtype=torch.int64, device=device)
+    gathered = torch.empty(7 * world, dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(gathered, t, group=group)
+    rows = gathered.view(world, 7).cpu().tolist()
+    i_base = j_base = k_base = 0
+    last = None   # (i, j) that closed the latest non-empty block
+    out = None
+    for r, (ni, nj, nk, fi, fj, li, lj) in enumerate(rows):
+        si = int(nk > 0 and last is not None and last[0] == fi)
+        sj = int(si and last[1] == fj)
+        if r == rank:
+            out = (i_base - si, j_base - sj, k_base, si, sj)
+        i_base += ni - si
+        j_base += nj - sj
+        k_base += nk
+        if nk > 0:
+            last = (li, lj)
+    return out, (i_base, j_base, k_base)
 
 
 def stitch(rows_local: int, nnz_local: int, group=None, device=None):

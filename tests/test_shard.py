@@ -108,3 +108,76 @@ def test_sharded_add_equals_unsharded(tmp_path, oracle, world):
     want = oracle.csr_add(a, b, 4)
     assert_same(CSR(want.rows, want.cols, rp, col, val), want, "stitched blocks")
     assert bases == [int(x) for x in np.concatenate([[0], np.cumsum([b[0][-1] for b in blocks])])[:-1]]
+
+
+# ---- CSF3: cuts on the k level, blocks with clipped first / last fibres, seam-aware stitch ----
+
+def _csf3_pair(dims, n, seed):
+    from nacho_b200.nacho.convert import csf3_levels
+    rng = np.random.default_rng(seed)
+    draw = lambda m: np.unique(np.stack([rng.integers(0, e, m) for e in dims], axis=1), axis=0)
+    ca = draw(n)
+    cb = np.unique(np.concatenate([ca[rng.random(len(ca)) < 0.3], draw(n)]), axis=0)
+    out = []
+    for c in (ca, cb):
+        levels = [np.asarray(x, np.int32) for x in csf3_levels(c)]
+        out.append((levels, rng.uniform(-1, 1, len(c)).astype(np.float32)))
+    return out
+
+
+def _csf3_result_blocks(oracle, dims, a, b, parts):
+    from oracle.cpu_oracle import CSF3
+    (la, va), (lb, vb) = a, b
+    cuts = shard.csf3_cuts(la, lb, dims, parts)
+    blocks = []
+    for (x0, y0), (x1, y1) in zip(cuts, cuts[1:]):
+        z = oracle.csf3_add(CSF3(dims, *shard.csf3_block(la, va, x0, x1)), CSF3(dims, *shard.csf3_block(lb, vb, y0, y1)))
+        blocks.append((z.i_idx, z.j_ptr, z.j_idx, z.k_ptr, z.k_idx, z.val))
+    return blocks
+
+
+@pytest.mark.parametrize("dims,n", [((6, 5, 40), 300), ((50, 40, 30), 5000), ((3, 3, 2000), 3000), ((2000, 3, 3), 4000),
+                                    ((1, 1, 5000), 900)])
+def test_csf3_blocks_stitch_to_the_unsharded_tree(oracle, dims, n):
+    """Cuts through the middle of slices and fibres (few slices, many entries each) and cuts
+    that leave blocks empty (more parts than fibres) all reassemble to the unsharded result."""
+    from oracle.cpu_oracle import CSF3
+    a, b = _csf3_pair(dims, n, seed=sum(dims))
+    want = oracle.csf3_add(CSF3(dims, *a[0], a[1]), CSF3(dims, *b[0], b[1]))
+    for parts in (1, 2, 3, 8, 64):
+        got = shard.concat_csf3_blocks(_csf3_result_blocks(oracle, dims, a, b, parts))
+        for g, w, name in zip(got, (want.i_idx, want.j_ptr, want.j_idx, want.k_ptr, want.k_idx, want.val),
+                              ("i_idx", "j_ptr", "j_idx", "k_ptr", "k_idx", "val")):
+            assert np.array_equal(g, w), f"{dims} in {parts} parts: {name} differs"
+
+
+def _csf3_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        dims = (5, 7, 300)   # 5 slices over 3 ranks: every boundary cuts a slice, most cut a fibre
+        a, b = _csf3_pair(dims, 4000, seed=77)
+        block = _csf3_result_blocks(Oracle(), dims, a, b, world)[rank]
+        (i_base, j_base, k_base, si, sj), totals = shard.stitch_csf3(block)
+        np.savez(os.path.join(out_dir, f"csf{rank}.npz"), bases=[i_base, j_base, k_base, si, sj], totals=totals,
+                 **{f"b{n}": x for n, x in enumerate(block)})
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_csf3_stitch_bases_over_gloo(tmp_path, oracle, world):
+    mp.spawn(_csf3_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    files = [np.load(tmp_path / f"csf{r}.npz") for r in range(world)]
+    blocks = [tuple(f[f"b{n}"] for n in range(6)) for f in files]
+    whole = shard.concat_csf3_blocks(blocks)
+    for f in files:
+        assert tuple(int(x) for x in f["totals"]) == (len(whole[0]), len(whole[2]), len(whole[4]))
+    for r, (f, blk) in enumerate(zip(files, blocks)):
+        i_base, j_base, k_base, si, sj = (int(x) for x in f["bases"])
+        # the block's nodes sit at their bases in the stitched tree (a shared first node sits at the base itself)
+        assert np.array_equal(whole[0][i_base:i_base + len(blk[0])], blk[0])
+        assert np.array_equal(whole[2][j_base:j_base + len(blk[2])], blk[2])
+        assert np.array_equal(whole[4][k_base:k_base + len(blk[4])], blk[4])
+        assert (si, sj) == (shard.csf3_seam(blocks[r - 1], blk) if r else (0, 0))

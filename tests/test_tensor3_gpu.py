@@ -122,3 +122,25 @@ def test_too_wide_extents_are_refused(nacho):
     t = nacho.to_coo3(c, v, dims, "cuda")
     with pytest.raises(NachoB200Error):
         nacho.gpu_coo3d_add_f32(t, t)
+
+
+def test_csf3_blocks_through_the_gpu_operator(nacho):
+    """The multi-GPU decomposition of the CSF3 add, run block after block on one GPU: cuts on the
+    k level, clipped sub-trees through gpu_csf_add_f32, seam-aware reassembly; equals the
+    unsharded result bit-for-bit."""
+    import torch
+    from nacho_b200 import shard
+    dims = (9, 50, 400)
+    (ca, va), (cb, vb) = _seeded(dims, 60_000, 31)
+    la, lb = csf3_levels(ca), csf3_levels(cb)
+    whole = csf3_from_gpu(nacho.gpu_csf_add_f32(nacho.to_csf3(ca, va, dims, "cuda"), nacho.to_csf3(cb, vb, dims, "cuda")))
+    shape = torch.tensor(list(dims), dtype=torch.int32)
+    to_gpu = lambda blk: nacho.CSF3_gpu(*[torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in blk], shape)
+    for parts in (2, 5):
+        cuts = shard.csf3_cuts(la, lb, dims, parts)
+        blocks = []
+        for (x0, y0), (x1, y1) in zip(cuts, cuts[1:]):
+            z = csf3_from_gpu(nacho.gpu_csf_add_f32(to_gpu(shard.csf3_block(la, va, x0, x1)), to_gpu(shard.csf3_block(lb, vb, y0, y1))))
+            blocks.append((z.i_idx, z.j_ptr, z.j_idx, z.k_ptr, z.k_idx, z.val))
+        got = shard.concat_csf3_blocks(blocks)
+        assert_same(CSF3(dims, *got), whole, f"CSF3 in {parts} blocks")
