@@ -32,11 +32,16 @@ struct Workspace {
     void *dev = nullptr;
     size_t dev_bytes = 0;
     int64_t *host = nullptr;  // pinned, 64 int64 slots
+    uint64_t generation = 0;  // bumped by every acquire: a holder can tell whether the block was handed out again
 };
 
 // `slot` selects one of several independent blocks per (device, stream): a driver that keeps an
 // intermediate alive across calls into other drivers takes slot 1 for it.
 int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out, int slot = 0);
+
+// Counts the calls of nb200_release_workspaces(): a Workspace pointer obtained under an earlier
+// value is dangling.
+uint64_t workspace_epoch();
 
 // Carves 256-byte-aligned sub-blocks out of a Workspace.
 class Carver {

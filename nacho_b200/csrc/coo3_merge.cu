@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(NT) k_coo3_partition_fine(Coo3In A, Coo3In B, 
 // arrive / the scan warp waits ("the tile's count is known").
 using WorkerBar = NamedBarrier<1, NT>;
 using CountBar = NamedBarrier<2, NT + 32>;
+using LevelBar = NamedBarrier<3, NT + 32>;  // second hand-over to the scan warp (CSF3 levels)
 
 constexpr int RAW_SLOTS = CAP + 16;  // words per staged raw array (i, j, k, value)
 static_assert(RAW_SLOTS >= KEY_SLOTS, "packed keys reuse the raw i and j arrays");
@@ -147,13 +148,15 @@ __device__ __forceinline__ int head_elems(const void *p) {
     return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
 }
 
-template <int MODE>
+template <int MODE, bool CSF_OUT>
 __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, Coo3In B, Packing pk, Cuts2 cuts, int32_t *tile_count,
-                                                                 uint64_t *tile_state_raw, FusedCtl *ctl, Coo3Out Z) {
+                                                                 uint64_t *tile_state_raw, FusedCtl *ctl, Coo3Out Z,
+                                                                 CsfLevelsOut csf) {
+    static_assert(!CSF_OUT || MODE == MODE_FUSED, "the CSF3 levels are written by the single-pass launch only");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
-    __shared__ int s_tile;
-    __shared__ long long s_base;
+    __shared__ long long s_base, s_base_levels, s_levels;
+    __shared__ unsigned long long s_prev_key;
     __shared__ __align__(8) uint64_t mbar;
     __shared__ int s_total;
     constexpr bool WRITES = MODE != MODE_COUNT;
@@ -171,6 +174,17 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
     const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
     const int n = na + nb;
+    if (CSF_OUT && tid == NT - 1) {
+        // the coordinate that precedes the tile's first result entry: the larger of the last
+        // entries before the cut (a cut never separates equal coordinates); all-ones if none
+        uint64_t prev = INF;
+        if (a0 > 0) prev = key_at(A, pk, (int64_t)a0 - 1);
+        if (b0 > 0) {
+            const uint64_t pb = key_at(B, pk, (int64_t)b0 - 1);
+            prev = prev == INF ? pb : max(prev, pb);
+        }
+        s_prev_key = prev;
+    }
 
     // Shared layout, in 4-byte words: four raw arrays of RAW_SLOTS words each (i, j, k, value),
     // where A's entry e sits at word oa + e and B's at word ob + e, chosen so that 16-byte
@@ -258,6 +272,18 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
             if (bse >= 0 && t == (int)gridDim.x - 1) ctl->total = bse + total;
         }
         __syncthreads();
+        if (CSF_OUT) {
+            // second walk: slices and fibres of all earlier tiles (packed), while the workers store
+            volatile uint64_t *level_state = csf.tile_state;
+            const int64_t lv = t == 0 ? 0 : lookback_predecessors(level_state, t, &ctl->status, 1000);
+            LevelBar::sync();  // the workers have published the tile's packed count by now
+            const long long packed = s_levels;
+            if (lane_id() == 0) {
+                if (t > 0) st_relaxed_gpu(level_state + t, LB_PREFIX | (uint64_t)(lv < 0 ? 0 : lv + packed));
+                s_base_levels = lv;
+            }
+            __syncthreads();
+        }
         return;
     }
 
@@ -359,16 +385,84 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
             yi += !tx;
         }
     }
+    // ---- CSF3 levels above k, first half: thread t looks after the staged result entries
+    // [t VT, t VT + VT); bit q of `new_i` / `new_ij`: entry q opens a new i slice / a new (i, j)
+    // fibre. The tile's packed count goes out before the tile waits for anything.
+    const int e0 = tid * VT;
+    unsigned new_i = 0, new_ij = 0;
+    int rank_i = 0, rank_ij = 0;
+    if (CSF_OUT) {
+        WorkerBar::sync();  // the staged entries of the other workers are in place
+        const int mine_n = max(0, min(VT, total - e0));
+        const int sh_ij = pk.bk, sh_i = pk.bj + pk.bk;
+        uint64_t prev = e0 == 0 ? (uint64_t)s_prev_key : (mine_n > 0 ? out_key[e0 - 1] : 0ull);
+#pragma unroll
+        for (int q = 0; q < VT; ++q) {
+            if (q < mine_n) {
+                const uint64_t cur = out_key[e0 + q];
+                new_i |= (unsigned)((cur >> sh_i) != (prev >> sh_i)) << q;
+                new_ij |= (unsigned)((cur >> sh_ij) != (prev >> sh_ij)) << q;
+                prev = cur;
+            }
+        }
+        int tot_i, tot_ij;
+        block_excl_sum2<NT, WorkerBar>(__popc(new_i), __popc(new_ij), scan_tmp, rank_i, rank_ij, tot_i, tot_ij);
+        if (tid == 0) {
+            const long long packed = ((long long)tot_i << 31) | (long long)tot_ij;
+            st_relaxed_gpu(csf.tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)packed);
+            s_levels = packed;
+        }
+        __threadfence_block();
+        LevelBar::arrive();  // the scan warp turns the packed count into the tile's inclusive prefix
+    }
+
     // ---- output base of the tile (from the scan warp, or from the scanned counts)
     if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
     const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
-    if (base < 0) return;  // a bounded wait gave up; the host reports it
+    if (base < 0) {  // a bounded wait gave up; the host reports it
+        if (CSF_OUT) __syncthreads();  // the scan warp still waits at the levels barrier
+        return;
+    }
     for (int i = tid; i < total; i += NT) {
         const uint64_t kq = out_key[i];
-        Z.i[base + i] = pk.i_of(kq);
-        Z.j[base + i] = pk.j_of(kq);
+        if (!CSF_OUT) {
+            Z.i[base + i] = pk.i_of(kq);
+            Z.j[base + i] = pk.j_of(kq);
+        }
         Z.k[base + i] = pk.k_of(kq);
         Z.val[base + i] = out_val[i];
+    }
+    if (!CSF_OUT) return;
+
+    // ---- CSF3 levels above k, second half: slices / fibres of the earlier tiles, then the scatter
+    __syncthreads();
+    const long long levels_base = s_base_levels;
+    if (levels_base < 0) return;
+    int r = (int)(levels_base >> 31) + rank_i;
+    int f = (int)(levels_base & 0x7fffffff) + rank_ij;
+#pragma unroll
+    for (int q = 0; q < VT; ++q) {
+        if ((new_ij >> q) & 1u) {
+            const uint64_t cur = out_key[e0 + q];
+            if (f < csf.cap_j) {
+                csf.j_idx[f] = pk.j_of(cur);
+                csf.k_ptr[f] = (int32_t)(base + e0 + q);
+            }
+            if ((new_i >> q) & 1u) {
+                if (r < csf.cap_i) {
+                    csf.i_idx[r] = pk.i_of(cur);
+                    csf.j_ptr[r] = f;
+                }
+                ++r;
+            }
+            ++f;
+        }
+    }
+    if (t == (int)gridDim.x - 1 && tid == NT - 1) {  // the last worker of the last tile holds the totals
+        csf.totals->n_i = r;
+        csf.totals->n_j = f;
+        if (f <= csf.cap_j) csf.k_ptr[f] = (int32_t)(base + total);
+        if (r <= csf.cap_i) csf.j_ptr[r] = f;
     }
 }
 
@@ -380,10 +474,11 @@ int bits_for(int32_t extent) {
     return b;
 }
 
-template <int MODE>
+template <int MODE, bool CSF_OUT = false>
 cudaError_t launch_coo3_tile(const Coo3In &A, const Coo3In &B, const Packing &pk, const Cuts2 &cuts, int32_t *tile_count,
-                             uint64_t *tile_state, FusedCtl *ctl, const Coo3Out &Z, int num_tiles, cudaStream_t stream) {
-    auto kernel = k_coo3_tile<MODE>;
+                             uint64_t *tile_state, FusedCtl *ctl, const Coo3Out &Z, int num_tiles, cudaStream_t stream,
+                             const CsfLevelsOut &csf = CsfLevelsOut{}) {
+    auto kernel = k_coo3_tile<MODE, CSF_OUT>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -393,8 +488,8 @@ cudaError_t launch_coo3_tile(const Coo3In &A, const Coo3In &B, const Packing &pk
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     static const char *const names[3] = {"coo3_add_count", "coo3_add_fill", "coo3_add_fused"};
-    LaunchScope scope(names[MODE], stream);
-    kernel<<<num_tiles, NT + 32, coo3_smem_bytes(), stream>>>(A, B, pk, cuts, tile_count, tile_state, ctl, Z);
+    LaunchScope scope(CSF_OUT ? "coo3_add_fused_csf" : names[MODE], stream);
+    kernel<<<num_tiles, NT + 32, coo3_smem_bytes(), stream>>>(A, B, pk, cuts, tile_count, tile_state, ctl, Z, csf);
     return cudaGetLastError();
 }
 
@@ -413,6 +508,12 @@ int check_coo3(const nb200_coo3 *t) {
 // `scratch` / `host_slot`, when given, replace the library's pooled workspace (the caller then
 // owns a block of coo3_add_scratch_bytes() bytes and a pinned int64[8]); the CSF3 add uses this
 // to keep its own temporaries and this function's in one pool block.
+//
+// `csf`, when given, asks the single-pass launch to write the CSF3 levels above k instead of the
+// merged i and j columns (z->i and z->j may then be null); `*csf_done` tells whether that
+// happened (the count -> scan -> fill route does not do it).
+int64_t coo3_add_tiles(int64_t total_entries) { return (total_entries + (CAP - 1) - 1) / (CAP - 1); }
+
 size_t coo3_add_scratch_bytes(int64_t total_entries) {
     const int64_t tiles = (total_entries + (CAP - 1) - 1) / (CAP - 1);
     Carver sizes;
@@ -425,8 +526,9 @@ size_t coo3_add_scratch_bytes(int64_t total_entries) {
 }
 
 int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool alloc, int64_t capacity, void *stream_v,
-                 void *scratch, int64_t *host_slot) {
+                 void *scratch, int64_t *host_slot, const CsfLevelsOut *csf, bool *csf_done) {
     int st;
+    if (csf_done) *csf_done = false;
     if ((st = check_coo3(a)) || (st = check_coo3(b))) return st;
     if (!z || a->dims[0] != b->dims[0] || a->dims[1] != b->dims[1] || a->dims[2] != b->dims[2]) return NB200_E_BADARG;
     if (!alloc && capacity < 0) return NB200_E_BADARG;
@@ -442,7 +544,7 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     z->nnz = 0;
     if (alloc) z->i = z->j = z->k = nullptr, z->val = nullptr;
     if (num_tiles == 0) return NB200_OK;
-    if (!alloc && capacity > 0 && (!z->i || !z->j || !z->k || !z->val)) return NB200_E_BADARG;
+    if (!alloc && capacity > 0 && (!z->k || !z->val)) return NB200_E_BADARG;
 
     auto fail = [&](int code) {
         if (alloc) {
@@ -476,6 +578,8 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     const Packing pk{bj, bk};
     static const bool force_two_pass = [] { const char *e = std::getenv("NACHO_B200_TWO_PASS"); return e && e[0] == '1'; }();
     const bool fused = alloc || (capacity >= total && !force_two_pass);
+    const bool levels = fused && csf != nullptr && !alloc;
+    if (!levels && !alloc && capacity > 0 && (!z->i || !z->j)) return NB200_E_BADARG;
     cudaError_t e;
     if (fused) {
         e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream);
@@ -499,7 +603,12 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_coo3_partition"));
     const Coo3Out Z{z->i, z->j, z->k, z->val};
     if (fused) {
-        e = launch_coo3_tile<MODE_FUSED>(A, B, pk, cuts, nullptr, tile_state, ctl, Z, num_tiles, stream);
+        if (levels) {
+            e = launch_coo3_tile<MODE_FUSED, true>(A, B, pk, cuts, nullptr, tile_state, ctl, Z, num_tiles, stream, *csf);
+            if (csf_done) *csf_done = true;
+        } else {
+            e = launch_coo3_tile<MODE_FUSED>(A, B, pk, cuts, nullptr, tile_state, ctl, Z, num_tiles, stream);
+        }
         if (e != cudaSuccess) return fail(note_cuda_error(e, "k_coo3_tile<fused>"));
         e = cudaMemcpyAsync(host_slot, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
@@ -538,11 +647,11 @@ using namespace nb200;
 extern "C" {
 
 int nb200_coo3d_add_f32(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, int32_t, int32_t, void *stream) {
-    return coo3_add_run(a, b, z, true, 0, stream, nullptr, nullptr);
+    return coo3_add_run(a, b, z, true, 0, stream, nullptr, nullptr, nullptr, nullptr);
 }
 
 int nb200_coo3d_add_f32_into(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, int64_t capacity, void *stream) {
-    return coo3_add_run(a, b, z, false, capacity, stream, nullptr, nullptr);
+    return coo3_add_run(a, b, z, false, capacity, stream, nullptr, nullptr, nullptr, nullptr);
 }
 
 }  // extern "C"

@@ -20,8 +20,9 @@
 namespace nb200 {
 
 int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool alloc, int64_t capacity, void *stream_v,
-                 void *scratch, int64_t *host_slot);
+                 void *scratch, int64_t *host_slot, const CsfLevelsOut *csf, bool *csf_done);
 size_t coo3_add_scratch_bytes(int64_t total_entries);
+int64_t coo3_add_tiles(int64_t total_entries);
 
 namespace {
 
@@ -236,7 +237,7 @@ int csf_add_run(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, bool al
 
     // one pool block: expanded (i, j) of A, of B and of the merged list, the merge's own scratch
     // and the compress pass's control block and tile words
-    const int64_t compress_tiles = (total + NT * CVT - 1) / (NT * CVT);
+    const int64_t compress_tiles = std::max<int64_t>((total + NT * CVT - 1) / (NT * CVT), coo3_add_tiles(total));
     Carver sizes;
     sizes.take<int32_t>((size_t)a->n_k);
     sizes.take<int32_t>((size_t)a->n_k);
@@ -269,13 +270,32 @@ int csf_add_run(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, bool al
     nb200_coo3 ca{{a->dims[0], a->dims[1], a->dims[2]}, a->n_k, ai, aj, a->k_idx, a->val};
     nb200_coo3 cb{{b->dims[0], b->dims[1], b->dims[2]}, b->n_k, bi, bj, b->k_idx, b->val};
     nb200_coo3 cz{{0, 0, 0}, 0, zi, zj, z->k_idx, z->val};
-    if ((st = coo3_add_run(&ca, &cb, &cz, false, total, stream, merge_scratch, ws->host))) return fail(st);
-    const int32_t nnz = cz.nnz;
-    z->n_k = nnz;
-
     CompressCtl *ctl = reinterpret_cast<CompressCtl *>(compress_block);
     static_assert(sizeof(CompressCtl) <= 4 * sizeof(uint64_t), "control block must fit its slot");
     uint64_t *tile_state = compress_block + 4;
+
+    // single-pass route: the merge writes the levels above k itself (no merged i / j columns, no
+    // compress pass); its second look-back runs over `tile_state`, its totals land in ctl
+    e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)coo3_add_tiles(total) + 4), stream);
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
+    const CsfLevelsOut levels{z->i_idx, z->j_ptr, z->j_idx, z->k_ptr, (int32_t)std::min<int64_t>(cap_i, INT32_MAX),
+                              (int32_t)std::min<int64_t>(cap_j, INT32_MAX), tile_state, reinterpret_cast<CsfTotals *>(&ctl->n_i)};
+    bool levels_done = false;
+    if ((st = coo3_add_run(&ca, &cb, &cz, false, total, stream, merge_scratch, ws->host, &levels, &levels_done))) return fail(st);
+    const int32_t nnz = cz.nnz;
+    z->n_k = nnz;
+    if (levels_done) {
+        e = cudaMemcpyAsync(ws->host, ctl, sizeof(CompressCtl), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "read result lengths"));
+        CompressCtl h;
+        std::memcpy(&h, ws->host, sizeof(h));
+        z->n_i = h.n_i;
+        z->n_j = h.n_j;
+        if (h.n_i > cap_i || h.n_j > cap_j) return fail(NB200_E_CAPACITY);
+        return NB200_OK;
+    }
+
     const int tiles = (int)(((int64_t)nnz + NT * CVT - 1) / (NT * CVT));
     e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)tiles + 4), stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));

@@ -7,6 +7,7 @@
 // The reference has no such call (its operators take device tensors); this is the form of the
 // same operator for callers whose data starts and ends on the host.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -17,7 +18,16 @@ namespace nb200 {
 namespace {
 
 constexpr int SLOTS = 3;                      // block k+1 loading, k merging, k-1 draining
-constexpr int64_t BLOCK_ENTRIES = 12 << 20;   // operand entries per block (A + B)
+constexpr int64_t BLOCK_ENTRIES = 12 << 20;   // operand entries per block (A + B) unless NACHO_B200_HOST_BLOCK names another count
+
+int64_t block_entries() {
+    static const int64_t n = [] {
+        const char *e = std::getenv("NACHO_B200_HOST_BLOCK");
+        const long long v = e ? std::atoll(e) : 0;
+        return v >= 1024 ? (int64_t)v : BLOCK_ENTRIES;
+    }();
+    return n;
+}
 
 struct Pipeline {
     cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
@@ -78,14 +88,14 @@ int csr2_host(into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b,
     z->row_ptr[0] = 0;
     if (rows == 0) return NB200_OK;
 
-    // ---- row blocks of about BLOCK_ENTRIES operand entries
+    // ---- row blocks of about block_entries() operand entries
     std::vector<Block> blocks;
     int64_t max_a = 0, max_b = 0;
     int32_t max_rows = 0;
     for (int32_t r = 0; r < rows;) {
         int32_t e = r;
         const int64_t start = (int64_t)arp[r] + brp[r];
-        while (e < rows && ((int64_t)arp[e + 1] + brp[e + 1]) - start <= BLOCK_ENTRIES) ++e;
+        while (e < rows && ((int64_t)arp[e + 1] + brp[e + 1]) - start <= block_entries()) ++e;
         if (e == r) e = r + 1;  // a single row larger than a block still goes through whole
         Block blk{r, e, arp[r], arp[e], brp[r], brp[e]};
         blocks.push_back(blk);

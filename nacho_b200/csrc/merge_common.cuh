@@ -23,6 +23,22 @@ struct FusedCtl {
     long long total;      // result entries, written by the last tile
 };
 
+// Optional second result form of the coordinate merge: the CSF3 levels above k. When a fused
+// launch of the COO3 tile kernel is given one of these, it does not write the merged i and j
+// columns; instead every tile flags the result entries that open a new i slice or a new (i, j)
+// fibre, obtains the number of slices / fibres of all earlier tiles by a second bounded look-back
+// (packed as slices << 31 | fibres in `tile_state`, one zeroed word per tile), and writes
+// i_idx / j_ptr / j_idx / k_ptr directly. The last tile leaves the totals in `totals`.
+struct CsfTotals {
+    int n_i, n_j;
+};
+struct CsfLevelsOut {
+    int32_t *i_idx, *j_ptr, *j_idx, *k_ptr;
+    int32_t cap_i, cap_j;  // entries the arrays can hold (offset arrays: one more)
+    uint64_t *tile_state;
+    CsfTotals *totals;
+};
+
 // Exclusive prefix of the per-tile counts, in place, by one CTA; the grand total goes to
 // *total_out (64-bit so that the host can detect int32 overflow).
 static __global__ void __launch_bounds__(1024) k_scan_tiles(int32_t *counts, int32_t n, int64_t *total_out) {

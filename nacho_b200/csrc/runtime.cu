@@ -20,6 +20,7 @@ std::atomic<uint64_t> g_launches{0};
 std::atomic<int> g_profile_on{0};
 
 std::mutex g_ws_mutex;
+std::atomic<uint64_t> g_ws_epoch{0};
 std::map<std::pair<std::pair<int, int>, cudaStream_t>, Workspace> g_workspaces;
 
 struct TimedLaunch {
@@ -85,9 +86,12 @@ int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out, int sl
         NB200_CUDA(cudaMalloc(&ws.dev, want));
         ws.dev_bytes = want;
     }
+    ++ws.generation;
     *out = &ws;
     return NB200_OK;
 }
+
+uint64_t workspace_epoch() { return g_ws_epoch.load(std::memory_order_acquire); }
 
 LaunchScope::LaunchScope(const char *name, cudaStream_t stream)
     : name_(name), stream_(stream), start_(nullptr), timed_(g_profile_on.load(std::memory_order_relaxed) != 0) {
@@ -150,6 +154,7 @@ int nb200_release_workspaces(void) {
         if (kv.second.host) cudaFreeHost(kv.second.host);
     }
     g_workspaces.clear();
+    g_ws_epoch.fetch_add(1, std::memory_order_release);
     cudaSetDevice(prev);
     return NB200_OK;
 }

@@ -23,6 +23,7 @@
 #include <algorithm>
 #include <climits>
 #include <cstring>
+#include <mutex>
 
 #include "merge_common.cuh"
 
@@ -434,11 +435,15 @@ __global__ void __launch_bounds__(256) k_esc_window_ptr(CsrView B, int32_t b_row
 // `row_list` is read from the front for the first n_front CTAs and from the back (list_len - 1
 // downwards) for the others. `words`: bitmap words in use, a multiple of NT that covers a window.
 // `win_ptr` is the window pointer table, or null (one window, or a table beyond its budget).
+// `cache` (one window only), when given, carries the bitmaps from the symbolic launch to the
+// numeric launch of one call, `words` per CTA: the symbolic launch stores them, the numeric
+// launch loads them instead of walking the products a first time.
 template <bool NUMERIC, typename RankT, int NT>
 __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const int32_t *__restrict__ win_ptr, int n_win,
                                                    const int32_t *__restrict__ row_list, int32_t list_len, int n_front, int words,
-                                                   int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
-                                                   int32_t *__restrict__ c_col, float *__restrict__ c_val) {
+                                                   uint32_t *cache, int32_t *__restrict__ row_count,
+                                                   const int32_t *__restrict__ c_rp, int32_t *__restrict__ c_col,
+                                                   float *__restrict__ c_val) {
     extern __shared__ __align__(16) unsigned char rk_smem[];
     uint32_t *bitmap = reinterpret_cast<uint32_t *>(rk_smem);
     RankT *rank = reinterpret_cast<RankT *>(rk_smem + (size_t)words * 4);
@@ -516,13 +521,22 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
             return any;
         };
 
-        for (int c = tid; c < words / 4; c += NT) reinterpret_cast<uint4 *>(bitmap)[c] = make_uint4(0u, 0u, 0u, 0u);
-        __syncthreads();
-        const bool any = pass(true, [&](int32_t col, float) {
-            const uint32_t cw = (uint32_t)(col - c_first);
-            atomicOr(bitmap + (cw >> 5), 1u << (cw & 31u));
-        });
-        if (!any) continue;  // uniform
+        uint4 *cached = cache ? reinterpret_cast<uint4 *>(cache + (size_t)r * words) : nullptr;
+        const bool from_cache = NUMERIC && cached != nullptr;
+        if (from_cache) {
+            for (int c = tid; c < words / 4; c += NT) reinterpret_cast<uint4 *>(bitmap)[c] = __ldcs(cached + c);
+            __syncthreads();
+        } else {
+            for (int c = tid; c < words / 4; c += NT) reinterpret_cast<uint4 *>(bitmap)[c] = make_uint4(0u, 0u, 0u, 0u);
+            __syncthreads();
+            const bool any = pass(true, [&](int32_t col, float) {
+                const uint32_t cw = (uint32_t)(col - c_first);
+                atomicOr(bitmap + (cw >> 5), 1u << (cw & 31u));
+            });
+            if (!any) continue;  // uniform
+            if (!NUMERIC && cached)
+                for (int c = tid; c < words / 4; c += NT) __stcs(cached + c, reinterpret_cast<const uint4 *>(bitmap)[c]);
+        }
 
         // warp v looks after its share of the words, lane = word within groups of 32
         const int groups = words / NT;
@@ -555,7 +569,7 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
         for (int k = tid; k < cnt; k += NT) c_val[out + k] = 0.f;
         __syncthreads();  // ranks complete, output zeroed (the reductions below come from this CTA only)
         float *row_val = c_val + out;  // the window's part of the row; its length fits 32 bits
-        pass(!one_chunk, [&](int32_t col, float v) {
+        pass(!one_chunk || from_cache, [&](int32_t col, float v) {
             const uint32_t cw = (uint32_t)(col - c_first);
             const uint32_t bits = bitmap[cw >> 5];
             atomicAdd(row_val + ((uint32_t)rank[cw >> 5] + __popc(bits & ((1u << (cw & 31u)) - 1u))), v);
@@ -575,6 +589,14 @@ __global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restri
 
 // ------------------------------------------------------------------------ host driver ----
 
+// Bitmap words a CTA of NT threads keeps for B's column count (one window's worth at most).
+template <int NT>
+int ranked_words(int32_t b_cols) {
+    const int64_t window_cols = std::min<int64_t>(b_cols, RK_WINDOW_COLS);
+    return (int)((((window_cols + 31) / 32 + NT - 1) / NT) * NT);
+}
+
+
 int check_operand(const nb200_csr *m) {
     if (!m || m->rows < 0 || m->cols < 0 || m->nnz < 0 || !m->row_ptr) return NB200_E_BADARG;
     if (m->nnz > 0 && (!m->col || !m->val)) return NB200_E_BADARG;
@@ -590,13 +612,17 @@ struct EscPlan {
     EscCtl *ctl;
     int n_win;             // column windows of RK_WINDOW_COLS
     int32_t *win_ptr;      // window pointer table (null: one window, or beyond its budget)
+    uint32_t *cache_ranked, *cache_heavy;  // bitmaps carried from the symbolic to the numeric pass (or null)
+    Workspace *cache_ws;   // pool block of the bitmaps (null without them)
     EscCtl host;           // counters read back after the row-work kernel
 };
 
 // Bins the rows (kernel + one read-back) and carves the scratch of a symbolic pass, a numeric
 // pass, or one after the other. `counts`: rows without products get their count written
 // (needed by the symbolic pass).
-int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, cudaStream_t stream, EscPlan *plan) {
+constexpr size_t BITMAP_CACHE_BUDGET = size_t(8) << 30;  // bytes of bitmaps carried between the passes of one call
+
+int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, bool carry_bitmaps, cudaStream_t stream, EscPlan *plan) {
     const int32_t rows = a->rows;
     const int64_t n_win = std::max<int64_t>(1, ((int64_t)b->cols + RK_WINDOW_COLS - 1) / RK_WINDOW_COLS);
     const size_t ptr_entries = n_win > 1 ? (size_t)b->rows * (size_t)(n_win + 1) : 0;
@@ -637,19 +663,41 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, cudaStream_
         k_esc_window_ptr<<<(unsigned)((ptr_entries + 255) / 256), 256, 0, stream>>>(B, b->rows, plan->n_win, plan->win_ptr);
         NB200_CUDA(cudaGetLastError());
     }
+    plan->cache_ranked = plan->cache_heavy = nullptr;
+    plan->cache_ws = nullptr;
+    if (carry_bitmaps && plan->n_win == 1) {
+        // a second pool block: its size is only known now, and the first must not move
+        const size_t ranked_bytes = (size_t)plan->host.n_ranked * ranked_words<RK_NT>(b->cols) * 4;
+        const size_t heavy_bytes = ((size_t)plan->host.n_giant + plan->host.n_heavy) * ranked_words<HEAVY_NT>(b->cols) * 4;
+        if (ranked_bytes + heavy_bytes > 0 && ranked_bytes + heavy_bytes <= BITMAP_CACHE_BUDGET) {
+            Carver cache_sizes;
+            cache_sizes.take<uint32_t>(ranked_bytes / 4);
+            cache_sizes.take<uint32_t>(heavy_bytes / 4);
+            Workspace *cache_ws = nullptr;
+            const int cache_st = acquire_workspace(stream, cache_sizes.used(), &cache_ws, 3);
+            if (cache_st == NB200_OK) {  // without room the numeric pass walks the products twice, as it does on its own
+                Carver cache_carve(cache_ws->dev);
+                plan->cache_ranked = ranked_bytes ? cache_carve.take<uint32_t>(ranked_bytes / 4) : nullptr;
+                plan->cache_heavy = heavy_bytes ? cache_carve.take<uint32_t>(heavy_bytes / 4) : nullptr;
+                plan->cache_ws = cache_ws;
+            } else if (cache_st != NB200_E_NOMEM) {
+                return cache_st;
+            }
+        }
+    }
     return NB200_OK;
 }
 
 template <bool NUMERIC, typename RankT, int NT>
 int launch_ranked(const CsrView &A, const CsrView &B, const EscPlan &plan, int32_t b_cols, const int32_t *list, int32_t list_len,
-                  int n_front, int n_rows, int32_t *count, const int32_t *c_rp, int32_t *c_col, float *c_val, cudaStream_t stream) {
-    const int64_t window_cols = std::min<int64_t>(b_cols, RK_WINDOW_COLS);
-    const int words = (int)((((window_cols + 31) / 32 + NT - 1) / NT) * NT);
+                  int n_front, int n_rows, uint32_t *cache, int32_t *count, const int32_t *c_rp, int32_t *c_col, float *c_val,
+                  cudaStream_t stream) {
+    const int words = ranked_words<NT>(b_cols);
     const size_t smem = (size_t)words * (4 + sizeof(RankT));
     NB200_CUDA(cudaFuncSetAttribute(k_esc_ranked<NUMERIC, RankT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)((size_t)RK_WORDS * (4 + sizeof(RankT)))));
-    k_esc_ranked<NUMERIC, RankT, NT><<<n_rows, NT, smem, stream>>>(A, B, plan.win_ptr, plan.n_win, list, list_len, n_front, words, count,
-                                                                   c_rp, c_col, c_val);
+    k_esc_ranked<NUMERIC, RankT, NT><<<n_rows, NT, smem, stream>>>(A, B, plan.win_ptr, plan.n_win, list, list_len, n_front, words, cache,
+                                                                   count, c_rp, c_col, c_val);
     NB200_CUDA(cudaGetLastError());
     return NB200_OK;
 }
@@ -666,13 +714,13 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
     if (n_heavy > 0) {  // first: the heaviest rows take longest
         LaunchScope scope(NUMERIC ? "esc_heavy_numeric" : "esc_heavy_symbolic", stream);
         if ((st = launch_ranked<NUMERIC, uint32_t, HEAVY_NT>(A, B, plan, b->cols, plan.lists.heavy_rows, a->rows, plan.host.n_giant, n_heavy,
-                                                             count, c_rp, c_col, c_val, stream)))
+                                                             plan.cache_heavy, count, c_rp, c_col, c_val, stream)))
             return st;
     }
     if (plan.host.n_ranked > 0) {
         LaunchScope scope(NUMERIC ? "esc_ranked_numeric" : "esc_ranked_symbolic", stream);
         if ((st = launch_ranked<NUMERIC, uint16_t, RK_NT>(A, B, plan, b->cols, plan.lists.ranked_rows, a->rows, plan.host.n_ranked,
-                                                          plan.host.n_ranked, count, c_rp, c_col, c_val, stream)))
+                                                          plan.host.n_ranked, plan.cache_ranked, count, c_rp, c_col, c_val, stream)))
             return st;
     }
     if (plan.host.n_medium > 0) {
@@ -692,6 +740,49 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
     return NB200_OK;
 }
 
+// The plan of the latest symbolic pass, kept for the numeric pass that normally follows it on the
+// same operands: the bins, the window pointer table and the bitmaps are then not computed again.
+// It is used only if the operand arrays, sizes, device and stream are the same and neither pool
+// block was handed out to anyone in between (their generations are unchanged).
+struct SavedPlan {
+    bool valid = false;
+    EscPlan plan{};
+    const void *a_rp = nullptr, *a_col = nullptr, *b_rp = nullptr, *b_col = nullptr;
+    int32_t a_rows = 0, a_nnz = 0, b_rows = 0, b_cols = 0, b_nnz = 0;
+    cudaStream_t stream = nullptr;
+    int device = -1;
+    uint64_t gen_main = 0, gen_cache = 0, epoch = 0;
+};
+std::mutex g_saved_mutex;
+SavedPlan g_saved;
+
+void save_plan(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, cudaStream_t stream) {
+    std::lock_guard<std::mutex> g(g_saved_mutex);
+    g_saved.valid = cudaGetDevice(&g_saved.device) == cudaSuccess;
+    g_saved.plan = plan;
+    g_saved.a_rp = a->row_ptr, g_saved.a_col = a->col, g_saved.b_rp = b->row_ptr, g_saved.b_col = b->col;
+    g_saved.a_rows = a->rows, g_saved.a_nnz = a->nnz, g_saved.b_rows = b->rows, g_saved.b_cols = b->cols, g_saved.b_nnz = b->nnz;
+    g_saved.stream = stream;
+    g_saved.epoch = workspace_epoch();
+    g_saved.gen_main = plan.ws->generation;
+    g_saved.gen_cache = plan.cache_ws ? plan.cache_ws->generation : 0;
+}
+
+bool take_saved_plan(const nb200_csr *a, const nb200_csr *b, cudaStream_t stream, EscPlan *out) {
+    std::lock_guard<std::mutex> g(g_saved_mutex);
+    int dev = -1;
+    if (!g_saved.valid || g_saved.epoch != workspace_epoch()) return false;  // the pool blocks may be gone
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != g_saved.device || stream != g_saved.stream) return false;
+    if (a->row_ptr != g_saved.a_rp || a->col != g_saved.a_col || b->row_ptr != g_saved.b_rp || b->col != g_saved.b_col) return false;
+    if (a->rows != g_saved.a_rows || a->nnz != g_saved.a_nnz || b->rows != g_saved.b_rows || b->cols != g_saved.b_cols ||
+        b->nnz != g_saved.b_nnz)
+        return false;
+    if (g_saved.plan.ws->generation != g_saved.gen_main) return false;
+    if (g_saved.plan.cache_ws && g_saved.plan.cache_ws->generation != g_saved.gen_cache) return false;
+    *out = g_saved.plan;
+    return true;
+}
+
 // `keep`: if given, the plan is handed back, so that a numeric pass that follows at once
 // (nothing else touching the stream's scratch in between) skips the binning.
 int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_t *products, void *stream_v, EscPlan *keep = nullptr) {
@@ -708,7 +799,7 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
         return NB200_OK;
     }
     EscPlan plan{};
-    if ((st = esc_prepare(a, b, true, stream, &plan))) return st;
+    if ((st = esc_prepare(a, b, true, true, stream, &plan))) return st;
     if (keep) *keep = plan;
     if (products) *products = (int64_t)plan.host.products;
     if ((st = esc_run_bins<false>(a, b, plan, nullptr, stream))) return st;
@@ -732,6 +823,7 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
     const int64_t nnz = h.total;
     if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
     c->nnz = (int32_t)nnz;
+    save_plan(a, b, plan, stream);
     return NB200_OK;
 }
 
@@ -744,7 +836,8 @@ int spgemm_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, void *s
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (kept) return esc_run_bins<true>(a, b, *kept, c, stream);
     EscPlan plan{};
-    if ((st = esc_prepare(a, b, false, stream, &plan))) return st;
+    if (take_saved_plan(a, b, stream, &plan)) return esc_run_bins<true>(a, b, plan, c, stream);
+    if ((st = esc_prepare(a, b, false, false, stream, &plan))) return st;
     return esc_run_bins<true>(a, b, plan, c, stream);
 }
 

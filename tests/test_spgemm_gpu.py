@@ -216,3 +216,40 @@ def test_symbolic_reports_products(nacho, oracle):
     ck(lib.nb200_spgemm_f32_symbolic(C.byref(sa), C.byref(sb), C.byref(c), C.byref(p), None), "symbolic")
     assert p.value == products and c.nnz == len(want.col)
     assert np.array_equal(rp.cpu().numpy(), want.row_ptr)
+
+
+def test_numeric_after_other_work_on_the_stream(nacho, oracle):
+    """The numeric pass reuses what the symbolic pass left in the scratch pool only if nothing
+    else used the pool in between; here a CSR add runs between the two passes, and a numeric
+    pass is also repeated with new values in A (same structure)."""
+    import ctypes as C
+    import torch
+    from nacho_b200 import synth
+    from nacho_b200._capi import CsrStruct, check as ck, lib
+    ta = synth.rmat_csr(scale=10, seed=4110)
+    tb = synth.transpose_csr(ta)
+    a, b = synth_csr(ta), synth_csr(tb)
+    want, v64, abs64, _ = oracle.spgemm(a, b, 8, extras=True)
+    ga, gb = synth_to_gpu(ta), synth_to_gpu(tb)
+    sa, sb = ga._struct(), gb._struct()
+    rp = torch.empty(a.rows + 1, dtype=torch.int32, device="cuda")
+    c = CsrStruct(0, 0, 0, rp.data_ptr(), None, None)
+    ck(lib.nb200_spgemm_f32_symbolic(C.byref(sa), C.byref(sb), C.byref(c), None, None), "symbolic")
+    nacho.gpu_csr_add_f32(ga, ga)                      # takes the scratch pool in between
+    col = torch.empty(c.nnz, dtype=torch.int32, device="cuda")
+    val = torch.empty(c.nnz, dtype=torch.float32, device="cuda")
+    c.col, c.val = col.data_ptr(), val.data_ptr()
+    ck(lib.nb200_spgemm_f32_numeric(C.byref(sa), C.byref(sb), C.byref(c), None), "numeric")
+    torch.cuda.synchronize()
+    assert np.array_equal(rp.cpu().numpy(), want.row_ptr) and np.array_equal(col.cpu().numpy(), want.col)
+    assert np.all(np.abs(val.cpu().numpy().astype(np.float64) - v64) <= REL_TOL * abs64 + 1e-30)
+
+    # symbolic again, then two numeric passes: the second with A's values doubled in place
+    ck(lib.nb200_spgemm_f32_symbolic(C.byref(sa), C.byref(sb), C.byref(c), None, None), "symbolic")
+    c.col, c.val = col.data_ptr(), val.data_ptr()
+    ck(lib.nb200_spgemm_f32_numeric(C.byref(sa), C.byref(sb), C.byref(c), None), "numeric")
+    ga.values.mul_(2.0)
+    ck(lib.nb200_spgemm_f32_numeric(C.byref(sa), C.byref(sb), C.byref(c), None), "numeric")
+    torch.cuda.synchronize()
+    assert np.array_equal(col.cpu().numpy(), want.col)
+    assert np.all(np.abs(val.cpu().numpy().astype(np.float64) - 2.0 * v64) <= 2.0 * REL_TOL * abs64 + 1e-30)
