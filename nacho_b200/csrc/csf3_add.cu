@@ -3,15 +3,18 @@
 // (src/backend/compute.cpp:619-1392 with the runtime-exclusion partition of
 // src/backend/partition.cpp:286-328, 586-811): merge the i lists, under equal i merge the j
 // fibres, under equal (i, j) merge k, otherwise copy the subtree. The result is the unique
-// canonical tree of the union of the coordinate sets, so it is produced here in three steps
-// that reuse the flat coordinate merge:
-//   1. k_csf_expand    every stored entry gets its (i, j) written out next to its k: one thread
-//                      per (i, j) fibre finds its i by binary search and fills the fibre's range;
+// canonical tree of the union of the coordinate sets, so it is produced here from the flat
+// coordinate merge:
+//   1. k_csf_expand    every stored entry gets its (i, j) written out next to its k: one warp
+//                      per 32 (i, j) fibres finds their i by binary search and fills their ranges;
 //   2. coo3_add_run    the sorted-union merge of the two coordinate lists (coo3_merge.cu); k and
-//                      the values go straight into the result's k_idx / val arrays;
-//   3. k_csf_compress  one pass over the merged (i, j) columns: head flags for new i and new
-//                      (i, j), a packed two-counter scan across tiles by bounded look-back, and
-//                      the scatter of i_idx / j_ptr / j_idx / k_ptr.
+//                      the values go straight into the result's k_idx / val arrays. On its
+//                      single-pass route the merge also writes i_idx / j_ptr / j_idx / k_ptr
+//                      itself (CsfLevelsOut) and nothing else is left to do;
+//   3. k_csf_compress  only after the count -> scan -> fill route of the merge: one pass over
+//                      the merged (i, j) columns: head flags for new i and new (i, j), a packed
+//                      two-counter scan across tiles by bounded look-back, and the scatter of
+//                      i_idx / j_ptr / j_idx / k_ptr.
 #include <algorithm>
 #include <cstring>
 
