@@ -46,7 +46,7 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per algorithmic byte of one launch
 # of a kernel, from one ncu capture of a reduced case each (profiles/*.md give the commands);
 # traffic grows in proportion to the entries, so the ratio is applied to the full launch.
-TRAFFIC_PER_ALGORITHMIC_BYTE = {"csr_add_fused": 0.877, "coo3_add_fused": 0.92}
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"csr_add_fused": 0.816, "coo3_add_fused": 0.92}
 
 
 def measured_peaks():

@@ -33,8 +33,8 @@ constexpr int NT = 256;
 
 // One warp per 32 consecutive (i, j) fibres. Each lane looks up its fibre's i (the last
 // fibre-list start <= q, by binary search) and j; the warp then walks the entries of its 32
-// fibres together, each lane finding the fibre of its entry among the 32 starts by shuffles,
-// so that the writes are coalesced however short the fibres are.
+// fibres together, 32 entries at a time, each lane taking the (i, j) of its entry's fibre from
+// the lane that holds it, so that the writes are coalesced however short the fibres are.
 __global__ void __launch_bounds__(NT) k_csf_expand(int32_t n_i, int32_t n_j, const int32_t *__restrict__ i_idx,
                                                    const int32_t *__restrict__ j_ptr, const int32_t *__restrict__ j_idx,
                                                    const int32_t *__restrict__ k_ptr, int32_t *__restrict__ out_i,
@@ -57,16 +57,27 @@ __global__ void __launch_bounds__(NT) k_csf_expand(int32_t n_i, int32_t n_j, con
     }
     const int32_t p_begin = __shfl_sync(FULL_MASK, start, 0);
     const int32_t p_end = ld_nc(k_ptr + min(q0 + 32, n_j));
+    // Within a block of 32 entries the fibre starts form a bit mask, and an entry's fibre is the
+    // number of fibres started at or before it. An empty fibre shares its start with its
+    // successor; a block that sees one falls back to a search over the 32 starts by shuffles.
     for (int32_t base = p_begin; base < p_end; base += 32) {
+        const int32_t rel = start - base;  // INT32_MAX - base for lanes past the last fibre: never in range
+        const bool in_block = rel >= 0 && rel < 32;
+        const int started = __popc(__ballot_sync(FULL_MASK, rel < 0));  // fibres that start before the block
+        const unsigned starts = __reduce_or_sync(FULL_MASK, in_block ? 1u << rel : 0u);
         const int32_t p = base + lane;
-        int lo = 0, hi = 31;  // largest lane whose fibre starts at or before p
+        int f = started + __popc(starts & (0xffffffffu >> (31 - lane))) - 1;
+        if (__popc(__ballot_sync(FULL_MASK, in_block)) != __popc(starts)) {  // uniform: an empty fibre in the block
+            int lo = 0, hi = 31;  // largest lane whose fibre starts at or before p
 #pragma unroll
-        for (int step = 0; step < 5; ++step) {
-            const int mid = (lo + hi + 1) >> 1;
-            const int32_t sm = __shfl_sync(FULL_MASK, start, mid);
-            if (sm <= p) lo = mid; else hi = mid - 1;
+            for (int step = 0; step < 5; ++step) {
+                const int mid = (lo + hi + 1) >> 1;
+                const int32_t sm = __shfl_sync(FULL_MASK, start, mid);
+                if (sm <= p) lo = mid; else hi = mid - 1;
+            }
+            f = lo;
         }
-        const int32_t vi = __shfl_sync(FULL_MASK, i, lo), vj = __shfl_sync(FULL_MASK, j, lo);
+        const int32_t vi = __shfl_sync(FULL_MASK, i, f), vj = __shfl_sync(FULL_MASK, j, f);
         if (p < p_end) {
             out_i[p] = vi;
             out_j[p] = vj;
