@@ -413,8 +413,8 @@ def main():
 
     def step():
         z = op_fn(*tensors)
-        if world > 1:  # stitch: every block's (rows, nnz) -> global row-offset bases
-            shard.stitch(rows_local, z.values.numel(), device=dev)
+        if world > 1:  # stitch: every block's (rows, nnz) -> global row-offset bases, left on the device
+            shard.stitch_on_device(rows_local, z.values.numel(), device=dev)
         return z
 
     def barrier():

@@ -201,6 +201,21 @@ def stitch_csf3(block, group=None, device=None):
     return out, (i_base, j_base, k_base)
 
 
+def stitch_on_device(rows_local: int, nnz_local: int, group=None, device=None):
+    """The same exchange as ``stitch`` without a host read-back: returns (bases, counts), two
+    int64 device tensors of shape (2,) and (world, 2): this rank's (row_base, nnz_base) and every
+    block's (rows, nnz). A consumer that adds the bases to the block's row offsets on the device
+    never has to wait for them on the host."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else "cpu"
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    mine = torch.tensor([rows_local, nnz_local], dtype=torch.int64, device=device)
+    gathered = torch.empty(2 * world, dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(gathered, mine, group=group)
+    counts = gathered.view(world, 2)
+    return counts[:rank].sum(dim=0), counts
+
+
 def stitch(rows_local: int, nnz_local: int, group=None, device=None):
     """All-gathers (rows, nnz) of every block. Returns (row_base, nnz_base, rows_all, nnz_all):
     this rank's global first row and the amount to add to its local row offsets, plus the

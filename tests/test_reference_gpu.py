@@ -120,3 +120,35 @@ def test_spgemm_laplacian_and_rmat(nacho, ref_gpu, oracle):
     check_spgemm(nacho, ref_gpu, oracle, lap, lap)
     ta = synth.rmat_csr(scale=11, seed=4011)
     check_spgemm(nacho, ref_gpu, oracle, ta, synth.transpose_csr(ta))
+
+
+def test_randomised_shapes_against_the_reference_gpu_kernels(nacho, ref_gpu):
+    """Forty seeded draws of shape, density and row skew through all four CSR kernels of both
+    sides: index arrays equal, add / multiply values bit-equal, SpGEMM values close (both sides
+    sum in no fixed order). Operands are kept non-empty."""
+    import torch
+    from nacho_b200 import synth
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        rows = int(rng.integers(1, 3000))
+        cols = int(rng.integers(2, 3000))
+        density = float(rng.choice([0.002, 0.01, 0.05, 0.2])) if rows * cols > 4000 else 0.3
+        if case % 3 == 0:   # skewed rows: lognormal lengths
+            lengths = np.minimum(np.round(rng.lognormal(0, 2.0, rows) * density * cols).astype(np.int64), cols)
+        else:
+            lengths = rng.binomial(cols, density, rows)
+        lengths[int(rng.integers(0, rows))] = max(1, int(lengths.max()))   # at least one stored entry
+        ops = [dev(synth.csr_from_lengths(np.maximum(lengths if k == 0 else rng.permutation(lengths), 0), cols, 100 * case + k))
+               for k in range(3)]
+        ga, gb, gc = (as_csr_gpu(nacho, t) for t in ops)
+        same_csr(nacho.gpu_csr_add_f32(ga, gb), ref_gpu.csr_add(ops[0], ops[1]))
+        same_csr(nacho.gpu_csr_mul_f32(ga, gb), ref_gpu.csr_mul(ops[0], ops[1]))
+        same_csr(nacho.gpu_csr_add_3_f32(ga, gb, gc), ref_gpu.csr_add_3(*ops))
+        if case % 2 == 0:   # C = A * B^T-shaped product: B gets `cols` rows
+            tb = dev(synth.random_csr(cols, int(rng.integers(2, 2000)), float(rng.choice([0.005, 0.03])) , 7000 + case))
+            if tb[3].numel() == 0:
+                continue
+            got = nacho.gpu_spgemm_f32(ga, as_csr_gpu(nacho, tb))
+            want = ref_gpu.spgemm(ops[0], tb)
+            same_csr(got, want, exact_values=False)
+            assert torch.allclose(got.values, want[4], rtol=1e-4, atol=1e-5)

@@ -81,6 +81,8 @@ def _worker(rank, world, port, out_dir):
         z = oracle.csr_add(blocks[0], blocks[1], 2)
         row_base, nnz_base, rows_all, nnz_all = shard.stitch(z.rows, len(z.col))
         assert row_base == r0 and sum(rows_all) == 2048
+        bases, counts = shard.stitch_on_device(z.rows, len(z.col))
+        assert bases.tolist() == [row_base, nnz_base] and counts[:, 0].tolist() == rows_all and counts[:, 1].tolist() == nnz_all
         np.savez(os.path.join(out_dir, f"block{rank}.npz"), rp=z.row_ptr, col=z.col, val=z.val,
                  row_base=row_base, nnz_base=nnz_base)
         # SpGEMM's replication step: rank 0 owns B, everyone ends up with it
