@@ -398,7 +398,11 @@ __device__ __forceinline__ void walk_segments(const int *seg_off, const int *seg
 constexpr int RK_WORDS = 8192;                     // bitmap words of one column window in shared memory
 constexpr int RK_WINDOW_COLS = RK_WORDS * 32;      // 262144 columns per window
 constexpr size_t RK_PTR_BUDGET = size_t(1) << 30;  // bytes of the window pointer table; beyond it windows are searched on the fly
-constexpr int RK_NT = 256, HEAVY_NT = 512;
+constexpr int RK_NT = 256, HEAVY_NT = 512;         // threads of a CTA for rows up to / above RANKED_P products
+constexpr size_t HEAVY_SMEM_NUMERIC = 104 * 1024;  // dynamic shared memory of a numeric heavy-row CTA: two per SM
+#ifndef ESC_RANKED_SMEM_KB
+#define ESC_RANKED_SMEM_KB 0                       // of a numeric ranked-row CTA; 0: bitmap and ranks only, four per SM
+#endif
 
 // First index in [lo, hi) whose column is >= key (hi if none).
 __device__ __forceinline__ int32_t first_col_at_least(const int32_t *__restrict__ col, int32_t lo, int32_t hi, int64_t key) {
@@ -429,28 +433,35 @@ __global__ void __launch_bounds__(256) k_esc_window_ptr(CsrView B, int32_t b_row
 // RK_WINDOW_COLS). Per window: pass 1 walks the row's products and sets a bit per produced column
 // in a shared-memory bitmap; a popcount scan turns the bitmap into the rank of every column within
 // the result row and the columns are written out; pass 2 walks the products again and adds each
-// one straight into its final position of C, which this CTA zeroed first (float32 reductions in
-// L2 on the row's own compact output range). Symbolic: pass 1 and the count only.
+// one into its final position: the first `acc_slots` positions of the window accumulate in shared
+// memory (float32 atomics there run several times faster than reductions in L2) and are stored
+// with coalesced writes at the end, the positions beyond them take a float32 reduction in L2 on
+// the row's own output range, which this CTA zeroed first. Symbolic: pass 1 and the count only.
+//
+// Ranks are kept in 16 bits relative to the first word of the warp that scanned them (a warp
+// scans `1 << wshift` consecutive words, at most 16384 columns) plus one base per warp.
 //
 // `row_list` is read from the front for the first n_front CTAs and from the back (list_len - 1
-// downwards) for the others. `words`: bitmap words in use, a multiple of NT that covers a window.
+// downwards) for the others. `words`: bitmap words in use, (NT / 32) << wshift, covering a window.
 // `win_ptr` is the window pointer table, or null (one window, or a table beyond its budget).
 // `cache` (one window only), when given, carries the bitmaps from the symbolic launch to the
 // numeric launch of one call, `words` per CTA: the symbolic launch stores them, the numeric
 // launch loads them instead of walking the products a first time.
-template <bool NUMERIC, typename RankT, int NT>
+template <bool NUMERIC, int NT>
 __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const int32_t *__restrict__ win_ptr, int n_win,
                                                    const int32_t *__restrict__ row_list, int32_t list_len, int n_front, int words,
-                                                   uint32_t *cache, int32_t *__restrict__ row_count,
+                                                   int wshift, int acc_slots, uint32_t *cache, int32_t *__restrict__ row_count,
                                                    const int32_t *__restrict__ c_rp, int32_t *__restrict__ c_col,
                                                    float *__restrict__ c_val) {
     extern __shared__ __align__(16) unsigned char rk_smem[];
     uint32_t *bitmap = reinterpret_cast<uint32_t *>(rk_smem);
-    RankT *rank = reinterpret_cast<RankT *>(rk_smem + (size_t)words * 4);
+    uint16_t *rank16 = reinterpret_cast<uint16_t *>(rk_smem + (size_t)words * 4);
+    float *acc = reinterpret_cast<float *>(rk_smem + (size_t)words * 6);
     __shared__ int seg_off[NT + 1];
     __shared__ int seg_start[NT];
     __shared__ float seg_a[NUMERIC ? NT : 1];
     __shared__ int scan_tmp[72];
+    __shared__ int warp_base[NT / 32];
     const int tid = threadIdx.x;
     const int r = blockIdx.x;
     const int32_t i = ld_nc(row_list + (r < n_front ? r : list_len - 1 - (r - n_front)));
@@ -538,9 +549,9 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
                 for (int c = tid; c < words / 4; c += NT) __stcs(cached + c, reinterpret_cast<const uint4 *>(bitmap)[c]);
         }
 
-        // warp v looks after its share of the words, lane = word within groups of 32
-        const int groups = words / NT;
-        const int wbase = warp_id() * groups * 32;
+        // warp v looks after the words [v << wshift, (v + 1) << wshift), lane = word within groups of 32
+        const int groups = 1 << (wshift - 5);
+        const int wbase = warp_id() << wshift;
         int mine = 0;
 #pragma unroll 4
         for (int g = 0; g < groups; ++g) mine += __popc(bitmap[wbase + g * 32 + lane_id()]);
@@ -550,7 +561,9 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
             out += cnt;
             continue;
         }
-        int running = __shfl_sync(FULL_MASK, excl, 0);  // columns of the window before this warp's words
+        const int my_base = __shfl_sync(FULL_MASK, excl, 0);  // columns of the window before this warp's words
+        if (lane_id() == 0) warp_base[warp_id()] = my_base;
+        int running = 0;
 #pragma unroll 2
         for (int g = 0; g < groups; ++g) {
             const int idx = wbase + g * 32 + lane_id();
@@ -558,22 +571,31 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
             const int c = __popc(bits);
             const int incl = warp_incl_sum(c);
             const int first = running + incl - c;
-            rank[idx] = (RankT)first;
-            int64_t pos = out + first;
+            rank16[idx] = (uint16_t)first;
+            int64_t pos = out + my_base + first;
             while (bits) {
                 c_col[pos++] = c_first + idx * 32 + (__ffs(bits) - 1);
                 bits &= bits - 1u;
             }
             running += __shfl_sync(FULL_MASK, incl, 31);
         }
-        for (int k = tid; k < cnt; k += NT) c_val[out + k] = 0.f;
-        __syncthreads();  // ranks complete, output zeroed (the reductions below come from this CTA only)
         float *row_val = c_val + out;  // the window's part of the row; its length fits 32 bits
+        const int in_acc = min(cnt, acc_slots);
+        for (int k = tid; k < in_acc; k += NT) acc[k] = 0.f;
+        for (int k = acc_slots + tid; k < cnt; k += NT) row_val[k] = 0.f;  // positions beyond the shared accumulator
+        __syncthreads();  // ranks complete, output zeroed (the reductions below come from this CTA only)
         pass(!one_chunk || from_cache, [&](int32_t col, float v) {
             const uint32_t cw = (uint32_t)(col - c_first);
-            const uint32_t bits = bitmap[cw >> 5];
-            atomicAdd(row_val + ((uint32_t)rank[cw >> 5] + __popc(bits & ((1u << (cw & 31u)) - 1u))), v);
+            const uint32_t wd = cw >> 5;
+            const uint32_t bits = bitmap[wd];
+            const uint32_t pos = (uint32_t)warp_base[wd >> wshift] + rank16[wd] + __popc(bits & ((1u << (cw & 31u)) - 1u));
+            if (pos < (uint32_t)acc_slots)
+                atomicAdd(acc + pos, v);      // shared memory
+            else
+                atomicAdd(row_val + pos, v);  // reduction in L2
         });
+        // the pass ends with a barrier: every sum is in place
+        for (int k = tid; k < in_acc; k += NT) row_val[k] = acc[k];
         out += cnt;
     }
     if (!NUMERIC && tid == 0) row_count[i] = (int32_t)out;
@@ -589,11 +611,14 @@ __global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restri
 
 // ------------------------------------------------------------------------ host driver ----
 
-// Bitmap words a CTA of NT threads keeps for B's column count (one window's worth at most).
-template <int NT>
-int ranked_words(int32_t b_cols) {
-    const int64_t window_cols = std::min<int64_t>(b_cols, RK_WINDOW_COLS);
-    return (int)((((window_cols + 31) / 32 + NT - 1) / NT) * NT);
+// Bitmap words a ranked-row CTA keeps for B's column count (one window's worth at most): every
+// warp scans a power of two of words, at least 32. `wshift` receives log2 of that count.
+int ranked_words(int nt, int32_t b_cols, int *wshift = nullptr) {
+    const int64_t need = (std::min<int64_t>(b_cols, RK_WINDOW_COLS) + 31) / 32;
+    int shift = 5;
+    while (((int64_t)(nt / 32) << shift) < need) ++shift;
+    if (wshift) *wshift = shift;
+    return (nt / 32) << shift;
 }
 
 
@@ -667,8 +692,8 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, bool carry_
     plan->cache_ws = nullptr;
     if (carry_bitmaps && plan->n_win == 1) {
         // a second pool block: its size is only known now, and the first must not move
-        const size_t ranked_bytes = (size_t)plan->host.n_ranked * ranked_words<RK_NT>(b->cols) * 4;
-        const size_t heavy_bytes = ((size_t)plan->host.n_giant + plan->host.n_heavy) * ranked_words<HEAVY_NT>(b->cols) * 4;
+        const size_t ranked_bytes = (size_t)plan->host.n_ranked * ranked_words(RK_NT, b->cols) * 4;
+        const size_t heavy_bytes = ((size_t)plan->host.n_giant + plan->host.n_heavy) * ranked_words(HEAVY_NT, b->cols) * 4;
         if (ranked_bytes + heavy_bytes > 0 && ranked_bytes + heavy_bytes <= BITMAP_CACHE_BUDGET) {
             Carver cache_sizes;
             cache_sizes.take<uint32_t>(ranked_bytes / 4);
@@ -688,16 +713,23 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, bool carry_
     return NB200_OK;
 }
 
-template <bool NUMERIC, typename RankT, int NT>
+template <bool NUMERIC, int NT>
 int launch_ranked(const CsrView &A, const CsrView &B, const EscPlan &plan, int32_t b_cols, const int32_t *list, int32_t list_len,
                   int n_front, int n_rows, uint32_t *cache, int32_t *count, const int32_t *c_rp, int32_t *c_col, float *c_val,
                   cudaStream_t stream) {
-    const int words = ranked_words<NT>(b_cols);
-    const size_t smem = (size_t)words * (4 + sizeof(RankT));
-    NB200_CUDA(cudaFuncSetAttribute(k_esc_ranked<NUMERIC, RankT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)((size_t)RK_WORDS * (4 + sizeof(RankT)))));
-    k_esc_ranked<NUMERIC, RankT, NT><<<n_rows, NT, smem, stream>>>(A, B, plan.win_ptr, plan.n_win, list, list_len, n_front, words, cache,
-                                                                   count, c_rp, c_col, c_val);
+    int wshift = 5;
+    const int words = ranked_words(NT, b_cols, &wshift);
+    // numeric: whatever the bitmap and the ranks leave of the CTA's shared memory accumulates sums
+    // The lighter rows do better without a shared accumulator: their CTAs are bound by the latency of
+    // a row's short phases, and four CTAs per SM hide more of it than three with an accumulator
+    // (7.7 against 9.2 ms on configuration 4a); the heavy rows gain (10.7 -> 7.5 ms).
+    const size_t budget = std::max(NT == HEAVY_NT ? HEAVY_SMEM_NUMERIC : (size_t)ESC_RANKED_SMEM_KB * 1024, (size_t)words * 6);
+    const int acc_slots = NUMERIC ? (int)((budget - (size_t)words * 6) / 4 / NT) * NT : 0;
+    const size_t smem = NUMERIC ? (size_t)words * 6 + (size_t)acc_slots * 4 : (size_t)words * 4;
+    NB200_CUDA(cudaFuncSetAttribute(k_esc_ranked<NUMERIC, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)(NUMERIC ? budget : (size_t)RK_WORDS * 4)));
+    k_esc_ranked<NUMERIC, NT><<<n_rows, NT, smem, stream>>>(A, B, plan.win_ptr, plan.n_win, list, list_len, n_front, words, wshift,
+                                                          acc_slots, cache, count, c_rp, c_col, c_val);
     NB200_CUDA(cudaGetLastError());
     return NB200_OK;
 }
@@ -713,13 +745,13 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
     const int n_heavy = plan.host.n_giant + plan.host.n_heavy;
     if (n_heavy > 0) {  // first: the heaviest rows take longest
         LaunchScope scope(NUMERIC ? "esc_heavy_numeric" : "esc_heavy_symbolic", stream);
-        if ((st = launch_ranked<NUMERIC, uint32_t, HEAVY_NT>(A, B, plan, b->cols, plan.lists.heavy_rows, a->rows, plan.host.n_giant, n_heavy,
+        if ((st = launch_ranked<NUMERIC, HEAVY_NT>(A, B, plan, b->cols, plan.lists.heavy_rows, a->rows, plan.host.n_giant, n_heavy,
                                                              plan.cache_heavy, count, c_rp, c_col, c_val, stream)))
             return st;
     }
     if (plan.host.n_ranked > 0) {
         LaunchScope scope(NUMERIC ? "esc_ranked_numeric" : "esc_ranked_symbolic", stream);
-        if ((st = launch_ranked<NUMERIC, uint16_t, RK_NT>(A, B, plan, b->cols, plan.lists.ranked_rows, a->rows, plan.host.n_ranked,
+        if ((st = launch_ranked<NUMERIC, RK_NT>(A, B, plan, b->cols, plan.lists.ranked_rows, a->rows, plan.host.n_ranked,
                                                           plan.host.n_ranked, plan.cache_ranked, count, c_rp, c_col, c_val, stream)))
             return st;
     }
