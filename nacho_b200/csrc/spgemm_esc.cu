@@ -438,8 +438,8 @@ __global__ void __launch_bounds__(256) k_esc_window_ptr(CsrView B, int32_t b_row
 // with coalesced writes at the end, the positions beyond them take a float32 reduction in L2 on
 // the row's own output range, which this CTA zeroed first. Symbolic: pass 1 and the count only.
 //
-// Ranks are kept in 16 bits relative to the first word of the warp that scanned them (a warp
-// scans `1 << wshift` consecutive words, at most 16384 columns) plus one base per warp.
+// Ranks are kept per 64 columns, in 16 bits relative to the first word of the warp that scanned
+// them (a warp scans `1 << wshift` consecutive words, at most 32768 columns), plus one base per warp.
 //
 // `row_list` is read from the front for the first n_front CTAs and from the back (list_len - 1
 // downwards) for the others. `words`: bitmap words in use, (NT / 32) << wshift, covering a window.
@@ -455,8 +455,9 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
                                                    float *__restrict__ c_val) {
     extern __shared__ __align__(16) unsigned char rk_smem[];
     uint32_t *bitmap = reinterpret_cast<uint32_t *>(rk_smem);
-    uint16_t *rank16 = reinterpret_cast<uint16_t *>(rk_smem + (size_t)words * 4);
-    float *acc = reinterpret_cast<float *>(rk_smem + (size_t)words * 6);
+    const uint64_t *bitmap64 = reinterpret_cast<const uint64_t *>(rk_smem);  // the same bits, 64 columns per element
+    uint16_t *rank16 = reinterpret_cast<uint16_t *>(rk_smem + (size_t)words * 4);  // one rank per 64 columns
+    float *acc = reinterpret_cast<float *>(rk_smem + (size_t)words * 5);
     __shared__ int seg_off[NT + 1];
     __shared__ int seg_start[NT];
     __shared__ float seg_a[NUMERIC ? NT : 1];
@@ -549,12 +550,12 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
                 for (int c = tid; c < words / 4; c += NT) __stcs(cached + c, reinterpret_cast<const uint4 *>(bitmap)[c]);
         }
 
-        // warp v looks after the words [v << wshift, (v + 1) << wshift), lane = word within groups of 32
-        const int groups = 1 << (wshift - 5);
-        const int wbase = warp_id() << wshift;
+        // warp v looks after the words [v << wshift, (v + 1) << wshift), 64 columns per lane and step
+        const int groups = 1 << (wshift - 6);
+        const int dbase = warp_id() << (wshift - 1);  // first 64-bit element of the warp
         int mine = 0;
 #pragma unroll 4
-        for (int g = 0; g < groups; ++g) mine += __popc(bitmap[wbase + g * 32 + lane_id()]);
+        for (int g = 0; g < groups; ++g) mine += __popcll(bitmap64[dbase + g * 32 + lane_id()]);
         int cnt;
         const int excl = block_excl_sum<NT>(mine, scan_tmp, cnt);
         if (!NUMERIC) {
@@ -566,16 +567,16 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
         int running = 0;
 #pragma unroll 2
         for (int g = 0; g < groups; ++g) {
-            const int idx = wbase + g * 32 + lane_id();
-            uint32_t bits = bitmap[idx];
-            const int c = __popc(bits);
+            const int idx = dbase + g * 32 + lane_id();
+            uint64_t bits = bitmap64[idx];
+            const int c = __popcll(bits);
             const int incl = warp_incl_sum(c);
             const int first = running + incl - c;
             rank16[idx] = (uint16_t)first;
             int64_t pos = out + my_base + first;
             while (bits) {
-                c_col[pos++] = c_first + idx * 32 + (__ffs(bits) - 1);
-                bits &= bits - 1u;
+                c_col[pos++] = c_first + idx * 64 + (__ffsll((long long)bits) - 1);
+                bits &= bits - 1ull;
             }
             running += __shfl_sync(FULL_MASK, incl, 31);
         }
@@ -586,9 +587,9 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
         __syncthreads();  // ranks complete, output zeroed (the reductions below come from this CTA only)
         pass(!one_chunk || from_cache, [&](int32_t col, float v) {
             const uint32_t cw = (uint32_t)(col - c_first);
-            const uint32_t wd = cw >> 5;
-            const uint32_t bits = bitmap[wd];
-            const uint32_t pos = (uint32_t)warp_base[wd >> wshift] + rank16[wd] + __popc(bits & ((1u << (cw & 31u)) - 1u));
+            const uint32_t dw = cw >> 6;
+            const uint64_t bits = bitmap64[dw];
+            const uint32_t pos = (uint32_t)warp_base[dw >> (wshift - 1)] + rank16[dw] + __popcll(bits & ((1ull << (cw & 63u)) - 1ull));
             if (pos < (uint32_t)acc_slots)
                 atomicAdd(acc + pos, v);      // shared memory
             else
@@ -612,10 +613,10 @@ __global__ void __launch_bounds__(256) k_esc_row_offsets(const int32_t *__restri
 // ------------------------------------------------------------------------ host driver ----
 
 // Bitmap words a ranked-row CTA keeps for B's column count (one window's worth at most): every
-// warp scans a power of two of words, at least 32. `wshift` receives log2 of that count.
+// warp scans a power of two of words, at least 64. `wshift` receives log2 of that count.
 int ranked_words(int nt, int32_t b_cols, int *wshift = nullptr) {
     const int64_t need = (std::min<int64_t>(b_cols, RK_WINDOW_COLS) + 31) / 32;
-    int shift = 5;
+    int shift = 6;
     while (((int64_t)(nt / 32) << shift) < need) ++shift;
     if (wshift) *wshift = shift;
     return (nt / 32) << shift;
@@ -723,9 +724,9 @@ int launch_ranked(const CsrView &A, const CsrView &B, const EscPlan &plan, int32
     // The lighter rows do better without a shared accumulator: their CTAs are bound by the latency of
     // a row's short phases, and four CTAs per SM hide more of it than three with an accumulator
     // (7.7 against 9.2 ms on configuration 4a); the heavy rows gain (10.7 -> 7.5 ms).
-    const size_t budget = std::max(NT == HEAVY_NT ? HEAVY_SMEM_NUMERIC : (size_t)ESC_RANKED_SMEM_KB * 1024, (size_t)words * 6);
-    const int acc_slots = NUMERIC ? (int)((budget - (size_t)words * 6) / 4 / NT) * NT : 0;
-    const size_t smem = NUMERIC ? (size_t)words * 6 + (size_t)acc_slots * 4 : (size_t)words * 4;
+    const size_t budget = std::max(NT == HEAVY_NT ? HEAVY_SMEM_NUMERIC : (size_t)ESC_RANKED_SMEM_KB * 1024, (size_t)words * 5);
+    const int acc_slots = NUMERIC ? (int)((budget - (size_t)words * 5) / 4 / NT) * NT : 0;
+    const size_t smem = NUMERIC ? (size_t)words * 5 + (size_t)acc_slots * 4 : (size_t)words * 4;
     NB200_CUDA(cudaFuncSetAttribute(k_esc_ranked<NUMERIC, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)(NUMERIC ? budget : (size_t)RK_WORDS * 4)));
     k_esc_ranked<NUMERIC, NT><<<n_rows, NT, smem, stream>>>(A, B, plan.win_ptr, plan.n_win, list, list_len, n_front, words, wshift,
