@@ -187,15 +187,19 @@ int nb200_csr_add_3_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200
  * expand src/backend/compute.cpp:526-611, sort/compress
  * src/backend/stitch_and_generate_gpu.cpp:14-139,257-363). Unlike the reference, product
  * counts are 64-bit (a product count above 2^31 is fine as long as nnz(C) fits int32) and
- * rows with at most 2048 products sum equal-column products in a fixed order (ascending j);
- * longer rows accumulate with float32 atomics (as the reference does for every row). Rows
- * longer than 2048 products need a dense per-row accumulator over B's column range (4 bytes
- * per column, up to 592 of them at once, 4 GiB in total); NB200_E_NOMEM if that cannot be had. */
+ * rows with at most 256 products sum equal-column products in a fixed order (ascending j);
+ * longer rows accumulate with float32 atomics (as the reference does for every row). No
+ * product is written to device memory; scratch is a few int32 per row, plus, for matrices wider
+ * than 262144 columns, a pointer table of one int32 per row of B and 262144 columns of width. */
 int nb200_spgemm_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int32_t num_blocks,
                      int32_t threads_per_block, void *stream);
 /* Two-step form for caller-owned memory: _symbolic fills c->row_ptr (rows + 1, caller-owned)
  * and c->nnz; the caller then provides col/val of c->nnz entries to _numeric.
- * `products` (may be NULL) receives the number of scalar products. */
+ * `products` (may be NULL) receives the number of scalar products. A _numeric call that follows
+ * a _symbolic call on the same arrays, device and stream, with no other call of this library on
+ * that stream in between, reuses what _symbolic left in the scratch pool (row bins and the column
+ * bitmaps of the long rows, up to 8 GiB) instead of computing it again; any other order of calls
+ * is equally valid and recomputes. */
 int nb200_spgemm_f32_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
                               int64_t *products, void *stream);
 int nb200_spgemm_f32_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
