@@ -639,13 +639,15 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
             const bool tx = (r[i] & 1u) == 0u;
-            float v = *(tx ? pa + ca : pb + (i - ca));
-            if ((twin >> i) & 1u) {  // an A entry whose twin is the next B entry
-                const float vb = pb[i - ca];
-                v = OP == OP_UNION ? v + vb : v * vb;
-            }
-            if ((emit >> i) & 1u) {
-                *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(v));
+            if (OP == OP_UNION) {
+                float v = *(tx ? pa + ca : pb + (i - ca));
+                if ((twin >> i) & 1u) v = v + pb[i - ca];  // an A entry whose twin is the next B entry
+                if ((emit >> i) & 1u) {
+                    *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(v));
+                    ++po;
+                }
+            } else if ((emit >> i) & 1u) {  // intersection: only the twins need their values
+                *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(pa[ca] * pb[i - ca]));
                 ++po;
             }
             ca += tx;
