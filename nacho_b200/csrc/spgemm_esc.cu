@@ -573,10 +573,21 @@ __global__ void __launch_bounds__(NT) k_esc_ranked(CsrView A, CsrView B, const i
             const int incl = warp_incl_sum(c);
             const int first = running + incl - c;
             rank16[idx] = (uint16_t)first;
-            int64_t pos = out + my_base + first;
-            while (bits) {
-                c_col[pos++] = c_first + idx * 64 + (__ffsll((long long)bits) - 1);
-                bits &= bits - 1ull;
+            // the lane's columns, in 32-bit halves and 32-bit positions (the loop is the hot part of
+            // the scan: one trip per result entry)
+            int32_t *gcol = c_col + (out + my_base);
+            int pos = first;
+            uint32_t half = (uint32_t)bits;
+            int32_t col0 = c_first + idx * 64;
+            while (half) {
+                gcol[pos++] = col0 + (__ffs((int)half) - 1);
+                half &= half - 1u;
+            }
+            half = (uint32_t)(bits >> 32);
+            col0 += 32;
+            while (half) {
+                gcol[pos++] = col0 + (__ffs((int)half) - 1);
+                half &= half - 1u;
             }
             running += __shfl_sync(FULL_MASK, incl, 31);
         }
