@@ -199,62 +199,60 @@ __device__ __forceinline__ void st_relaxed_gpu_i32(int *p, int v) {
     asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Called by all 32 lanes of one warp. Returns the sum of the aggregates of tiles [0, t).
-// Each round inspects LOOKBACK_DEPTH * 32 predecessors with all of a lane's loads in flight
-// together, so a round costs one memory round trip however many words it covers.
-constexpr int LOOKBACK_DEPTH = 1;
-
-// Sum of the counts of tiles [0, t), read off the tile words of the predecessors; publishes
-// nothing. Polls with `sleep_ns` between rounds. Returns -1 (and records the tile in `status`)
-// if a bounded wait gives up. Called by all 32 lanes of one warp, t > 0.
+// Sum of the counts of tiles [0, t), read off the tile words of the predecessors, 32 at a time
+// from the nearest one backwards; publishes nothing. A round is complete once every word up to
+// the nearest tile that already knows its prefix is published (the words beyond it are not
+// needed); until then the warp polls, sleeping `sleep_ns` between polls -- or `hurry_ns` once
+// `*hurry` is non-zero (the caller's own tile is waiting for the result by then, so the poll
+// traffic no longer competes with useful work). Returns -1 (and records the tile in `status`) if
+// a bounded wait gives up. Called by all 32 lanes of one warp, t > 0.
+template <int DEPTH = 1>
 __device__ __forceinline__ int64_t lookback_predecessors(volatile uint64_t *state, int t, DeviceStatus *status,
-                                                         unsigned sleep_ns) {
+                                                         unsigned sleep_ns, const volatile int *hurry = nullptr,
+                                                         unsigned hurry_ns = 64) {
+    // One round covers DEPTH * 32 predecessors, nearest first (word j of a lane is tile
+    // pos - 32 j - lane), with all of a lane's loads in flight together.
     int64_t exclusive = 0;
-    bool failed = false, done = false;
-    for (int pos = t - 1; !done; pos -= 32 * LOOKBACK_DEPTH) {
-        uint64_t s[LOOKBACK_DEPTH];
-        bool timed_out = false;
-        int polls = 0;
-        for (;;) {
-            bool ready = true;
+    for (int pos = t - 1;; pos -= 32 * DEPTH) {
+        uint64_t s[DEPTH];
+        unsigned need[DEPTH];
+        bool found = false;
+        for (int polls = 0;; ++polls) {
 #pragma unroll
-            for (int j = 0; j < LOOKBACK_DEPTH; ++j) {
+            for (int j = 0; j < DEPTH; ++j) {
                 const int idx = pos - 32 * j - lane_id();
-                // lanes that fall before tile 0 stand for an empty prefix
-                s[j] = idx >= 0 ? ld_relaxed_gpu(state + idx) : LB_PREFIX;
+                s[j] = idx >= 0 ? ld_relaxed_gpu(state + idx) : LB_PREFIX;  // before tile 0: an empty prefix
             }
+            bool ready = true;
+            found = false;
 #pragma unroll
-            for (int j = 0; j < LOOKBACK_DEPTH; ++j) ready = ready && (s[j] >> 62) != 0;
-            // only words up to the nearest prefix matter; waiting for all of them is simpler and
-            // they belong to tiles that started earlier still
-            if (__all_sync(FULL_MASK, ready)) break;
-            if (++polls >= LOOKBACK_POLL_LIMIT) {
-                timed_out = true;
-                break;
+            for (int j = 0; j < DEPTH; ++j) {
+                const unsigned prefix_lanes = __ballot_sync(FULL_MASK, (s[j] >> 62) == 2);
+                const unsigned published = __ballot_sync(FULL_MASK, (s[j] >> 62) != 0);
+                if (found) {
+                    need[j] = 0u;  // beyond the nearest prefix: not needed
+                } else {
+                    const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 31;
+                    need[j] = first == 31 ? FULL_MASK : (1u << (first + 1)) - 1u;
+                    ready = ready && (published & need[j]) == need[j];
+                    found = prefix_lanes != 0u;
+                }
             }
-            __nanosleep(sleep_ns);
+            if (ready) break;
+            if (polls >= LOOKBACK_POLL_LIMIT) {
+                if (lane_id() == 0 && atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
+                return -1;
+            }
+            __nanosleep(hurry && *hurry ? hurry_ns : sleep_ns);
         }
-        if (__any_sync(FULL_MASK, timed_out)) {
-            failed = true;
-            break;
-        }
+        long long v = 0;
 #pragma unroll
-        for (int j = 0; j < LOOKBACK_DEPTH; ++j) {
-            if (done) break;
-            const unsigned prefix_lanes = __ballot_sync(FULL_MASK, (s[j] >> 62) == 2);
-            const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 32;
-            long long v = lane_id() <= first ? (long long)(s[j] & LB_VALUE_MASK) : 0;
+        for (int j = 0; j < DEPTH; ++j) v += (need[j] >> lane_id()) & 1u ? (long long)(s[j] & LB_VALUE_MASK) : 0;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
-            exclusive += v;
-            if (prefix_lanes) done = true;
-        }
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
+        exclusive += v;
+        if (found) return exclusive;
     }
-    if (failed) {
-        if (lane_id() == 0 && atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
-        return -1;
-    }
-    return exclusive;
 }
 
 // Publishes the tile's count, walks back, publishes the inclusive prefix. Returns the sum of the

@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int scan_tmp[72];
     __shared__ long long s_base, s_base_levels, s_levels;
+    __shared__ int s_hurry, s_hurry_levels;  // set once the tile's count / packed level count is out
     __shared__ unsigned long long s_prev_key;
     __shared__ __align__(8) uint64_t mbar;
     __shared__ int s_total;
@@ -167,6 +168,8 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
     if (tid == 0) {
         mbar_init(&mbar, 1);
         mbar_fence_init();
+        s_hurry = 0;
+        s_hurry_levels = 0;
     }
     __syncthreads();
     // tiles are numbered by CTA index: CTAs are dispatched in increasing index order, so a tile
@@ -263,7 +266,7 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
         // the output base is the sum of the counts of all earlier tiles and does not depend on
         // this tile's count: walk the predecessors' words while the workers merge
         if (MODE != MODE_FUSED) return;
-        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, 1000);
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, 1000, &s_hurry, 1000);
         CountBar::sync();  // the workers have published the tile's count by now
         const int total = s_total;
         if (lane_id() == 0) {
@@ -275,7 +278,7 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
         if (CSF_OUT) {
             // second walk: slices and fibres of all earlier tiles (packed), while the workers store
             volatile uint64_t *level_state = csf.tile_state;
-            const int64_t lv = t == 0 ? 0 : lookback_predecessors(level_state, t, &ctl->status, 1000);
+            const int64_t lv = t == 0 ? 0 : lookback_predecessors(level_state, t, &ctl->status, 1000, &s_hurry_levels, 1000);
             LevelBar::sync();  // the workers have published the tile's packed count by now
             const long long packed = s_levels;
             if (lane_id() == 0) {
@@ -361,6 +364,7 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
             // successors can add this tile's count from here on
             st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
             s_total = total;
+            *(volatile int *)&s_hurry = 1;
         }
         __threadfence_block();
         CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
@@ -411,6 +415,7 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
             const long long packed = ((long long)tot_i << 31) | (long long)tot_ij;
             st_relaxed_gpu(csf.tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)packed);
             s_levels = packed;
+            *(volatile int *)&s_hurry_levels = 1;
         }
         __threadfence_block();
         LevelBar::arrive();  // the scan warp turns the packed count into the tile's inclusive prefix

@@ -37,8 +37,15 @@ namespace {
 #ifndef CSR2_VT
 #define CSR2_VT 19
 #endif
+#ifndef CSR2_LB_DEPTH
+#define CSR2_LB_DEPTH 1      // predecessors read per round of the look-back, in units of 32
+#endif
+#ifndef CSR2_LB_HURRY
+#define CSR2_LB_HURRY 1000  // ns between polls of the look-back once the tile itself waits for the result (faster polling
+                            // was measured: 64 ns costs 5 %, the poll traffic slows the workers of the other tiles)
+#endif
 #ifndef CSR2_LB_SLEEP
-#define CSR2_LB_SLEEP 1000  // nanoseconds between polls of the predecessors' tile words (shorter polls measurably slow the workers)
+#define CSR2_LB_SLEEP 2000  // nanoseconds between polls of the predecessors' tile words (shorter polls measurably slow the workers)
 #endif
 #ifndef CSR2_MIN_CTAS
 #define CSR2_MIN_CTAS 3
@@ -415,6 +422,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     constexpr uint32_t INF = 0xffffffffu;
     __shared__ long long s_base;
     __shared__ int s_total;
+    __shared__ int s_hurry;  // set once the tile's count is out: from then on the tile waits for its base
     const int tid = threadIdx.x;
     const bool scan_warp = tid >= NT;
     const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
@@ -447,6 +455,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     const int head_a = min(na, ha), head_b = min(nb, hb);
     const int nva = (na - head_a) >> 2, nvb = (nb - head_b) >> 2;  // 16-byte vectors in the interior
     if (tid == 0) {
+        s_hurry = 0;
         uint32_t bytes = 16u * (uint32_t)(nva + nvb);
         if (WRITES) bytes += (va_bulk ? 16u * nva : 0u) + (vb_bulk ? 16u * nvb : 0u);
         mbar_arrive_expect_tx(mbar, bytes);
@@ -502,7 +511,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         // predecessors' words starts now, while the workers are still merging, and is usually
         // over by the time they know their count.
         if (MODE != MODE_FUSED) return;
-        const int64_t bse = t == 0 ? 0 : lookback_predecessors(tile_state, t, &ctl->status, CSR2_LB_SLEEP);
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors<CSR2_LB_DEPTH>(tile_state, t, &ctl->status, CSR2_LB_SLEEP, &s_hurry, CSR2_LB_HURRY);
         CountBar::sync();  // the workers have published the tile's count by now
         const int total = s_total;
         if (lane_id() == 0) {
@@ -623,6 +632,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
             // successors can add this tile's count from here on
             st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
             s_total = total;
+            *(volatile int *)&s_hurry = 1;
         }
         __threadfence_block();
         CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
