@@ -165,16 +165,44 @@ __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const i
     uint32_t my_col = 0;
     float my_val = 0.f;
     bool have = false;
+    // Expansion, 32 entries of the row at a time (one round unless the row holds entries whose rows
+    // of B are empty): lane l reads entry l and its row of B; the products of the round take the
+    // lanes [base, base + total) in expansion order, each finding its entry among the round's
+    // non-empty ones from the mask of slice starts.
     int base = 0;
-    for (int32_t e = lo; e < hi; ++e) {  // uniform across the warp
-        const int32_t j = ld_nc(A.col + e);
-        const int32_t b_lo = ld_nc(B.rp + j), len = ld_nc(B.rp + j + 1) - b_lo;
-        if (lane >= base && lane < base + len) {
-            my_col = (uint32_t)ld_nc(B.col + b_lo + (lane - base));
-            if (NUMERIC) my_val = ld_nc(A.val + e) * ld_nc(B.val + b_lo + (lane - base));
+    for (int32_t chunk = lo; chunk < hi; chunk += 32) {  // uniform across the warp
+        int32_t b_lo = 0, len = 0;
+        float a = 0.f;
+        if (chunk + lane < hi) {
+            const int32_t j = ld_nc(A.col + chunk + lane);
+            b_lo = ld_nc(B.rp + j);
+            len = ld_nc(B.rp + j + 1) - b_lo;
+            if (NUMERIC) a = ld_nc(A.val + chunk + lane);
+        }
+        const int incl = warp_incl_sum(len);
+        const int start = base + incl - len;                       // first lane of this entry's products
+        const unsigned nonempty = __ballot_sync(FULL_MASK, len > 0);
+        const unsigned starts = __reduce_or_sync(FULL_MASK, len > 0 ? 1u << start : 0u);  // the row has at most 32 products
+        const int total = __shfl_sync(FULL_MASK, incl, 31);
+        // the entry of lane `lane`'s product: the n-th non-empty one, n = slice starts at or before the lane
+        const int nth = __popc(starts & (0xffffffffu >> (31 - lane)));
+        const int owner = nth > 0 ? (int)__fns(nonempty, 0, nth) : 0;
+        const int32_t o_lo = __shfl_sync(FULL_MASK, b_lo, owner);
+        const int o_start = __shfl_sync(FULL_MASK, start, owner);
+        const float o_a = __shfl_sync(FULL_MASK, a, owner);
+        if (lane >= base && lane < base + total) {
+            my_col = (uint32_t)ld_nc(B.col + o_lo + (lane - o_start));
+            if (NUMERIC) my_val = o_a * ld_nc(B.val + o_lo + (lane - o_start));
             have = true;
         }
-        base += len;
+        base += total;
+    }
+    if (!NUMERIC) {
+        // distinct columns: a lane counts if it is the first of the lanes that hold its column
+        const unsigned peers = __match_any_sync(FULL_MASK, have ? my_col : 0x80000000u | (uint32_t)lane);
+        const unsigned firsts = __ballot_sync(FULL_MASK, have && lane == __ffs(peers) - 1);
+        if (lane == 0) row_count[i] = __popc(firsts);
+        return;
     }
     uint32_t col;
     int src;
@@ -195,10 +223,6 @@ __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const i
     const uint32_t prev_col = __shfl_up_sync(FULL_MASK, col, 1);
     const bool head = valid && (lane == 0 || prev_col != col);
     const unsigned heads = __ballot_sync(FULL_MASK, head);
-    if (!NUMERIC) {
-        if (lane == 0) row_count[i] = __popc(heads);
-        return;
-    }
     float v = __shfl_sync(FULL_MASK, my_val, src);  // value of the product now at this lane
     float acc = v;
     // longest run of equal columns in this row (distance from a head to the next head or to
