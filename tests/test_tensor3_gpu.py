@@ -144,3 +144,35 @@ def test_csf3_blocks_through_the_gpu_operator(nacho):
             blocks.append((z.i_idx, z.j_ptr, z.j_idx, z.k_ptr, z.k_idx, z.val))
         got = shard.concat_csf3_blocks(blocks)
         assert_same(CSF3(dims, *got), whole, f"CSF3 in {parts} blocks")
+
+
+def test_count_scan_fill_route_in_a_child_process(tmp_path):
+    """NACHO_B200_TWO_PASS=1 (read once per process) sends the coordinate merge through count ->
+    scan -> fill, and the CSF3 add through its separate compress pass; both must still match the
+    C oracle bit-for-bit."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "two_pass.py"
+    script.write_text(f'''
+import sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, {os.path.join(root, "tests")!r})
+import numpy as np
+import test_tensor3_gpu as t3
+from helpers import assert_same, csf3_levels
+from nacho_b200 import nacho
+from oracle.cpu_oracle import COO3, CSF3, Oracle
+oracle = Oracle()
+for dims, n, seed in (((40, 30, 25), 900, 1), ((1 << 12, 1 << 10, 1 << 8), 120_000, 2), ((5, 1 << 16, 1 << 12), 90_000, 3)):
+    (ca, va), (cb, vb) = t3._seeded(dims, n, seed)
+    a, b = COO3(dims, ca[:, 0], ca[:, 1], ca[:, 2], va), COO3(dims, cb[:, 0], cb[:, 1], cb[:, 2], vb)
+    z = nacho.gpu_coo3d_add_f32(nacho.to_coo3(ca, va, dims, "cuda"), nacho.to_coo3(cb, vb, dims, "cuda"))
+    assert_same(t3.coo3_from_gpu(z), oracle.coo3_add(a, b, 8), "coo3, two passes")
+    f = nacho.gpu_csf_add_f32(nacho.to_csf3(ca, va, dims, "cuda"), nacho.to_csf3(cb, vb, dims, "cuda"))
+    assert_same(t3.csf3_from_gpu(f), oracle.csf3_add(CSF3(dims, *csf3_levels(ca), va), CSF3(dims, *csf3_levels(cb), vb)), "csf3, compress pass")
+print("two-pass ok")
+''')
+    env = dict(os.environ, NACHO_B200_TWO_PASS="1")
+    r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "two-pass ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
