@@ -37,6 +37,10 @@ namespace {
 #ifndef CSR2_VT
 #define CSR2_VT 19
 #endif
+#ifndef CSR2_RESIDENT
+#define CSR2_RESIDENT 0      // 1: single pass as resident CTAs that take tile after tile from a ticket. Measured on
+                             // configuration 3: 1.21 ms against 0.69 ms with one CTA per tile, so it is off.
+#endif
 #ifndef CSR2_LB_DEPTH
 #define CSR2_LB_DEPTH 1      // predecessors read per round of the look-back, in units of 32
 #endif
@@ -142,6 +146,11 @@ struct KeyTraits<uint64_t> {
     __device__ static __forceinline__ uint64_t make(uint32_t row, uint32_t col, int) { return ((uint64_t)row << 32) | col; }
 };
 
+// Hardware barriers of the tile kernel: 0 = the whole CTA (__syncthreads), 1 = the NT worker
+// threads, 2 = workers arrive / the scan warp waits ("the tile's count is known").
+using WorkerBar = NamedBarrier<1, NT>;
+using CountBar = NamedBarrier<2, NT + 32>;
+
 // Generic tile body: any key width, plain loads and stores. Used for the tiles whose rows do not
 // fit a 32-bit composite key; the common case takes csr2_tile_fast below.
 template <typename KeyT, int VT, int OP, int MODE>
@@ -150,7 +159,7 @@ template <typename KeyT, int VT, int OP, int MODE>
 __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits,
                                                const int t, int32_t *tile_count, volatile uint64_t *tile_state,
                                                FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
-                                               int *scan_tmp, int *thread_rank, unsigned *thread_emit) {
+                                               int *scan_tmp, int *thread_rank, unsigned *thread_emit, const int num_tiles) {
     using KT = KeyTraits<KeyT>;
     constexpr int CAP = NT * VT;  // most merged entries a tile can hold
     constexpr bool WRITES = MODE != MODE_COUNT;
@@ -183,7 +192,7 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
         my_sa = ld_nc(A.rp + my_row) - a0;
         my_sb = ld_nc(B.rp + my_row) - b0;
     }
-    __syncthreads();
+    WorkerBar::sync();
 
     // ---- mark the first entry of every row that starts inside the tile with its row number
     // relative to i0 (max wins where empty rows share a start), then spread it forward with a
@@ -201,7 +210,7 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
             else atomicMax(reinterpret_cast<unsigned *>(ky) + 2 * sb + 1, rr);
         }
     }
-    __syncthreads();
+    WorkerBar::sync();
     {
         // thread tid owns merged-array slots [tid*VT, tid*VT+VT): first the A part, then B
         const int lo = tid * VT, hi = min(lo + VT, n);
@@ -210,7 +219,7 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
             if (i < na) ma = max(ma, KT::row_of(kx[i], cbits)); else mb = max(mb, KT::row_of(ky[i - na], cbits));
         }
         unsigned ea, eb;
-        block_excl_max2<NT>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
+        block_excl_max2<NT, WorkerBar>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
         for (int i = lo; i < hi; ++i) {
             if (i < na) {
                 const KeyT k = kx[i];
@@ -225,7 +234,7 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
         if (tid < VT + 1) ky[nb + tid] = KT::INF;
         if (tid == 0) kx[na] = KT::INF;
     }
-    __syncthreads();
+    WorkerBar::sync();
 
     // ---- split the tile among threads: merge-path diagonal tid * VT, ties take A first
     const int diag = min(tid * VT, n);
@@ -271,7 +280,7 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
     // ---- rank the survivors inside the tile
     int total;
     const int mine = __popc(emit);
-    const int rank = block_excl_sum<NT>(mine, scan_tmp, total);  // syncs: key reads are done
+    const int rank = block_excl_sum<NT, WorkerBar>(mine, scan_tmp, total);  // syncs: key reads are done
     if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
         return;
@@ -289,15 +298,15 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
         }
         thread_rank[tid] = rank;
         thread_emit[tid] = emit;
-        __syncthreads();
+        WorkerBar::sync();
         base = s_base;
         if (base < 0) return;  // a bounded wait gave up; the host reports it
-        if (t == (int)gridDim.x - 1 && tid == 0) ctl->total = base + total;
+        if (t == num_tiles - 1 && tid == 0) ctl->total = base + total;
     }
     if (MODE == MODE_FILL) {
         thread_rank[tid] = rank;
         thread_emit[tid] = emit;
-        __syncthreads();
+        WorkerBar::sync();
     }
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
@@ -339,7 +348,7 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
             yi += !tx;
         }
     }
-    __syncthreads();
+    WorkerBar::sync();
     for (int i = tid; i < total; i += NT) {
         Z.col[base + i] = out_col[i];
         Z.val[base + i] = out_val[i];
@@ -395,10 +404,6 @@ __device__ __forceinline__ void bitonic_merge(uint32_t (&r)[N]) {
     }
 }
 
-// Hardware barriers of the tile kernel: 0 = the whole CTA (__syncthreads), 1 = the NT worker
-// threads, 2 = workers arrive / the scan warp waits ("the tile's count is known").
-using WorkerBar = NamedBarrier<1, NT>;
-using CountBar = NamedBarrier<2, NT + 32>;
 
 // Fast tile body. Keys are 32-bit composites (row in tile, column, operand bit):
 //     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
@@ -411,11 +416,11 @@ using CountBar = NamedBarrier<2, NT + 32>;
 // single-pass mode the scan warp meanwhile turns the tile's count into its output base by
 // look-back over earlier tiles, so that this wait overlaps the workers' compaction.
 template <int VT, int OP, int MODE>
-__device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits,
+__device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits,
                                                const int t, int32_t *tile_count, volatile uint64_t *tile_state,
                                                FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
                                                int *scan_tmp, int *thread_rank, unsigned *thread_emit,
-                                               uint64_t *mbar) {
+                                               uint64_t *mbar, const int num_tiles, const unsigned mbar_phase) {
     using P = FastPlan<VT>;
     constexpr int NETV = P::NETV;
     constexpr bool WRITES = MODE != MODE_COUNT;
@@ -495,14 +500,14 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         my_sa = ld_nc(A.rp + my_row) - a0;
         my_sb = ld_nc(B.rp + my_row) - b0;
     }
-    const bool landed = mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);
+    const bool landed = mbar_wait_bounded(mbar, mbar_phase, MBAR_POLL_LIMIT);
     if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
         if (tid == 0) {
             if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
             if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;  // successors must not wait on this tile
-            mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
+            mbar_wait_bounded(mbar, mbar_phase, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
         }
-        return;
+        return false;  // the barrier's phase is unknown from here on: the CTA takes no further tile
     }
 
     if (scan_warp) {
@@ -510,17 +515,17 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         // tiles, which does not depend on this tile's own count. So the walk over the
         // predecessors' words starts now, while the workers are still merging, and is usually
         // over by the time they know their count.
-        if (MODE != MODE_FUSED) return;
+        if (MODE != MODE_FUSED) return true;
         const int64_t bse = t == 0 ? 0 : lookback_predecessors<CSR2_LB_DEPTH>(tile_state, t, &ctl->status, CSR2_LB_SLEEP, &s_hurry, CSR2_LB_HURRY);
         CountBar::sync();  // the workers have published the tile's count by now
         const int total = s_total;
         if (lane_id() == 0) {
             if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
             s_base = bse;
-            if (bse >= 0 && t == (int)gridDim.x - 1) ctl->total = bse + total;
+            if (bse >= 0 && t == num_tiles - 1) ctl->total = bse + total;
         }
         __syncthreads();
-        return;
+        return true;
     }
 
     // ---- mark the first entry of every row that starts inside the tile with its row number
@@ -623,7 +628,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     const int rank = block_excl_sum<NT, WorkerBar>(mine, scan_tmp, total);  // its syncs also retire the key reads
     if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
-        return;
+        return true;
     }
     thread_rank[tid] = rank;
     thread_emit[tid] = emit;
@@ -667,7 +672,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     // ---- output base of the tile
     if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
     const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
-    if (base < 0) return;  // a bounded wait gave up; the host reports it
+    if (base < 0) return true;  // a bounded wait gave up; the host reports it
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
     // tile those are the survivors among the first d = (A entries before row r) + (B entries
@@ -691,6 +696,7 @@ __device__ __forceinline__ void csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         gz_col[i] = (int32_t)p.x;
         gz_val[i] = __uint_as_float(p.y);
     }
+    return true;
 }
 
 template <int VT, int OP, int MODE>
@@ -724,12 +730,64 @@ __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __gr
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
     const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
     if (narrow) {
-        csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar);
+        csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar,
+                                     (int)gridDim.x, 0u);
     } else {
         if (threadIdx.x >= NT) return;  // the generic body works with the NT worker threads alone
-        csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit);
+        csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit,
+                                                  (int)gridDim.x);
     }
 }
+
+#if CSR2_RESIDENT
+// The single-pass launch as resident CTAs that take tile after tile from a ticket. A tile is only
+// ever taken by a running CTA and after every earlier tile was taken, so the look-back waits on
+// running CTAs whatever the number of resident ones; the next ticket is fetched while the current
+// tile is worked on, and a CTA's start-up (shared memory, barrier, first loads) is paid once per
+// CTA instead of once per tile. Wide-key tiles run the generic body on the worker threads alone;
+// the scan warp sits them out at the barrier that ends every tile.
+template <int VT, int OP>
+__global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile_resident(const __grid_constant__ CsrIn A, const __grid_constant__ CsrIn B,
+                                                                                  const __grid_constant__ Cuts cuts, int cbits, int num_tiles,
+                                                                                  uint64_t *tile_state, FusedCtl *ctl,
+                                                                                  const __grid_constant__ CsrOut Z) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int scan_tmp[72];
+    __shared__ int thread_rank[NT];
+    __shared__ unsigned thread_emit[NT];
+    __shared__ __align__(8) uint64_t mbar;
+    __shared__ int s_next;
+    if (threadIdx.x == 0) {
+        s_next = atomicAdd(&ctl->ticket, 1);
+        mbar_init(&mbar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    unsigned phase = 0u;  // parity of the copy barrier: it completes once per tile of the fast body
+    for (;;) {
+        const int t = s_next;
+        if (t >= num_tiles) break;  // uniform: every thread reads the same word
+        __syncthreads();            // ... and has read it before it is replaced
+        if (threadIdx.x == NT) s_next = atomicAdd(&ctl->ticket, 1);  // by the scan warp: it has slack, the workers do not wait for the reply
+        const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
+        const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
+        bool go_on = true;
+        if (narrow) {
+            go_on = csr2_tile_fast<VT, OP, MODE_FUSED>(A, B, cuts, cbits, t, nullptr, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank,
+                                                       thread_emit, &mbar, num_tiles, phase);
+            phase ^= 1u;
+        } else if (threadIdx.x < NT) {
+            csr2_tile_generic<uint64_t, VT, OP, MODE_FUSED>(A, B, cuts, 32, t, nullptr, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank,
+                                                            thread_emit, num_tiles);
+        }
+        __syncthreads();  // the tile is stored: shared memory may be reused, the next ticket is in place
+        if (!go_on) break;  // uniform (decided at a CTA-wide barrier vote)
+        // the next tile's bulk copies overwrite what the threads read and wrote through ordinary
+        // loads and stores up to the barrier above: order the two proxies
+        if (threadIdx.x == 0) fence_async_smem();
+    }
+}
+#endif  // CSR2_RESIDENT
 
 // ------------------------------------------------------------------------ host driver ----
 
@@ -767,6 +825,29 @@ cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cb
     }
     static const char *const names[2][3] = {{"csr_add_count", "csr_add_fill", "csr_add_fused"},
                                             {"csr_mul_count", "csr_mul_fill", "csr_mul_fused"}};
+#if CSR2_RESIDENT
+    if (MODE == MODE_FUSED) {
+        // resident CTAs that take tiles from the ticket in ctl (zeroed by the caller with the tile words)
+        auto resident = k_csr2_tile_resident<VT_CSR2, OP>;
+        static int ctas[64] = {};  // CTAs that fit the device at once, per instantiation and device
+        if (dev < 0 || dev >= 64 || ctas[dev] == 0) {
+            cudaError_t e = cudaFuncSetAttribute(resident, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            int per_sm = 0, sms = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, resident, NT + 32, smem);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev < 0 ? 0 : dev);
+            if (e != cudaSuccess) return e;
+            const int fit = std::max(1, per_sm) * std::max(1, sms);
+            if (dev >= 0 && dev < 64) ctas[dev] = fit;
+            LaunchScope scope(names[OP][MODE], stream);
+            resident<<<std::min(num_tiles, fit), NT + 32, smem, stream>>>(A, B, cuts, cbits, num_tiles, tile_state, ctl, Z);
+            return cudaGetLastError();
+        }
+        LaunchScope scope(names[OP][MODE], stream);
+        resident<<<std::min(num_tiles, ctas[dev]), NT + 32, smem, stream>>>(A, B, cuts, cbits, num_tiles, tile_state, ctl, Z);
+        return cudaGetLastError();
+    }
+#endif
     LaunchScope scope(names[OP][MODE], stream);
     kernel<<<num_tiles, NT + 32, smem, stream>>>(A, B, cuts, cbits, tile_count, tile_state, ctl, Z);
     return cudaGetLastError();
