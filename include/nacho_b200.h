@@ -151,6 +151,20 @@ int nb200_csr_add_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
 int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
                               int64_t capacity, void *stream);
 
+/* Asynchronous forms of add and multiply: like the _into forms with a capacity of at least the
+ * worst case (nnz(A) + nnz(B) for add, min(nnz(A), nnz(B)) for multiply; less returns
+ * NB200_E_CAPACITY), but the call returns as soon as its kernels are queued. The result length and
+ * the device-side status arrive, in stream order, in two int64 DEVICE words:
+ * device_result[0] = nnz(Z), device_result[1] = an nb200_status (NB200_OK, NB200_E_TIMEOUT or
+ * NB200_E_OVERFLOW). z->nnz is left 0. For callers that consume the length on the device -- a
+ * multi-GPU stitch that all-gathers the block lengths, a pipeline that launches the next operator
+ * from the same stream -- and must not stall the host once per call. The reference has no
+ * counterpart: its drivers read every length back (src/backend/stitch_and_generate_gpu.cpp:660-671). */
+int nb200_csr_add_f32_async(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity,
+                            int64_t *device_result, void *stream);
+int nb200_csr_mul_f32_async(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity,
+                            int64_t *device_result, void *stream);
+
 /* Z = A .* B, sorted intersection per row, value a * b. Replaces
  * csr_mul::csr_mul_gpu_i32_f32 (compiler.cpp:116; src/backend/compute.cpp:434-440). An empty
  * result has an all-zero row_ptr (src/backend/stitch_and_generate.cpp:168-220).
@@ -167,6 +181,9 @@ int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
  * download of the one before overlap. z->row_ptr (rows + 1), z->col and z->val (`capacity`
  * entries each) are the caller's; on return z->nnz is the result length and the arrays are
  * complete (the call synchronises its own streams). NB200_E_CAPACITY if the result does not fit.
+ * Calls on one device take turns (the library holds a per-device lock for the whole call); on any
+ * error return the call has first waited for every copy it had queued, so the host buffers are no
+ * longer read or written once it is back.
  * The reference has no counterpart: its operators take device tensors only. */
 int nb200_csr_add_f32_host(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity);
 int nb200_csr_mul_f32_host(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity);
@@ -199,7 +216,9 @@ int nb200_spgemm_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int32
  * a _symbolic call on the same arrays, device and stream, with no other call of this library on
  * that stream in between, reuses what _symbolic left in the scratch pool (row bins and the column
  * bitmaps of the long rows, up to 8 GiB) instead of computing it again; any other order of calls
- * is equally valid and recomputes. */
+ * is equally valid and recomputes. That reuse assumes the patterns of A and B (row offsets and
+ * columns) are unchanged between the two calls -- their values may differ -- and that c->row_ptr is
+ * the array _symbolic filled; a caller that rewrites a pattern in place must call _symbolic again. */
 int nb200_spgemm_f32_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
                               int64_t *products, void *stream);
 int nb200_spgemm_f32_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
@@ -220,12 +239,25 @@ int nb200_coo3d_add_f32_into(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo
  * j_idx n_j(A)+n_j(B); k_ptr that + 1; k_idx / val n_k(A)+n_k(B). The _into form takes the
  * three capacities (entries of i_idx, j_idx, k_idx); j_ptr / k_ptr must hold one entry more
  * than cap_i / cap_j, and cap_k must be at least n_k(A)+n_k(B) (the merge works in place in
- * the result's k_idx / val arrays). Extents needing more than 63 bits in total
- * (bits(dim0)+bits(dim1)+bits(dim2)) return NB200_E_UNSUPPORTED, here and for COO3. */
+ * the result's k_idx / val arrays). Any extents up to 2^31 - 1 per mode work, here and for COO3:
+ * coordinates that fit 63 bits together are merged as packed 64-bit keys, wider ones as
+ * (i, j) / k word pairs (the reference's three-int32 tuple compare, src/backend/tensor.cpp:447-560). */
 int nb200_csf_add_f32(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z,
                       int32_t num_blocks, int32_t threads_per_block, void *stream);
 int nb200_csf_add_f32_into(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z,
                            int64_t cap_i, int64_t cap_j, int64_t cap_k, void *stream);
+
+/* ---- self-test -------------------------------------------------------------------------- */
+
+/* Exercises the give-up path of the bounded device-side waits without faulting or hanging the
+ * GPU: runs the single-pass CSR add on (a, b) WITHOUT its first tile and with a look-back limit of
+ * `polls` polls, so that the second tile waits for a count nobody publishes, gives up, records it
+ * and lets its successors through. Needs operands of at least three tiles (a few thousand entries
+ * each); `capacity` >= nnz(A) + nnz(B). Returns NB200_E_TIMEOUT when the path works (the contents
+ * of z are then meaningless, but every write stayed inside its arrays); the context stays usable.
+ * Has no counterpart in the reference, which has no device-side waits. */
+int nb200_selftest_lookback_timeout(const nb200_csr *a, const nb200_csr *b, nb200_csr *z,
+                                    int64_t capacity, int32_t polls, void *stream);
 
 #ifdef __cplusplus
 }

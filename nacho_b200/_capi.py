@@ -53,6 +53,9 @@ PROTOTYPES = {
     "nb200_csr_add_f32": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),
     "nb200_csr_add_f32_into": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p]),
     "nb200_csr_add_f32_noalloc": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p]),
+    "nb200_csr_add_f32_async": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p, C.c_void_p]),
+    "nb200_csr_mul_f32_async": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p, C.c_void_p]),
+    "nb200_selftest_lookback_timeout": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_int32, C.c_void_p]),
     "nb200_csr_mul_f32": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),
     "nb200_csr_mul_f32_into": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64, C.c_void_p]),
     "nb200_csr_add_f32_host": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int64]),

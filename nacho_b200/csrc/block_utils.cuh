@@ -205,11 +205,12 @@ __device__ __forceinline__ void st_relaxed_gpu_i32(int *p, int v) {
 // needed); until then the warp polls, sleeping `sleep_ns` between polls -- or `hurry_ns` once
 // `*hurry` is non-zero (the caller's own tile is waiting for the result by then, so the poll
 // traffic no longer competes with useful work). Returns -1 (and records the tile in `status`) if
-// a bounded wait gives up. Called by all 32 lanes of one warp, t > 0.
+// a bounded wait gives up after `poll_limit` polls of one round. Called by all 32 lanes of one
+// warp, t > 0.
 template <int DEPTH = 1>
 __device__ __forceinline__ int64_t lookback_predecessors(volatile uint64_t *state, int t, DeviceStatus *status,
                                                          unsigned sleep_ns, const volatile int *hurry = nullptr,
-                                                         unsigned hurry_ns = 64) {
+                                                         unsigned hurry_ns = 64, const int poll_limit = LOOKBACK_POLL_LIMIT) {
     // One round covers DEPTH * 32 predecessors, nearest first (word j of a lane is tile
     // pos - 32 j - lane), with all of a lane's loads in flight together.
     int64_t exclusive = 0;
@@ -239,7 +240,7 @@ __device__ __forceinline__ int64_t lookback_predecessors(volatile uint64_t *stat
                 }
             }
             if (ready) break;
-            if (polls >= LOOKBACK_POLL_LIMIT) {
+            if (polls >= poll_limit) {
                 if (lane_id() == 0 && atomicCAS(&status->error, 0, ERR_LOOKBACK_TIMEOUT) == 0) status->detail = t;
                 return -1;
             }

@@ -7,7 +7,8 @@
 // (src/backend/partition.cpp:813-993, :964-983). Here each coordinate is packed into one
 // 64-bit key, i in the top bits, then j, then k, using just enough bits for each extent, so
 // that tuple order is integer order. Tensors whose three extents need more than 63 bits in
-// total are refused with NB200_E_UNSUPPORTED.
+// total take a second, simpler tile kernel that compares (i, j) and k as a 64-bit and a 32-bit
+// word, i.e. the full three-int32 tuple compare of the reference for any extents.
 //
 // Kernels: k_coo3_partition (one warp per tile cut, 32-ary diagonal search) and k_coo3_tile
 // (one CTA per tile: pack keys into shared memory, split by merge-path, merge VT entries per
@@ -51,6 +52,7 @@ struct Coo3Out {
 };
 
 struct Packing {
+    using Key = uint64_t;
     int bj, bk;  // bits of j and k; i takes the rest
     __host__ __device__ uint64_t pack(int32_t i, int32_t j, int32_t k) const {
         return ((((uint64_t)(uint32_t)i << bj) | (uint32_t)j) << bk) | (uint32_t)k;
@@ -60,12 +62,28 @@ struct Packing {
     __host__ __device__ int32_t k_of(uint64_t key) const { return (int32_t)(key & ((1ull << bk) - 1ull)); }
 };
 
+// Coordinates too wide for one 64-bit word: (i, j) in one word, k in another, compared in that
+// order -- the three-int32 tuple order of the reference (src/backend/tensor.cpp:447-560).
+struct Key96 {
+    uint64_t ij;
+    uint32_t k;
+    __device__ bool operator<=(const Key96 &o) const { return ij < o.ij || (ij == o.ij && k <= o.k); }
+    __device__ bool operator==(const Key96 &o) const { return ij == o.ij && k == o.k; }
+};
+struct WidePacking {
+    using Key = Key96;
+    __device__ Key96 pack(int32_t i, int32_t j, int32_t k) const {
+        return Key96{((uint64_t)(uint32_t)i << 32) | (uint32_t)j, (uint32_t)k};
+    }
+};
+
 struct Cuts2 {
     int32_t *a;
     int32_t *b;
 };
 
-__device__ __forceinline__ uint64_t key_at(const Coo3In &T, const Packing &pk, int64_t p) {
+template <typename PK>
+__device__ __forceinline__ typename PK::Key key_at(const Coo3In &T, const PK &pk, int64_t p) {
     return pk.pack(ld_nc(T.i + p), ld_nc(T.j + p), ld_nc(T.k + p));
 }
 
@@ -76,7 +94,8 @@ __device__ __forceinline__ uint64_t key_at(const Coo3In &T, const Packing &pk, i
 // stay on one side of a cut.
 constexpr int COARSE = 32;
 
-__device__ __forceinline__ void finish_cut(const Coo3In &A, const Coo3In &B, const Packing &pk, int64_t d, int64_t x,
+template <typename PK>
+__device__ __forceinline__ void finish_cut(const Coo3In &A, const Coo3In &B, const PK &pk, int64_t d, int64_t x,
                                            int32_t *pa, int32_t *pb) {
     int64_t y = d - x;
     if (x > 0 && y < B.nnz && key_at(A, pk, x - 1) == key_at(B, pk, y)) ++y;
@@ -84,7 +103,8 @@ __device__ __forceinline__ void finish_cut(const Coo3In &A, const Coo3In &B, con
     *pb = (int32_t)y;
 }
 
-__global__ void __launch_bounds__(NT) k_coo3_partition_coarse(Coo3In A, Coo3In B, Packing pk, int64_t total, int32_t tile_step,
+template <typename PK>
+__global__ void __launch_bounds__(NT) k_coo3_partition_coarse(Coo3In A, Coo3In B, PK pk, int64_t total, int32_t tile_step,
                                                               int32_t num_tiles, Cuts2 cuts) {
     const int c = (blockIdx.x * NT + threadIdx.x) >> 5;
     const int64_t t64 = (int64_t)c * COARSE;
@@ -109,7 +129,8 @@ __global__ void __launch_bounds__(NT) k_coo3_partition_coarse(Coo3In A, Coo3In B
     }
 }
 
-__global__ void __launch_bounds__(NT) k_coo3_partition_fine(Coo3In A, Coo3In B, Packing pk, int64_t total, int32_t tile_step,
+template <typename PK>
+__global__ void __launch_bounds__(NT) k_coo3_partition_fine(Coo3In A, Coo3In B, PK pk, int64_t total, int32_t tile_step,
                                                             int32_t num_tiles, Cuts2 cuts) {
     const int t = blockIdx.x * NT + threadIdx.x;
     if (t >= num_tiles || t % COARSE == 0) return;
@@ -471,7 +492,141 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
     }
 }
 
+// ---------------------------------------------------------------- wide coordinates ----
+
+// Tile kernel for extents that need more than 63 bits together. One CTA of WNT threads per tile of
+// WNT * WVT - 1 merged entries: (i, j) words and k words staged in shared memory with plain loads,
+// merge-path split with the two-word compare, sequential merge of WVT entries per thread, values
+// fetched from global memory, compaction through shared memory, coalesced stores. Single pass with
+// bounded look-back, or count / fill around a scan, like the packed-key kernel.
+constexpr int WNT = 256, WVT = 7, WCAP = WNT * WVT, WKS = WCAP + 2 + WVT;
+
+template <int MODE>
+__global__ void __launch_bounds__(WNT) k_coo3_tile_wide(Coo3In A, Coo3In B, Cuts2 cuts, int32_t *tile_count, uint64_t *tile_state_raw,
+                                                         FusedCtl *ctl, Coo3Out Z) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int scan_tmp[40];
+    __shared__ long long s_base;
+    volatile uint64_t *tile_state = tile_state_raw;
+    const WidePacking pk;
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x;  // CTAs are dispatched in index order; waits on earlier tiles are bounded
+    const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
+    const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
+    const int n = na + nb;
+    uint64_t *hx = reinterpret_cast<uint64_t *>(smem_raw), *hy = hx + na + 1;
+    uint32_t *lx = reinterpret_cast<uint32_t *>(hx + WKS), *ly = lx + na + 1;
+    float *out_val = reinterpret_cast<float *>(lx + WKS);
+    for (int e = tid; e < na; e += WNT) {
+        const Key96 q = key_at(A, pk, (int64_t)a0 + e);
+        hx[e] = q.ij;
+        lx[e] = q.k;
+    }
+    for (int e = tid; e < nb; e += WNT) {
+        const Key96 q = key_at(B, pk, (int64_t)b0 + e);
+        hy[e] = q.ij;
+        ly[e] = q.k;
+    }
+    if (tid < WVT + 1) hy[nb + tid] = ~0ull, ly[nb + tid] = ~0u;  // all-ones orders after every coordinate
+    if (tid == 0) hx[na] = ~0ull, lx[na] = ~0u;
+    __syncthreads();
+    auto kx = [&](int p) { return Key96{hx[p], lx[p]}; };
+    auto ky = [&](int p) { return Key96{hy[p], ly[p]}; };
+
+    // ---- split the tile among threads: merge-path diagonal tid * WVT, ties take A first
+    const int diag = min(tid * WVT, n);
+    int x, y;
+    {
+        int lo = max(0, diag - nb), hi = min(diag, na);
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (kx(mid) <= ky(diag - 1 - mid)) lo = mid + 1; else hi = mid;
+        }
+        x = lo;
+        y = diag - lo;
+    }
+    const int x0 = x, y0 = y;
+
+    // ---- merge WVT entries; bit i of `from_a`: entry i came from A; of `twin`: the same
+    // coordinate is in B too; of `emit`: the entry goes to the result
+    Key96 key[WVT];
+    unsigned from_a = 0, twin = 0, emit = 0;
+    {
+        const int valid = min(WVT, n - diag);
+        Key96 cx = kx(x), cy = ky(y);
+        Key96 last_x = x > 0 ? kx(x - 1) : Key96{~0ull, ~0u};
+#pragma unroll
+        for (int i = 0; i < WVT; ++i) {
+            const bool tx = cx <= cy;
+            const bool both = cx == cy;
+            key[i] = tx ? cx : cy;
+            from_a |= (unsigned)tx << i;
+            twin |= (unsigned)(tx && both) << i;
+            emit |= (unsigned)(i < valid && (tx || !(cy == last_x))) << i;
+            last_x = tx ? cx : last_x;
+            x += tx;
+            y += !tx;
+            cx = kx(x);
+            cy = ky(y);
+        }
+    }
+    int total;
+    const int rank = block_excl_sum<WNT>(__popc(emit), scan_tmp, total);  // syncs: key reads are done
+    if (MODE == MODE_COUNT) {
+        if (tid == 0) tile_count[t] = total;
+        return;
+    }
+    if (MODE == MODE_FUSED && warp_id() == 0) {
+        const int64_t b = lookback_exclusive(tile_state, t, total, &ctl->status);
+        if (lane_id() == 0) {
+            s_base = b;
+            if (b >= 0 && t == (int)gridDim.x - 1) ctl->total = b + total;
+        }
+    }
+    // ---- compact through shared memory (the staging arrays reuse the key words), store coalesced
+    {
+        int r = rank, xi = x0, yi = y0;
+#pragma unroll
+        for (int i = 0; i < WVT; ++i) {
+            const bool tx = (from_a >> i) & 1u;
+            if ((emit >> i) & 1u) {
+                float v = tx ? ld_nc(A.val + a0 + xi) : ld_nc(B.val + b0 + yi);
+                if ((twin >> i) & 1u) v = v + ld_nc(B.val + b0 + yi);
+                hx[r] = key[i].ij;
+                lx[r] = key[i].k;
+                out_val[r] = v;
+                ++r;
+            }
+            xi += tx;
+            yi += !tx;
+        }
+    }
+    __syncthreads();
+    const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
+    if (base < 0) return;  // a bounded wait gave up; the host reports it
+    for (int e = tid; e < total; e += WNT) {
+        const uint64_t ij = hx[e];
+        Z.i[base + e] = (int32_t)(ij >> 32);
+        Z.j[base + e] = (int32_t)(uint32_t)ij;
+        Z.k[base + e] = (int32_t)lx[e];
+        Z.val[base + e] = out_val[e];
+    }
+}
+
+constexpr size_t coo3_wide_smem_bytes() { return 12 * (size_t)WKS + 4 * (size_t)WCAP; }
+
+template <int MODE>
+cudaError_t launch_coo3_tile_wide(const Coo3In &A, const Coo3In &B, const Cuts2 &cuts, int32_t *tile_count, uint64_t *tile_state,
+                                  FusedCtl *ctl, const Coo3Out &Z, int num_tiles, cudaStream_t stream) {
+    static const char *const names[3] = {"coo3_add_wide_count", "coo3_add_wide_fill", "coo3_add_wide_fused"};
+    LaunchScope scope(names[MODE], stream);
+    k_coo3_tile_wide<MODE><<<num_tiles, WNT, coo3_wide_smem_bytes(), stream>>>(A, B, cuts, tile_count, tile_state, ctl, Z);
+    return cudaGetLastError();
+}
+
 constexpr size_t coo3_smem_bytes() { return 16 * (size_t)RAW_SLOTS; }
+static_assert(coo3_wide_smem_bytes() <= 48 * 1024, "the wide tile kernel stays within the default shared-memory limit");
+
 
 int bits_for(int32_t extent) {
     int b = 1;
@@ -517,10 +672,11 @@ int check_coo3(const nb200_coo3 *t) {
 // `csf`, when given, asks the single-pass launch to write the CSF3 levels above k instead of the
 // merged i and j columns (z->i and z->j may then be null); `*csf_done` tells whether that
 // happened (the count -> scan -> fill route does not do it).
-int64_t coo3_add_tiles(int64_t total_entries) { return (total_entries + (CAP - 1) - 1) / (CAP - 1); }
+// (Both sized for the smaller tile of the wide-coordinate kernel, an upper bound for the other.)
+int64_t coo3_add_tiles(int64_t total_entries) { return (total_entries + (WCAP - 1) - 1) / (WCAP - 1); }
 
 size_t coo3_add_scratch_bytes(int64_t total_entries) {
-    const int64_t tiles = (total_entries + (CAP - 1) - 1) / (CAP - 1);
+    const int64_t tiles = coo3_add_tiles(total_entries);
     Carver sizes;
     sizes.take<int32_t>((size_t)tiles + 1);
     sizes.take<int32_t>((size_t)tiles + 1);
@@ -538,10 +694,10 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     if (!z || a->dims[0] != b->dims[0] || a->dims[1] != b->dims[1] || a->dims[2] != b->dims[2]) return NB200_E_BADARG;
     if (!alloc && capacity < 0) return NB200_E_BADARG;
     const int bi = bits_for(a->dims[0]), bj = bits_for(a->dims[1]), bk = bits_for(a->dims[2]);
-    if (bi + bj + bk > 63) return NB200_E_UNSUPPORTED;
+    const bool wide = bi + bj + bk > 63;  // the coordinates do not pack into one 64-bit key
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const int64_t total = (int64_t)a->nnz + b->nnz;
-    constexpr int tile_step = CAP - 1;
+    const int tile_step = wide ? WCAP - 1 : CAP - 1;
     const int64_t tiles64 = (total + tile_step - 1) / tile_step;
     if (tiles64 > INT32_MAX - 1) return NB200_E_OVERFLOW;
     const int num_tiles = (int)tiles64;
@@ -574,7 +730,7 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     cuts.a = carve.take<int32_t>((size_t)num_tiles + 1);
     cuts.b = carve.take<int32_t>((size_t)num_tiles + 1);
     int32_t *tile_count = carve.take<int32_t>((size_t)num_tiles + 1);
-    int64_t *d_total = carve.take<int64_t>(1);
+    carve.take<int64_t>(1);
     uint64_t *fused_block = carve.take<uint64_t>((size_t)num_tiles + 8);
     FusedCtl *ctl = reinterpret_cast<FusedCtl *>(fused_block);
     uint64_t *tile_state = fused_block + 4;
@@ -583,12 +739,11 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     const Packing pk{bj, bk};
     static const bool force_two_pass = [] { const char *e = std::getenv("NACHO_B200_TWO_PASS"); return e && e[0] == '1'; }();
     const bool fused = alloc || (capacity >= total && !force_two_pass);
-    const bool levels = fused && csf != nullptr && !alloc;
+    const bool levels = fused && csf != nullptr && !alloc && !wide;  // the wide kernel writes coordinates only
     if (!levels && !alloc && capacity > 0 && (!z->i || !z->j)) return NB200_E_BADARG;
-    cudaError_t e;
+    cudaError_t e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * (fused ? (size_t)num_tiles + 4 : 4), stream);
+    if (e != cudaSuccess) return note_cuda_error(e, "cudaMemsetAsync");
     if (fused) {
-        e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream);
-        if (e != cudaSuccess) return note_cuda_error(e, "cudaMemsetAsync");
         if (alloc) {
             void **arrays[4] = {reinterpret_cast<void **>(&z->i), reinterpret_cast<void **>(&z->j),
                                 reinterpret_cast<void **>(&z->k), reinterpret_cast<void **>(&z->val)};
@@ -601,14 +756,21 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     {
         LaunchScope scope("coo3_partition", stream);
         const int warps = num_tiles / COARSE + 2;
-        k_coo3_partition_coarse<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
-        k_coo3_partition_fine<<<(num_tiles + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        if (wide) {
+            k_coo3_partition_coarse<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, WidePacking{}, total, tile_step, num_tiles, cuts);
+            k_coo3_partition_fine<<<(num_tiles + NT - 1) / NT, NT, 0, stream>>>(A, B, WidePacking{}, total, tile_step, num_tiles, cuts);
+        } else {
+            k_coo3_partition_coarse<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+            k_coo3_partition_fine<<<(num_tiles + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        }
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_coo3_partition"));
     const Coo3Out Z{z->i, z->j, z->k, z->val};
     if (fused) {
-        if (levels) {
+        if (wide) {
+            e = launch_coo3_tile_wide<MODE_FUSED>(A, B, cuts, nullptr, tile_state, ctl, Z, num_tiles, stream);
+        } else if (levels) {
             e = launch_coo3_tile<MODE_FUSED, true>(A, B, pk, cuts, nullptr, tile_state, ctl, Z, num_tiles, stream, *csf);
             if (csf_done) *csf_done = true;
         } else {
@@ -625,23 +787,35 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
         z->nnz = (int32_t)h.total;
         return NB200_OK;
     }
-    e = launch_coo3_tile<MODE_COUNT>(A, B, pk, cuts, tile_count, nullptr, nullptr, Coo3Out{}, num_tiles, stream);
+    // count -> scan -> fill. The scan leaves the result length in the control block, whose status
+    // word also collects a give-up of either tile launch (a bulk copy that did not land in time).
+    auto read_ctl = [&](FusedCtl &h) -> int {
+        cudaError_t c = cudaMemcpyAsync(host_slot, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream);
+        if (c == cudaSuccess) c = cudaStreamSynchronize(stream);
+        if (c != cudaSuccess) return note_cuda_error(c, "read result length");
+        std::memcpy(&h, host_slot, sizeof(h));
+        return NB200_OK;
+    };
+    FusedCtl h;
+    e = wide ? launch_coo3_tile_wide<MODE_COUNT>(A, B, cuts, tile_count, nullptr, ctl, Coo3Out{}, num_tiles, stream)
+             : launch_coo3_tile<MODE_COUNT>(A, B, pk, cuts, tile_count, nullptr, ctl, Coo3Out{}, num_tiles, stream);
     if (e != cudaSuccess) return note_cuda_error(e, "k_coo3_tile<count>");
     {
         LaunchScope scope("scan_tiles", stream);
-        k_scan_tiles<<<1, 1024, 0, stream>>>(tile_count, num_tiles, d_total);
+        k_scan_tiles<<<1, 1024, 0, stream>>>(tile_count, num_tiles, reinterpret_cast<int64_t *>(&ctl->total));
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return note_cuda_error(e, "k_scan_tiles");
-    e = cudaMemcpyAsync(host_slot, d_total, sizeof(int64_t), cudaMemcpyDeviceToHost, stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-    if (e != cudaSuccess) return note_cuda_error(e, "read result length");
-    const int64_t nnz = host_slot[0];
-    if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
-    z->nnz = (int32_t)nnz;
-    if (nnz > capacity) return NB200_E_CAPACITY;
-    e = launch_coo3_tile<MODE_FILL>(A, B, pk, cuts, tile_count, nullptr, nullptr, Z, num_tiles, stream);
+    if ((st = read_ctl(h))) return st;
+    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.total > INT32_MAX) return NB200_E_OVERFLOW;
+    z->nnz = (int32_t)h.total;
+    if (h.total > capacity) return NB200_E_CAPACITY;
+    e = wide ? launch_coo3_tile_wide<MODE_FILL>(A, B, cuts, tile_count, nullptr, ctl, Z, num_tiles, stream)
+             : launch_coo3_tile<MODE_FILL>(A, B, pk, cuts, tile_count, nullptr, ctl, Z, num_tiles, stream);
     if (e != cudaSuccess) return note_cuda_error(e, "k_coo3_tile<fill>");
+    if ((st = read_ctl(h))) return st;
+    if (h.status.error != 0) return NB200_E_TIMEOUT;
     return NB200_OK;
 }
 

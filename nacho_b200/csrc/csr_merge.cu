@@ -4,12 +4,13 @@
 // The merged sequence of all stored entries of A and B, ordered by (row, column) with A first
 // on ties, is cut into tiles of TILE_STEP entries. A partition kernel finds every cut with
 // warp-wide 32-ary searches (rows on the summed row offsets, then the merge-path diagonal
-// inside the row). One CTA then owns one tile: it stages the tile's column indices and values
-// in shared memory with coalesced loads, turns them into composite (row-in-tile, column) keys
-// so that row boundaries need no special casing, splits the tile among its threads with an
-// in-shared-memory merge-path search, merges VT entries per thread in registers, compacts
-// the survivors with a CTA scan and writes them back coalesced. Row offsets of the result are
-// produced by the same pass: a tile owns the offsets of the rows that begin inside it.
+// inside the row). One CTA then owns one tile: the copy engine stages the tile's column indices
+// and values in shared memory, the columns are turned into composite (row-in-tile, column) keys
+// so that row boundaries need no special casing, and each of the CTA's eight worker warps merges
+// its share of the tile in registers (a bitonic network over register slots striped across the
+// warp), ranks the survivors with warp votes and stores them coalesced straight from registers.
+// Row offsets of the result are produced by the same pass: a tile owns the offsets of the rows
+// that begin inside it.
 //
 // Reference behaviour restated (not its code): partition src/backend/partition.cpp:813-993
 // (equal columns never split, :964-983), count src/backend/compute.cpp:152-271, fill
@@ -24,22 +25,17 @@
 #include "common.cuh"
 #include "merge_common.cuh"
 #include "tma.cuh"
+#include "warp_merge.cuh"
 
 namespace nb200 {
 
 namespace {
 
-// Tuning knobs (compile-time): threads per CTA, merged entries per thread, and the number of
-// CTAs per SM the register allocator is asked to leave room for.
-#ifndef CSR2_NT
-#define CSR2_NT 256
-#endif
-#ifndef CSR2_VT
-#define CSR2_VT 19
-#endif
-#ifndef CSR2_RESIDENT
-#define CSR2_RESIDENT 0      // 1: single pass as resident CTAs that take tile after tile from a ticket. Measured on
-                             // configuration 3: 1.21 ms against 0.69 ms with one CTA per tile, so it is off.
+// Tuning knobs (compile-time): register slots per lane of a worker warp (a warp merges up to
+// 32 * V entries at a time), and the number of CTAs per SM the register allocator is asked to
+// leave room for. The CTA always has 256 worker threads and one scan warp.
+#ifndef CSR2_V
+#define CSR2_V 20
 #endif
 #ifndef CSR2_LB_DEPTH
 #define CSR2_LB_DEPTH 1      // predecessors read per round of the look-back, in units of 32
@@ -54,7 +50,7 @@ namespace {
 #ifndef CSR2_MIN_CTAS
 #define CSR2_MIN_CTAS 3
 #endif
-constexpr int NT = CSR2_NT;
+constexpr int NT = 256;
 
 
 struct CsrIn {
@@ -127,42 +123,58 @@ __global__ void __launch_bounds__(NT) k_csr2_partition(CsrIn A, CsrIn B, int32_t
 
 // ------------------------------------------------------------------------ tile kernel ----
 
-template <typename KeyT>
-struct KeyTraits;
-
-template <>
-struct KeyTraits<uint32_t> {
-    static constexpr uint32_t INF = 0xffffffffu;
-    __device__ static __forceinline__ uint32_t row_of(uint32_t k, int cbits) { return k >> cbits; }
-    __device__ static __forceinline__ uint32_t col_of(uint32_t k, int cbits) { return k & ((1u << cbits) - 1u); }
-    __device__ static __forceinline__ uint32_t make(uint32_t row, uint32_t col, int cbits) { return (row << cbits) | col; }
-};
-
-template <>
-struct KeyTraits<uint64_t> {
-    static constexpr uint64_t INF = ~0ull;
-    __device__ static __forceinline__ uint32_t row_of(uint64_t k, int) { return (uint32_t)(k >> 32); }
-    __device__ static __forceinline__ uint32_t col_of(uint64_t k, int) { return (uint32_t)k; }
-    __device__ static __forceinline__ uint64_t make(uint32_t row, uint32_t col, int) { return ((uint64_t)row << 32) | col; }
-};
-
 // Hardware barriers of the tile kernel: 0 = the whole CTA (__syncthreads), 1 = the NT worker
 // threads, 2 = workers arrive / the scan warp waits ("the tile's count is known").
 using WorkerBar = NamedBarrier<1, NT>;
 using CountBar = NamedBarrier<2, NT + 32>;
 
-// Generic tile body: any key width, plain loads and stores. Used for the tiles whose rows do not
-// fit a 32-bit composite key; the common case takes csr2_tile_fast below.
-template <typename KeyT, int VT, int OP, int MODE>
+// Shared-memory plan of the tile kernel, in 4-byte words. The tile's column indices (turned into
+// keys in place) and values use the same word positions in two arrays of SLOTS words: A's entry e
+// sits at word oa + e and B's at word obv + e, where oa and obv are chosen so that a global address
+// on a 16-byte boundary lands on a 16-byte boundary in shared memory too (what a bulk copy needs).
+//
+// The eight worker warps each take STEP_W merged entries of the tile (one more or less where a cut
+// would separate the two entries of one position), hold them in 32 * V register slots and write
+// them to the result from there, so nothing else is staged.
+template <int V>
+struct WarpPlan {
+    static constexpr int W = NT / 32;                              // worker warps
+    static constexpr int CH = V <= 12 ? 12 : (V <= 20 ? 20 : 28);  // key words each thread scans
+    static constexpr int SLOTS = NT * CH;                          // key words = value words
+    static constexpr int FIT = (SLOTS - 12) / W;                   // entries per warp the staging area has room for
+    static constexpr int STEP_W = 32 * V - 1 < FIT ? 32 * V - 1 : FIT;
+    static constexpr int TILE_STEP = W * STEP_W - 1;               // merged entries between two tile cuts
+    static constexpr int CAP = TILE_STEP + 1;                      // most merged entries of one tile
+    static constexpr size_t BYTES = 8 * (size_t)SLOTS;
+    // A thread's CH-word chunk is read and written as 16-byte vectors; an odd number of vectors
+    // per chunk keeps those accesses free of shared-memory bank conflicts.
+    static_assert((CH / 4) % 2 == 1, "the chunk must be an odd number of 16-byte vectors");
+    static_assert(CAP + 12 <= SLOTS, "the padded tile must fit the staging arrays");
+    static_assert(STEP_W + 1 <= 32 * V, "a warp's entries must fit its register slots");
+    static_assert(V <= 32, "slot masks are 32 bits wide");
+};
+
+// Merged entries per thread of the wide-key body, so that its CTA covers a whole tile.
+template <int V>
+struct WideVt {
+    static constexpr int value = (WarpPlan<V>::CAP + NT - 1) / NT;
+};
+
+// Tiles whose rows do not fit a 32-bit composite key (long runs of empty rows) take this body:
+// 64-bit keys (row in tile, column), plain loads, a sequential merge of VT entries per thread,
+// values fetched from global memory. It is rarely taken and kept simple; the common case is
+// csr2_tile_warp below.
+template <int VT, int OP, int MODE>
 // (Not inlined, so the structs are taken by address: the kernel declares them __grid_constant__,
 // which lets that address point at the parameter space instead of a per-thread stack copy.)
-__device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits,
-                                               const int t, int32_t *tile_count, volatile uint64_t *tile_state,
-                                               FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
-                                               int *scan_tmp, int *thread_rank, unsigned *thread_emit, const int num_tiles) {
-    using KT = KeyTraits<KeyT>;
-    constexpr int CAP = NT * VT;  // most merged entries a tile can hold
-    constexpr bool WRITES = MODE != MODE_COUNT;
+__device__ __noinline__ void csr2_tile_wide(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int t, int32_t *tile_count,
+                                            volatile uint64_t *tile_state, FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
+                                            const int num_tiles, const int poll_limit) {
+    constexpr uint64_t INF = ~0ull;
+    __shared__ int scan_tmp[72];
+    __shared__ int thread_rank[NT];
+    __shared__ unsigned thread_emit[NT];
+    __shared__ long long s_base;
     const int tid = threadIdx.x;
     const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
@@ -170,45 +182,24 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
     const int n = na + nb;
 
     // Shared layout: keys of A, a sentinel, keys of B, a sentinel, then VT words of slack so
-    // that the merge may read a little past the end; values mirror the same positions.
-    constexpr int KEY_SLOTS = CAP + 2 + VT;
-    KeyT *kx = reinterpret_cast<KeyT *>(smem_raw);
-    KeyT *ky = kx + na + 1;
-    float *vx = reinterpret_cast<float *>(smem_raw + sizeof(KeyT) * KEY_SLOTS);
-    float *vy = vx + na + 1;
+    // that the merge may read a little past the end.
+    constexpr int KEY_SLOTS = NT * VT + 2 + VT;
+    uint64_t *kx = reinterpret_cast<uint64_t *>(smem_raw);
+    uint64_t *ky = kx + na + 1;
+    unsigned *kx_hi = reinterpret_cast<unsigned *>(kx) + 1, *ky_hi = reinterpret_cast<unsigned *>(ky) + 1;
 
-    // ---- stage columns (and values) in shared memory, coalesced
-    for (int i = tid; i < na; i += NT) kx[i] = (KeyT)(uint32_t)ld_nc(A.col + a0 + i);
-    for (int i = tid; i < nb; i += NT) ky[i] = (KeyT)(uint32_t)ld_nc(B.col + b0 + i);
-    if (WRITES) {
-        for (int i = tid; i < na; i += NT) vx[i] = ld_nc(A.val + a0 + i);
-        for (int i = tid; i < nb; i += NT) vy[i] = ld_nc(B.val + b0 + i);
-    }
-    // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over
-    // the threads); kept in registers for the row-offset pass at the end
-    const int64_t my_row = (int64_t)i0 + 1 + tid;
-    int32_t my_sa = 0, my_sb = 0;
-    if (my_row <= i1) {
-        my_sa = ld_nc(A.rp + my_row) - a0;
-        my_sb = ld_nc(B.rp + my_row) - b0;
-    }
+    for (int i = tid; i < na; i += NT) kx[i] = (uint64_t)(uint32_t)ld_nc(A.col + a0 + i);
+    for (int i = tid; i < nb; i += NT) ky[i] = (uint64_t)(uint32_t)ld_nc(B.col + b0 + i);
     WorkerBar::sync();
 
     // ---- mark the first entry of every row that starts inside the tile with its row number
-    // relative to i0 (max wins where empty rows share a start), then spread it forward with a
-    // running maximum so that every entry carries its row in the high bits of its key.
-    for (int64_t r = my_row; r <= i1; r += NT) {
+    // relative to i0 in the key's upper word (max wins where empty rows share a start), then spread
+    // it forward with a running maximum so that every entry carries its row.
+    for (int64_t r = (int64_t)i0 + 1 + tid; r <= i1; r += NT) {
         const uint32_t rr = (uint32_t)(r - i0);
-        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
-        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
-        if (sa < na) {
-            if (sizeof(KeyT) == 4) atomicMax(reinterpret_cast<unsigned *>(kx) + sa, (rr << cbits) | ((unsigned)kx[sa] & ((1u << cbits) - 1u)));
-            else atomicMax(reinterpret_cast<unsigned *>(kx) + 2 * sa + 1, rr);
-        }
-        if (sb < nb) {
-            if (sizeof(KeyT) == 4) atomicMax(reinterpret_cast<unsigned *>(ky) + sb, (rr << cbits) | ((unsigned)ky[sb] & ((1u << cbits) - 1u)));
-            else atomicMax(reinterpret_cast<unsigned *>(ky) + 2 * sb + 1, rr);
-        }
+        const int sa = ld_nc(A.rp + r) - a0, sb = ld_nc(B.rp + r) - b0;
+        if (sa < na) atomicMax(kx_hi + 2 * sa, rr);
+        if (sb < nb) atomicMax(ky_hi + 2 * sb, rr);
     }
     WorkerBar::sync();
     {
@@ -216,23 +207,21 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
         const int lo = tid * VT, hi = min(lo + VT, n);
         unsigned ma = 0, mb = 0;
         for (int i = lo; i < hi; ++i) {
-            if (i < na) ma = max(ma, KT::row_of(kx[i], cbits)); else mb = max(mb, KT::row_of(ky[i - na], cbits));
+            if (i < na) ma = max(ma, kx_hi[2 * i]); else mb = max(mb, ky_hi[2 * (i - na)]);
         }
         unsigned ea, eb;
         block_excl_max2<NT, WorkerBar>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
         for (int i = lo; i < hi; ++i) {
             if (i < na) {
-                const KeyT k = kx[i];
-                ea = max(ea, KT::row_of(k, cbits));
-                kx[i] = KT::make(ea, KT::col_of(k, cbits), cbits);
+                ea = max(ea, kx_hi[2 * i]);
+                kx_hi[2 * i] = ea;
             } else {
-                const KeyT k = ky[i - na];
-                eb = max(eb, KT::row_of(k, cbits));
-                ky[i - na] = KT::make(eb, KT::col_of(k, cbits), cbits);
+                eb = max(eb, ky_hi[2 * (i - na)]);
+                ky_hi[2 * (i - na)] = eb;
             }
         }
-        if (tid < VT + 1) ky[nb + tid] = KT::INF;
-        if (tid == 0) kx[na] = KT::INF;
+        if (tid < VT + 1) ky[nb + tid] = INF;
+        if (tid == 0) kx[na] = INF;
     }
     WorkerBar::sync();
 
@@ -250,21 +239,20 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
     }
     const int x0 = x, y0 = y;
 
-    // ---- merge VT entries; straight-line code, no divergent branches. Bit i of `from_a` says
-    // entry i came from A, of `twin` that the same column is in B too, of `emit` that the
-    // entry goes to the result.
-    KeyT key[VT];
+    // ---- merge VT entries. Bit i of `from_a` says entry i came from A, of `twin` that the same
+    // column is in B too, of `emit` that the entry goes to the result.
+    uint32_t col[VT];
     unsigned from_a = 0, twin = 0, emit = 0;
     {
         const int valid = min(VT, n - diag);
-        KeyT hx = kx[x], hy = ky[y];
-        KeyT last_x = x > 0 ? kx[x - 1] : KT::INF;
+        uint64_t hx = kx[x], hy = ky[y];
+        uint64_t last_x = x > 0 ? kx[x - 1] : INF;
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
             const bool ok = i < valid;
             const bool tx = hx <= hy;
             const bool both = hx == hy;
-            key[i] = tx ? hx : hy;
+            col[i] = (uint32_t)(tx ? hx : hy);
             const bool out = OP == OP_UNION ? (tx || hy != last_x) : (tx && both);
             from_a |= (unsigned)tx << i;
             twin |= (unsigned)(tx && both) << i;
@@ -291,59 +279,59 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
     if (MODE == MODE_FILL) {
         base = tile_count[t];  // exclusive prefix over tiles, made between the two passes
     } else {
-        __shared__ long long s_base;
         if (warp_id() == 0) {
-            const int64_t b = lookback_exclusive(tile_state, t, total, &ctl->status);
+            if (lane_id() == 0) st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
+            int64_t b = 0;
+            if (t > 0) {
+                b = lookback_predecessors(tile_state, t, &ctl->status, 32, nullptr, 64, poll_limit);
+                if (lane_id() == 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(b < 0 ? 0 : b + total));
+            }
             if (lane_id() == 0) s_base = b;
         }
-        thread_rank[tid] = rank;
-        thread_emit[tid] = emit;
-        WorkerBar::sync();
+    }
+    thread_rank[tid] = rank;
+    thread_emit[tid] = emit;
+    WorkerBar::sync();
+    if (MODE == MODE_FUSED) {
         base = s_base;
         if (base < 0) return;  // a bounded wait gave up; the host reports it
         if (t == num_tiles - 1 && tid == 0) ctl->total = base + total;
-    }
-    if (MODE == MODE_FILL) {
-        thread_rank[tid] = rank;
-        thread_emit[tid] = emit;
-        WorkerBar::sync();
     }
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
     // tile those are the survivors among the first d = (A entries before row r) + (B entries
     // before row r) merged entries, read off the per-thread ranks. The tile owns rows
     // i0+1 .. i1 (the next tile's first row).
-    for (int64_t r = my_row; r <= i1; r += NT) {
-        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
-        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
-        const int d = sa + sb;
+    for (int64_t r = (int64_t)i0 + 1 + tid; r <= i1; r += NT) {
+        const int d = (ld_nc(A.rp + r) - a0) + (ld_nc(B.rp + r) - b0);
         const int owner = d / VT, off = d - owner * VT;
         const int before = owner >= NT ? total : thread_rank[owner] + __popc(thread_emit[owner] & ((1u << off) - 1u));
         Z.rp[r] = (int32_t)(base + before);
     }
     if (t == 0 && tid == 0) Z.rp[0] = 0;
 
-    // ---- fetch values, compact through shared memory (the staging area reuses the key
-    // arrays; the syncs above separate the last key read from the first write), store coalesced
+    // ---- fetch values, compact through shared memory (the staging arrays reuse the key words:
+    // the barriers above separate the last key read from the first write), store coalesced
     int32_t *out_col = reinterpret_cast<int32_t *>(smem_raw);
-    // 64-bit keys leave room for both staging arrays inside the key area; 32-bit keys need a
-    // third array after the values. Either way the footprint is 12 bytes per slot.
-    float *out_val = sizeof(KeyT) == 8 ? reinterpret_cast<float *>(smem_raw) + KEY_SLOTS
-                                       : reinterpret_cast<float *>(smem_raw) + 2 * KEY_SLOTS;
+    float *out_val = reinterpret_cast<float *>(smem_raw) + KEY_SLOTS;
     {
         int r = rank, xi = x0, yi = y0;
 #pragma unroll
         for (int i = 0; i < VT; ++i) {
             const bool tx = (from_a >> i) & 1u;
             const bool both = (twin >> i) & 1u;
-            const float va = vx[xi], vb = vy[yi];  // always inside the slack-padded arrays
-            float v = tx ? va : vb;
-            v = both ? (OP == OP_UNION ? va + vb : va * vb) : v;
             if ((emit >> i) & 1u) {
-                out_col[r] = (int32_t)KT::col_of(key[i], cbits);
+                float v;
+                if (OP == OP_UNION) {
+                    v = tx ? ld_nc(A.val + a0 + xi) : ld_nc(B.val + b0 + yi);
+                    if (both) v = v + ld_nc(B.val + b0 + yi);
+                } else {
+                    v = ld_nc(A.val + a0 + xi) * ld_nc(B.val + b0 + yi);
+                }
+                out_col[r] = (int32_t)col[i];
                 out_val[r] = v;
+                ++r;
             }
-            r += (emit >> i) & 1u;
             xi += tx;
             yi += !tx;
         }
@@ -355,26 +343,6 @@ __device__ __noinline__ void csr2_tile_generic(const CsrIn &A, const CsrIn &B, c
     }
 }
 
-// Shared-memory plan of the fast tile body, in 4-byte words. Keys and values use the same
-// word positions: A's entry e sits at word oa + e and B's at word obv + e, where oa and obv
-// are chosen so that a global address on a 16-byte boundary lands on a 16-byte boundary in
-// shared memory too (what a bulk copy needs). The column staging array of the result reuses
-// the key words (the keys live in registers by then); the value staging array follows.
-template <int VT>
-struct FastPlan {
-    static constexpr int CAP = NT * VT;
-    static constexpr int NETV = VT + 1;                          // merge-network slots in use
-    static constexpr int CH = (VT + 1 + 3) & ~3;                 // words each thread scans
-    static constexpr int SLOTS = NT * CH + ((NETV + 4 + 3) & ~3);  // key words = value words
-    static constexpr int OUT = CAP + 8;                          // staging words per array
-    static constexpr size_t BYTES = 4 * (size_t)(2 * SLOTS + OUT);
-    // A thread's CH-word chunk is read and written as 16-byte vectors; an odd number of
-    // vectors per chunk keeps those accesses free of shared-memory bank conflicts.
-    static_assert((CH / 4) % 2 == 1, "choose VT so that (VT + 1) rounded up to 4 is an odd multiple of 4");
-    static_assert(NT * CH >= CAP + 12, "scan range must cover the padded tile");
-    static_assert(OUT <= SLOTS, "column staging must fit the key words it reuses");
-};
-
 constexpr int MBAR_POLL_LIMIT = 1 << 24;
 constexpr int ERR_COPY_TIMEOUT = 2;
 
@@ -383,52 +351,44 @@ __device__ __forceinline__ int head_elems(const void *p) {
     return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
 }
 
-// Sorts N keys held in registers that form a bitonic sequence (ascending run, then descending
-// run). For N that is not a power of two the keys are treated as the top N slots of the next
-// power-of-two network whose lower slots hold zeros; compare-exchanges that would touch
-// those virtual slots leave them unchanged and are dropped at compile time.
-template <int N>
-__device__ __forceinline__ void bitonic_merge(uint32_t (&r)[N]) {
-    constexpr int NET = N <= 8 ? 8 : (N <= 16 ? 16 : 32);
-    constexpr int PAD = NET - N;
-#pragma unroll
-    for (int d = NET / 2; d > 0; d >>= 1) {
-#pragma unroll
-        for (int i = PAD; i < NET; ++i) {
-            if ((i & d) == 0) {
-                const uint32_t lo = min(r[i - PAD], r[i + d - PAD]), hi = max(r[i - PAD], r[i + d - PAD]);
-                r[i - PAD] = lo;
-                r[i + d - PAD] = hi;
-            }
-        }
-    }
-}
-
-
-// Fast tile body. Keys are 32-bit composites (row in tile, column, operand bit):
+// The common tile body. Keys are 32-bit composites (row in tile, column, operand bit):
 //     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
 // so that one unsigned compare orders entries by (row, column) with A first on ties, and
 // two entries are the same position exactly when their keys differ in the last bit only.
 //
-// The CTA has NT worker threads and one more warp, the scan warp. Workers stage the operands
-// with bulk copies, build keys, split the tile by merge-path, merge VT entries each in
-// registers with a bitonic network, and compact the survivors into shared memory. In the
-// single-pass mode the scan warp meanwhile turns the tile's count into its output base by
-// look-back over earlier tiles, so that this wait overlaps the workers' compaction.
-template <int VT, int OP, int MODE>
-__device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits,
-                                               const int t, int32_t *tile_count, volatile uint64_t *tile_state,
-                                               FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw,
-                                               int *scan_tmp, int *thread_rank, unsigned *thread_emit,
-                                               uint64_t *mbar, const int num_tiles, const unsigned mbar_phase) {
-    using P = FastPlan<VT>;
-    constexpr int NETV = P::NETV;
+// The CTA has NT worker threads (eight warps) and one more warp, the scan warp.
+//   1. One thread hands the tile's column and value ranges to the copy engine (bulk copies that
+//      complete on an mbarrier). While they fly, each worker warp finds the row of the first key
+//      word it will scan (32-ary search over the row offsets).
+//   2. The workers mark the first entry of every row that starts in the tile with the row number
+//      (one CTA barrier), then every warp spreads the marks over its own 32 * CH words with a
+//      running maximum and appends the operand bit: keys (one CTA barrier).
+//   3. From here each warp works alone: it cuts its STEP_W merged entries out of the tile by
+//      merge-path (32-ary search), loads them as a bitonic sequence striped over its registers,
+//      sorts them with a merge network (register compare-exchanges and butterfly shuffles), flags
+//      pairs, and ranks the survivors with warp votes. No barrier, no shared-memory bank conflict.
+//   4. The warps' counts meet at one barrier. In the single-pass mode the scan warp has meanwhile
+//      walked the predecessors' tile words (bounded decoupled look-back), so the tile's output base
+//      is one addition away; the workers gather the values in the meantime.
+//   5. Every warp stores its survivors straight from registers: the 32 lanes of one register slot
+//      are consecutive result entries. The row offsets of the rows that begin in the tile come
+//      from the warps' vote masks.
+template <int V, int OP, int MODE>
+__device__ __forceinline__ void csr2_tile_warp(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits, const int t,
+                                               const int num_tiles, int32_t *tile_count, volatile uint64_t *tile_state, FusedCtl *ctl,
+                                               const CsrOut &Z, unsigned char *smem_raw, uint64_t *mbar, const int poll_limit) {
+    using P = WarpPlan<V>;
+    constexpr int W = P::W;
     constexpr bool WRITES = MODE != MODE_COUNT;
-    constexpr uint32_t INF = 0xffffffffu;
     __shared__ long long s_base;
     __shared__ int s_total;
     __shared__ int s_hurry;  // set once the tile's count is out: from then on the tile waits for its base
+    __shared__ int s_wtotal[W];          // survivors of each warp
+    __shared__ int s_wstart[W];          // merged position (in the tile) of each warp's first entry
+    __shared__ unsigned s_vote[W][V];    // per register slot: the lanes whose entry survives
+    __shared__ unsigned short s_before[W][V];  // per register slot: survivors of the warp in earlier slots
     const int tid = threadIdx.x;
+    const int lane = tid & 31, wid = tid >> 5;
     const bool scan_warp = tid >= NT;
     const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
     const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
@@ -436,22 +396,17 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     const int n = na + nb;
     const uint32_t cmask = (1u << cbits) - 1u;
 
-    // layout: values | keys | extra words. The (column, value) staging pairs of the result
-    // reuse the keys (in registers by then) and run on into the extra words.
     float *vals = reinterpret_cast<float *>(smem_raw);
     uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw) + P::SLOTS;
-    uint2 *out_pair = reinterpret_cast<uint2 *>(keys);
-    static_assert(P::SLOTS % 2 == 0 && P::SLOTS + P::OUT >= 2 * P::OUT, "staging pairs must fit keys + extra words, 8-byte aligned");
 
     const int32_t *ga_col = A.col + a0, *gb_col = B.col + b0;
     const float *ga_val = A.val + a0, *gb_val = B.val + b0;
     const int ha = head_elems(ga_col), hb = head_elems(gb_col);
     const int oa = (4 - ha) & 3;                 // word of A's entry 0
-    const int ob = (oa + na + 1 + 3) & ~3;       // first word of B's region (A's sentinel before it)
+    const int ob = (oa + na + 3) & ~3;           // first word of B's region
     const int obv = ob + ((4 - hb) & 3);         // word of B's entry 0
     const int scan_end = (obv + nb + 3) & ~3;
     uint32_t *kx = keys + oa, *ky = keys + obv;
-    const float *vy = vals + obv;
 
     // ---- stage the tile. One thread hands the 16-byte-aligned interior of each array to the
     // copy engine; a few other threads load the ragged ends (at most 3 entries each side).
@@ -484,13 +439,9 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     }
     if (WRITES && !va_bulk && !scan_warp) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
     if (WRITES && !vb_bulk && !scan_warp) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
-    // padding words that precede live keys must read as "no row mark"; the end-of-list
-    // sentinels are all-ones, which the row spreading below keeps above every live key
+    // padding words that precede live keys must read as "no row mark"
     if (tid >= 64 && tid < 64 + 3) { if (tid - 64 < oa) keys[tid - 64] = 0u; }
     if (tid >= 68 && tid < 68 + 3) { if (ob + (tid - 68) < obv) keys[ob + (tid - 68)] = 0u; }
-    if (tid == 72) keys[oa + na] = INF;
-    if (tid >= 76 && tid < 76 + NETV + 1) keys[obv + nb + (tid - 76)] = INF;
-    static_assert(76 + NETV + 1 <= NT, "sentinel writers must be worker threads");
 
     // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over the
     // workers); kept in registers for the row-offset pass at the end
@@ -500,14 +451,28 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         my_sa = ld_nc(A.rp + my_row) - a0;
         my_sb = ld_nc(B.rp + my_row) - b0;
     }
-    const bool landed = mbar_wait_bounded(mbar, mbar_phase, MBAR_POLL_LIMIT);
+    // ---- the row (relative to i0) that the first key word of this warp's scan region belongs to:
+    // the last row that starts at or before it. Regions that begin with an operand's first entry,
+    // or in padding before it, start from row 0 of the tile.
+    const int w0 = wid * 32 * P::CH;
+    const bool region_in_a = w0 < ob;
+    unsigned carry = 0;
+    if (!scan_warp) {
+        const int pos = region_in_a ? w0 - oa : w0 - obv;
+        if (pos > 0 && i1 > i0) {
+            const int32_t *rp = region_in_a ? A.rp : B.rp;
+            const int32_t start = region_in_a ? a0 : b0;
+            carry = (unsigned)(warp_last_true(i0, i1, [&](int64_t r) { return ld_nc(rp + r) - start <= pos; }) - i0);
+        }
+    }
+    const bool landed = mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);
     if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
         if (tid == 0) {
             if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
             if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;  // successors must not wait on this tile
-            mbar_wait_bounded(mbar, mbar_phase, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
+            mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
         }
-        return false;  // the barrier's phase is unknown from here on: the CTA takes no further tile
+        return;
     }
 
     if (scan_warp) {
@@ -515,17 +480,18 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         // tiles, which does not depend on this tile's own count. So the walk over the
         // predecessors' words starts now, while the workers are still merging, and is usually
         // over by the time they know their count.
-        if (MODE != MODE_FUSED) return true;
-        const int64_t bse = t == 0 ? 0 : lookback_predecessors<CSR2_LB_DEPTH>(tile_state, t, &ctl->status, CSR2_LB_SLEEP, &s_hurry, CSR2_LB_HURRY);
+        if (MODE != MODE_FUSED) return;
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors<CSR2_LB_DEPTH>(tile_state, t, &ctl->status, CSR2_LB_SLEEP, &s_hurry,
+                                                                             CSR2_LB_HURRY, poll_limit);
         CountBar::sync();  // the workers have published the tile's count by now
         const int total = s_total;
-        if (lane_id() == 0) {
+        if (lane == 0) {
             if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
             s_base = bse;
             if (bse >= 0 && t == num_tiles - 1) ctl->total = bse + total;
         }
         __syncthreads();
-        return true;
+        return;
     }
 
     // ---- mark the first entry of every row that starts inside the tile with its row number
@@ -540,8 +506,8 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     WorkerBar::sync();
 
     // ---- spread the marks forward (running maximum) so that every key carries its row, and
-    // append the operand bit. Each thread owns CH consecutive words; A's region and B's region
-    // run separately.
+    // append the operand bit. Each thread owns CH consecutive words, each warp 32 * CH; A's words
+    // and B's words run separately (a warp's region may hold the end of A and the start of B).
     {
         constexpr int NV = P::CH / 4;
         const int w_base = tid * P::CH;
@@ -554,8 +520,9 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
             const unsigned m = max(max(q[j].x & ~cmask, q[j].y & ~cmask), max(q[j].z & ~cmask, q[j].w & ~cmask));
             if (w < ob) ma = max(ma, m); else mb = max(mb, m);
         }
-        unsigned ea, eb;
-        block_excl_max2<NT, WorkerBar>(ma, mb, reinterpret_cast<unsigned *>(scan_tmp), ea, eb);
+        unsigned ea = __shfl_up_sync(FULL_MASK, warp_incl_max(ma), 1), eb = __shfl_up_sync(FULL_MASK, warp_incl_max(mb), 1);
+        if (lane == 0) ea = eb = 0u;
+        if (region_in_a) ea = max(ea, carry << cbits); else eb = max(eb, carry << cbits);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int w = w_base + 4 * j;
@@ -573,65 +540,67 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
     }
     WorkerBar::sync();
 
-    // ---- split the tile among threads: merge-path diagonal tid * VT (the operand bit makes
-    // an A entry smaller than the B entry at the same position, so ties take A first)
-    const int diag = min(tid * VT, n);
-    int x0;
-    {
-        int lo = max(0, diag - nb), hi = min(diag, na);
-        while (lo < hi) {
-            const int mid = (lo + hi) >> 1;
-            if (kx[mid] < ky[diag - 1 - mid]) lo = mid + 1; else hi = mid;
-        }
-        x0 = lo;
+    // ---- this warp's merged entries [wid STEP_W, (wid + 1) STEP_W) of the tile, as ranges of A
+    // and of B (both cuts keep the two entries of one position together)
+    int x0, y0, x1, y1;
+    warp_merge_cut(kx, na, ky, nb, wid * P::STEP_W, x0, y0);
+    warp_merge_cut(kx, na, ky, nb, (wid + 1) * P::STEP_W, x1, y1);
+    const int ca = x1 - x0, cb = y1 - y0, cnt = ca + cb;
+
+    // ---- merge in registers: slot e of the warp (register e / 32 of lane e % 32) ends up with
+    // the warp's e-th merged key; the all-ones padding collects in the slots from cnt on
+    uint32_t r[V];
+    warp_load_bitonic<V>(r, kx + x0, ca, ky + y0, cb);
+    warp_bitonic_merge<V>(r);
+
+    // Bit j of a mask speaks about slot 32 j + lane. `same`: the slot holds an A entry and the next
+    // slot its B twin; `dup`: the slot holds a B entry whose A twin is the slot before; `from_a`:
+    // the slot holds an A entry (or padding); `live`: the slot holds an entry.
+    const unsigned same = warp_pair_mask<V>(r);
+    const unsigned dup = warp_shift_mask_up(same);
+    unsigned from_a = 0, live = 0;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        from_a |= (~r[j] & 1u) << j;
+        live |= (unsigned)(32 * j + lane < cnt) << j;
     }
-    const int y0 = diag - x0;
-    thread_rank[tid] = x0;  // borrowed to pass every thread's split to its left neighbour
+    const unsigned emit = OP == OP_UNION ? (live & ~dup) : same;
+
+    // ---- rank the survivors: warp votes per register slot
+    {
+        int run = 0;
+        unsigned my_vote = 0;
+        int my_before = 0;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const unsigned b = __ballot_sync(FULL_MASK, (emit >> j) & 1u);
+            if (lane == j) {
+                my_vote = b;
+                my_before = run;
+            }
+            run += __popc(b);
+        }
+        if (lane < V) {
+            s_vote[wid][lane] = my_vote;
+            s_before[wid][lane] = (unsigned short)my_before;
+        }
+        if (lane == 0) {
+            s_wtotal[wid] = run;
+            s_wstart[wid] = x0 + y0;
+        }
+    }
     WorkerBar::sync();
-    const int cnt = min(VT, n - diag);
-    const int x1 = tid + 1 < NT ? thread_rank[tid + 1] : na;
-    const int a = min(x1, x0 + cnt) - x0, b = cnt - a;
-
-    // ---- merge in registers: A's entries ascending, the successor of the thread's range, an
-    // all-ones plateau, B's entries descending -- a bitonic sequence -- through a merge network
-    uint32_t r[NETV];
-    {
-        const uint32_t succ = min(kx[x0 + a], ky[y0 + b]);  // next merged key after this thread's range
+    int total = 0, wbase = 0;  // survivors of the tile, and of the warps before this one
 #pragma unroll
-        for (int i = 0; i < NETV; ++i) {
-            const bool is_a = i < a, is_b = i >= NETV - b;
-            const uint32_t *p = is_a ? kx + x0 + i : ky + y0 + (NETV - 1 - i);
-            const uint32_t v = *p;  // stays inside the slack-padded key array either way
-            r[i] = (is_a || is_b) ? v : (i == a ? succ : INF);
-        }
+    for (int w = 0; w < W; ++w) {
+        const int c = s_wtotal[w];
+        wbase += w < wid ? c : 0;
+        total += c;
     }
-    const uint32_t prev_a = x0 > 0 ? kx[x0 - 1] : 0u;  // only an A entry can pair with a B entry
-    bitonic_merge<NETV>(r);
-
-    // Bit i of `from_a`: entry i came from A; of `same`: entries i and i+1 are one position (an A
-    // entry and its B twin); of `emit`: entry i goes to the result.
-    unsigned from_a = 0, same = 0;
-#pragma unroll
-    for (int i = 0; i < VT; ++i) {
-        from_a |= (~r[i] & 1u) << i;
-        same |= (unsigned)((r[i] ^ r[i + 1]) == 1u) << i;
-    }
-    const unsigned live = (1u << cnt) - 1u;
-    const unsigned dup = (same << 1) | (unsigned)(x0 > 0 && (prev_a ^ r[0]) == 1u);  // B entries whose A twin precedes them
-    const unsigned twin = same & from_a & live;
-    const unsigned emit = OP == OP_UNION ? (live & ~dup) : twin;
-    static_assert(VT < 32, "entry masks are 32 bits wide");
-
-    // ---- rank the survivors inside the tile
-    int total;
-    const int mine = __popc(emit);
-    const int rank = block_excl_sum<NT, WorkerBar>(mine, scan_tmp, total);  // its syncs also retire the key reads
     if (MODE == MODE_COUNT) {
         if (tid == 0) tile_count[t] = total;
-        return true;
+        return;
     }
-    thread_rank[tid] = rank;
-    thread_emit[tid] = emit;
     if (MODE == MODE_FUSED) {
         if (tid == 0) {
             // successors can add this tile's count from here on
@@ -643,159 +612,119 @@ __device__ __forceinline__ bool csr2_tile_fast(const CsrIn &A, const CsrIn &B, c
         CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
     }
 
-    // ---- compact (column, value) pairs of the survivors into the staging array. Entry i of the
-    // thread came from A iff its key's operand bit is clear; its value sits at A's start + (A
-    // entries before it) or B's start + (B entries before it), and an A entry's twin is the
-    // next B entry.
+    // ---- values of the survivors, while the scan warp finishes. A's entries of the warp are in
+    // order, so the A entry of a slot is number (A entries in earlier slots) of the warp's range,
+    // and a slot's B entry -- its own, or the twin of its A entry, which is the next slot -- is
+    // number (slot - A entries before it).
+    float v[V];
     {
         const float *pa = vals + oa + x0, *pb = vals + obv + y0;
-        uint2 *po = out_pair + rank;
-        int ca = 0;  // A entries among the thread's first i entries
+        const unsigned lt = (1u << lane) - 1u;
+        int run_a = 0;
 #pragma unroll
-        for (int i = 0; i < VT; ++i) {
-            const bool tx = (r[i] & 1u) == 0u;
-            if (OP == OP_UNION) {
-                float v = *(tx ? pa + ca : pb + (i - ca));
-                if ((twin >> i) & 1u) v = v + pb[i - ca];  // an A entry whose twin is the next B entry
-                if ((emit >> i) & 1u) {
-                    *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(v));
-                    ++po;
+        for (int j = 0; j < V; ++j) {
+            const bool fa = (from_a >> j) & 1u, tw = (same >> j) & 1u, em = (emit >> j) & 1u;
+            const unsigned ba = __ballot_sync(FULL_MASK, fa && ((live >> j) & 1u));
+            const int ia = run_a + __popc(ba & lt), ib = 32 * j + lane - ia;
+            run_a += __popc(ba);
+            float x = 0.f;
+            if (em) {
+                if (OP == OP_UNION) {
+                    x = fa ? pa[ia] : pb[ib];
+                    if (tw) x = x + pb[ib];  // an A entry whose twin is the next B entry
+                } else {
+                    x = pa[ia] * pb[ib];
                 }
-            } else if ((emit >> i) & 1u) {  // intersection: only the twins need their values
-                *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(pa[ca] * pb[i - ca]));
-                ++po;
             }
-            ca += tx;
+            v[j] = x;
         }
     }
 
     // ---- output base of the tile
-    if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
+    if (MODE == MODE_FUSED) __syncthreads();
     const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
-    if (base < 0) return true;  // a bounded wait gave up; the host reports it
+    if (base < 0) return;  // a bounded wait gave up; the host reports it
+
+    // ---- store the survivors, coalesced: the emitting lanes of one register slot write
+    // consecutive result entries
+    {
+        int32_t *gz_col = Z.col + base + wbase;
+        float *gz_val = Z.val + base + wbase;
+        const unsigned lt = (1u << lane) - 1u;
+        int run = 0;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const unsigned b = __ballot_sync(FULL_MASK, (emit >> j) & 1u);
+            if ((emit >> j) & 1u) {
+                const int p = run + __popc(b & lt);
+                gz_col[p] = (int32_t)((r[j] >> 1) & cmask);
+                gz_val[p] = v[j];
+            }
+            run += __popc(b);
+        }
+    }
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
     // tile those are the survivors among the first d = (A entries before row r) + (B entries
-    // before row r) merged entries, read off the per-thread ranks. The tile owns rows
-    // i0+1 .. i1 (the next tile's first row).
+    // before row r) merged entries: whole warps, whole register slots of the warp that holds
+    // merged position d, and the lanes below d's in its slot. The tile owns rows i0+1 .. i1 (the
+    // next tile's first row).
     for (int64_t rw = my_row; rw <= i1; rw += NT) {
         const int sa = rw == my_row ? my_sa : ld_nc(A.rp + rw) - a0;
         const int sb = rw == my_row ? my_sb : ld_nc(B.rp + rw) - b0;
         const int d = sa + sb;
-        const int owner = d / VT, off = d - owner * VT;
-        const int before = owner >= NT ? total : thread_rank[owner] + __popc(thread_emit[owner] & ((1u << off) - 1u));
+        int before = total;
+        if (d < n) {
+            int w = min(d / P::STEP_W, W - 1);
+            if (s_wstart[w] > d) --w;  // a cut moved by one to keep a pair together
+            before = 0;
+            for (int q = 0; q < w; ++q) before += s_wtotal[q];
+            const int e = d - s_wstart[w];
+            before += s_before[w][e >> 5] + __popc(s_vote[w][e >> 5] & ((1u << (e & 31)) - 1u));
+        }
         Z.rp[rw] = (int32_t)(base + before);
     }
     if (t == 0 && tid == 0) Z.rp[0] = 0;
-
-    // ---- store the compacted tile, coalesced
-    int32_t *gz_col = Z.col + base;
-    float *gz_val = Z.val + base;
-    for (int i = tid; i < total; i += NT) {
-        const uint2 p = out_pair[i];
-        gz_col[i] = (int32_t)p.x;
-        gz_val[i] = __uint_as_float(p.y);
-    }
-    return true;
 }
 
-template <int VT, int OP, int MODE>
+template <int V, int OP, int MODE>
 __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __grid_constant__ CsrIn A, const __grid_constant__ CsrIn B,
                                                                          const __grid_constant__ Cuts cuts, int cbits, int32_t *tile_count,
                                                                          uint64_t *tile_state, FusedCtl *ctl,
-                                                                         const __grid_constant__ CsrOut Z) {
+                                                                         const __grid_constant__ CsrOut Z, int first_tile, int poll_limit) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ int scan_tmp[72];
-    __shared__ int thread_rank[NT];
-    __shared__ unsigned thread_emit[NT];
     __shared__ __align__(8) uint64_t mbar;
-    __shared__ int s_tile;
     // Tiles are numbered by CTA index: CTAs are dispatched in increasing index order, so a tile
     // only ever waits on CTAs that were dispatched before it (and every such wait is bounded).
-    // Set CSR2_TICKET to number tiles with an atomic ticket taken at CTA start instead.
-    int t = blockIdx.x;
+    // first_tile is 0 except in the self-test of the bounded waits, which leaves tile 0 out.
+    const int t = blockIdx.x + first_tile;
+    const int num_tiles = gridDim.x + first_tile;
     if (threadIdx.x == 0) {
-#ifdef CSR2_TICKET
-        if (MODE == MODE_FUSED) s_tile = atomicAdd(&ctl->ticket, 1);
-#endif
         mbar_init(&mbar, 1);
         mbar_fence_init();
     }
     __syncthreads();
-#ifdef CSR2_TICKET
-    if (MODE == MODE_FUSED) t = s_tile;
-#endif
     // 32-bit composite keys hold ((row in tile << cbits | column) << 1 | operand) when that
     // fits; tiles that span too many rows for that (long runs of empty rows) use 64-bit keys.
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
     const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
     if (narrow) {
-        csr2_tile_fast<VT, OP, MODE>(A, B, cuts, cbits, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit, &mbar,
-                                     (int)gridDim.x, 0u);
+        csr2_tile_warp<V, OP, MODE>(A, B, cuts, cbits, t, num_tiles, tile_count, tile_state, ctl, Z, smem_raw, &mbar, poll_limit);
     } else {
-        if (threadIdx.x >= NT) return;  // the generic body works with the NT worker threads alone
-        csr2_tile_generic<uint64_t, VT, OP, MODE>(A, B, cuts, 32, t, tile_count, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank, thread_emit,
-                                                  (int)gridDim.x);
+        if (threadIdx.x >= NT) return;  // the wide-key body works with the NT worker threads alone
+        csr2_tile_wide<WideVt<V>::value, OP, MODE>(A, B, cuts, t, tile_count, tile_state, ctl, Z, smem_raw, num_tiles, poll_limit);
     }
 }
-
-#if CSR2_RESIDENT
-// The single-pass launch as resident CTAs that take tile after tile from a ticket. A tile is only
-// ever taken by a running CTA and after every earlier tile was taken, so the look-back waits on
-// running CTAs whatever the number of resident ones; the next ticket is fetched while the current
-// tile is worked on, and a CTA's start-up (shared memory, barrier, first loads) is paid once per
-// CTA instead of once per tile. Wide-key tiles run the generic body on the worker threads alone;
-// the scan warp sits them out at the barrier that ends every tile.
-template <int VT, int OP>
-__global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile_resident(const __grid_constant__ CsrIn A, const __grid_constant__ CsrIn B,
-                                                                                  const __grid_constant__ Cuts cuts, int cbits, int num_tiles,
-                                                                                  uint64_t *tile_state, FusedCtl *ctl,
-                                                                                  const __grid_constant__ CsrOut Z) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ int scan_tmp[72];
-    __shared__ int thread_rank[NT];
-    __shared__ unsigned thread_emit[NT];
-    __shared__ __align__(8) uint64_t mbar;
-    __shared__ int s_next;
-    if (threadIdx.x == 0) {
-        s_next = atomicAdd(&ctl->ticket, 1);
-        mbar_init(&mbar, 1);
-        mbar_fence_init();
-    }
-    __syncthreads();
-    unsigned phase = 0u;  // parity of the copy barrier: it completes once per tile of the fast body
-    for (;;) {
-        const int t = s_next;
-        if (t >= num_tiles) break;  // uniform: every thread reads the same word
-        __syncthreads();            // ... and has read it before it is replaced
-        if (threadIdx.x == NT) s_next = atomicAdd(&ctl->ticket, 1);  // by the scan warp: it has slack, the workers do not wait for the reply
-        const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
-        const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
-        bool go_on = true;
-        if (narrow) {
-            go_on = csr2_tile_fast<VT, OP, MODE_FUSED>(A, B, cuts, cbits, t, nullptr, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank,
-                                                       thread_emit, &mbar, num_tiles, phase);
-            phase ^= 1u;
-        } else if (threadIdx.x < NT) {
-            csr2_tile_generic<uint64_t, VT, OP, MODE_FUSED>(A, B, cuts, 32, t, nullptr, tile_state, ctl, Z, smem_raw, scan_tmp, thread_rank,
-                                                            thread_emit, num_tiles);
-        }
-        __syncthreads();  // the tile is stored: shared memory may be reused, the next ticket is in place
-        if (!go_on) break;  // uniform (decided at a CTA-wide barrier vote)
-        // the next tile's bulk copies overwrite what the threads read and wrote through ordinary
-        // loads and stores up to the barrier above: order the two proxies
-        if (threadIdx.x == 0) fence_async_smem();
-    }
-}
-#endif  // CSR2_RESIDENT
 
 // ------------------------------------------------------------------------ host driver ----
 
-constexpr int VT_CSR2 = CSR2_VT;
+constexpr int V_CSR2 = CSR2_V;
+constexpr int TILE_STEP = WarpPlan<V_CSR2>::TILE_STEP;
 
-template <int VT>
+// Dynamic shared memory of the tile kernel: the staging arrays of the common body, or the 64-bit
+// keys of the wide-key body, whichever is larger.
 constexpr size_t csr2_smem_bytes() {
-    return std::max<size_t>(FastPlan<VT>::BYTES, 12 * (size_t)(NT * VT + 2 + VT));
+    return std::max<size_t>(WarpPlan<V_CSR2>::BYTES, 8 * (size_t)(NT * WideVt<V_CSR2>::value + 2 + WideVt<V_CSR2>::value));
 }
 
 int col_bits(int32_t cols) {
@@ -810,47 +739,48 @@ int check_csr(const nb200_csr *m, bool need_arrays) {
     return NB200_OK;
 }
 
+// Raises the tile kernel's dynamic shared-memory limit once per instantiation and device.
 template <int OP, int MODE>
-cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits, int32_t *tile_count,
-                        uint64_t *tile_state, FusedCtl *ctl, const CsrOut &Z, int num_tiles, cudaStream_t stream) {
-    constexpr size_t smem = csr2_smem_bytes<VT_CSR2>();
-    auto kernel = k_csr2_tile<VT_CSR2, OP, MODE>;
-    static bool configured[64] = {};  // per instantiation and device
+cudaError_t configure_tile_kernel() {
+    static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(k_csr2_tile<V_CSR2, OP, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csr2_smem_bytes());
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
+    return cudaSuccess;
+}
+
+// Test knobs of a launch: the first tile to run (the self-test of the bounded waits leaves tile 0
+// out, so that every other tile waits for a count that never comes) and the number of polls after
+// which a look-back gives up.
+struct LaunchKnobs {
+    int first_tile = 0;
+    int poll_limit = LOOKBACK_POLL_LIMIT;
+};
+
+template <int OP, int MODE>
+cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cbits, int32_t *tile_count,
+                        uint64_t *tile_state, FusedCtl *ctl, const CsrOut &Z, int num_tiles, cudaStream_t stream,
+                        const LaunchKnobs &knobs = LaunchKnobs()) {
+    cudaError_t e = configure_tile_kernel<OP, MODE>();
+    if (e != cudaSuccess) return e;
     static const char *const names[2][3] = {{"csr_add_count", "csr_add_fill", "csr_add_fused"},
                                             {"csr_mul_count", "csr_mul_fill", "csr_mul_fused"}};
-#if CSR2_RESIDENT
-    if (MODE == MODE_FUSED) {
-        // resident CTAs that take tiles from the ticket in ctl (zeroed by the caller with the tile words)
-        auto resident = k_csr2_tile_resident<VT_CSR2, OP>;
-        static int ctas[64] = {};  // CTAs that fit the device at once, per instantiation and device
-        if (dev < 0 || dev >= 64 || ctas[dev] == 0) {
-            cudaError_t e = cudaFuncSetAttribute(resident, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-            int per_sm = 0, sms = 0;
-            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, resident, NT + 32, smem);
-            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev < 0 ? 0 : dev);
-            if (e != cudaSuccess) return e;
-            const int fit = std::max(1, per_sm) * std::max(1, sms);
-            if (dev >= 0 && dev < 64) ctas[dev] = fit;
-            LaunchScope scope(names[OP][MODE], stream);
-            resident<<<std::min(num_tiles, fit), NT + 32, smem, stream>>>(A, B, cuts, cbits, num_tiles, tile_state, ctl, Z);
-            return cudaGetLastError();
-        }
-        LaunchScope scope(names[OP][MODE], stream);
-        resident<<<std::min(num_tiles, ctas[dev]), NT + 32, smem, stream>>>(A, B, cuts, cbits, num_tiles, tile_state, ctl, Z);
-        return cudaGetLastError();
-    }
-#endif
+    if (num_tiles - knobs.first_tile <= 0) return cudaSuccess;
     LaunchScope scope(names[OP][MODE], stream);
-    kernel<<<num_tiles, NT + 32, smem, stream>>>(A, B, cuts, cbits, tile_count, tile_state, ctl, Z);
+    k_csr2_tile<V_CSR2, OP, MODE><<<num_tiles - knobs.first_tile, NT + 32, csr2_smem_bytes(), stream>>>(
+        A, B, cuts, cbits, tile_count, tile_state, ctl, Z, knobs.first_tile, knobs.poll_limit);
     return cudaGetLastError();
+}
+
+// Copies the control block's total and status into two device words the caller reads later
+// ({result entries, device status}), so that a call can return without waiting for the GPU.
+__global__ void k_publish_result(const FusedCtl *ctl, int64_t *out) {
+    out[0] = ctl->total;
+    out[1] = ctl->status.error != 0 ? NB200_E_TIMEOUT : (ctl->total > INT32_MAX ? NB200_E_OVERFLOW : NB200_OK);
 }
 
 // Shared driver of add and multiply. When `alloc` is set the result arrays are allocated
@@ -859,8 +789,13 @@ cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cb
 // With room for the largest possible result (every operand entry for a union, the smaller
 // operand for an intersection) the single-pass kernel runs. A caller-provided capacity below
 // that bound takes the two-pass route, which knows the exact length before it writes.
+//
+// `device_result`, when given, makes the call asynchronous: the result length and the device
+// status go to those two device words in stream order and the host does not wait (z->nnz stays 0).
+// Only the single-pass route can do that; the call refuses a capacity below the bound.
 template <int OP>
-int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, int64_t capacity, void *stream_v) {
+int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, int64_t capacity, void *stream_v,
+             int64_t *device_result = nullptr, const LaunchKnobs &knobs = LaunchKnobs()) {
     int st;
     if ((st = check_csr(a, true)) || (st = check_csr(b, true))) return st;
     if (!z || a->rows != b->rows || a->cols != b->cols) return NB200_E_BADARG;
@@ -868,11 +803,13 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const int32_t rows = a->rows;
     const int64_t total = (int64_t)a->nnz + b->nnz;
-    constexpr int tile_step = NT * VT_CSR2 - 1;
-    const int64_t tiles64 = (total + tile_step - 1) / tile_step;
+    const int64_t tiles64 = (total + TILE_STEP - 1) / TILE_STEP;
     if (tiles64 > INT32_MAX - 1) return NB200_E_OVERFLOW;
     const int num_tiles = (int)tiles64;
     const int64_t bound = OP == OP_UNION ? total : std::min<int64_t>(a->nnz, b->nnz);
+    // a caller's arrays must exist wherever the kernels may write: capacity > 0 promises col / val
+    if (!alloc && capacity > 0 && total > 0 && (!z->col || !z->val)) return NB200_E_BADARG;
+    if (device_result && (alloc || capacity < bound)) return NB200_E_CAPACITY;
 
     z->rows = rows;
     z->cols = a->cols;
@@ -895,6 +832,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     };
     if (num_tiles == 0) {  // both operands empty: all-zero offsets, nothing else
         cudaError_t e = cudaMemsetAsync(z->row_ptr, 0, sizeof(int32_t) * ((size_t)rows + 1), stream);
+        if (e == cudaSuccess && device_result) e = cudaMemsetAsync(device_result, 0, 2 * sizeof(int64_t), stream);
         if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
         return NB200_OK;
     }
@@ -904,7 +842,6 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     sizes.take<int32_t>((size_t)num_tiles + 1);
     sizes.take<int32_t>((size_t)num_tiles + 1);
     sizes.take<int32_t>((size_t)num_tiles + 1);
-    sizes.take<int64_t>(1);
     sizes.take<uint64_t>((size_t)num_tiles + 8);
     Workspace *ws = nullptr;
     if ((st = acquire_workspace(stream, sizes.used(), &ws))) return fail(st);
@@ -914,8 +851,8 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     cuts.a = carve.take<int32_t>((size_t)num_tiles + 1);
     cuts.b = carve.take<int32_t>((size_t)num_tiles + 1);
     int32_t *tile_count = carve.take<int32_t>((size_t)num_tiles + 1);
-    int64_t *d_total = carve.take<int64_t>(1);
-    // control block and tile words of the single-pass kernel, contiguous for one memset
+    // control block (status word, result length) and the tile words of the single-pass kernel,
+    // contiguous for one memset; the two-pass route uses the control block alone
     uint64_t *fused_block = carve.take<uint64_t>((size_t)num_tiles + 8);
     static_assert(sizeof(FusedCtl) <= 4 * sizeof(uint64_t), "control block must fit its slot");
     FusedCtl *ctl = reinterpret_cast<FusedCtl *>(fused_block);
@@ -925,34 +862,43 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     const int cbits = col_bits(a->cols);
     // NACHO_B200_TWO_PASS=1 forces the count -> scan -> fill route (for comparisons).
     static const bool force_two_pass = [] { const char *e = std::getenv("NACHO_B200_TWO_PASS"); return e && e[0] == '1'; }();
-    const bool fused = alloc || (capacity >= bound && !force_two_pass);
-    cudaError_t e;
-    if (fused) {
-        e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream);
-        if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
-        if (alloc && bound > 0) {
-            e = cudaMallocAsync(reinterpret_cast<void **>(&z->col), sizeof(int32_t) * (size_t)bound, stream);
-            if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&z->val), sizeof(float) * (size_t)bound, stream);
-            if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMallocAsync"));
-        }
+    const bool fused = alloc || device_result || (capacity >= bound && !force_two_pass);
+    cudaError_t e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * (fused ? (size_t)num_tiles + 4 : 4), stream);
+    if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
+    if (fused && alloc && bound > 0) {
+        e = cudaMallocAsync(reinterpret_cast<void **>(&z->col), sizeof(int32_t) * (size_t)bound, stream);
+        if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&z->val), sizeof(float) * (size_t)bound, stream);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMallocAsync"));
     }
     {
         LaunchScope scope("csr2_partition", stream);
         const int warps = num_tiles + 1;
         const int blocks = (warps * 32 + NT - 1) / NT;
-        k_csr2_partition<<<blocks, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts);
+        k_csr2_partition<<<blocks, NT, 0, stream>>>(A, B, rows, total, TILE_STEP, num_tiles, cuts);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_partition"));
 
-    if (fused) {
-        e = launch_tile<OP, MODE_FUSED>(A, B, cuts, cbits, nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
-        if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fused>"));
-        e = cudaMemcpyAsync(ws->host, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-        if (e != cudaSuccess) return fail(note_cuda_error(e, "read result length"));
-        FusedCtl h;
+    // Reads the control block back (one small copy and the call's only wait for the GPU).
+    auto read_ctl = [&](FusedCtl &h) -> int {
+        cudaError_t c = cudaMemcpyAsync(ws->host, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream);
+        if (c == cudaSuccess) c = cudaStreamSynchronize(stream);
+        if (c != cudaSuccess) return note_cuda_error(c, "read result length");
         std::memcpy(&h, ws->host, sizeof(h));
+        return NB200_OK;
+    };
+
+    FusedCtl h;
+    if (fused) {
+        e = launch_tile<OP, MODE_FUSED>(A, B, cuts, cbits, nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream, knobs);
+        if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fused>"));
+        if (device_result) {
+            k_publish_result<<<1, 1, 0, stream>>>(ctl, device_result);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return fail(note_cuda_error(e, "k_publish_result"));
+            return NB200_OK;
+        }
+        if ((st = read_ctl(h))) return fail(st);
         if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
         if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
         z->nnz = (int32_t)h.total;
@@ -965,23 +911,25 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
         return NB200_OK;
     }
 
-    e = launch_tile<OP, MODE_COUNT>(A, B, cuts, cbits, tile_count, nullptr, nullptr, CsrOut{nullptr, nullptr, nullptr}, num_tiles, stream);
+    // count -> scan -> fill. The scan leaves the result length in the control block, whose status
+    // word also collects a give-up of either tile launch (a bulk copy that did not land in time).
+    e = launch_tile<OP, MODE_COUNT>(A, B, cuts, cbits, tile_count, nullptr, ctl, CsrOut{nullptr, nullptr, nullptr}, num_tiles, stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<count>"));
     {
         LaunchScope scope("scan_tiles", stream);
-        k_scan_tiles<<<1, 1024, 0, stream>>>(tile_count, num_tiles, d_total);
+        k_scan_tiles<<<1, 1024, 0, stream>>>(tile_count, num_tiles, reinterpret_cast<int64_t *>(&ctl->total));
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_scan_tiles"));
-    e = cudaMemcpyAsync(ws->host, d_total, sizeof(int64_t), cudaMemcpyDeviceToHost, stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "read result length"));
-    const int64_t nnz = ws->host[0];
-    if (nnz > INT32_MAX) return fail(NB200_E_OVERFLOW);
-    z->nnz = (int32_t)nnz;
-    if (nnz > capacity) return NB200_E_CAPACITY;
-    e = launch_tile<OP, MODE_FILL>(A, B, cuts, cbits, tile_count, nullptr, nullptr, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
+    if ((st = read_ctl(h))) return fail(st);
+    if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+    if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
+    z->nnz = (int32_t)h.total;
+    if (h.total > capacity) return NB200_E_CAPACITY;
+    e = launch_tile<OP, MODE_FILL>(A, B, cuts, cbits, tile_count, nullptr, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fill>"));
+    if ((st = read_ctl(h))) return fail(st);
+    if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
     return NB200_OK;
 }
 
@@ -1040,8 +988,8 @@ int noalloc_scratch_address(void **out) {
         NB200_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
         // the tile kernel needs more dynamic shared memory than the default limit; set that
         // here too so that later calls are launches and nothing else
-        NB200_CUDA(cudaFuncSetAttribute(k_csr2_tile<VT_CSR2, OP_UNION, MODE_FUSED>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csr2_smem_bytes<VT_CSR2>()));
+        NB200_CUDA(cudaFuncSetAttribute(k_csr2_tile<V_CSR2, OP_UNION, MODE_FUSED>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csr2_smem_bytes()));
         address[dev] = p;
     }
     *out = address[dev];
@@ -1055,7 +1003,7 @@ int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const int32_t rows = a->rows;
     const int64_t total = (int64_t)a->nnz + b->nnz;
-    constexpr int tile_step = NT * VT_CSR2 - 1;
+    constexpr int tile_step = TILE_STEP;
     const int64_t tiles64 = (total + tile_step - 1) / tile_step;
     if (tiles64 > NOALLOC_MAX_TILES) return NB200_E_UNSUPPORTED;
     if (capacity < total) return NB200_E_CAPACITY;  // this entry point has the single-pass route only
@@ -1088,8 +1036,8 @@ int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_
     const int warps = num_tiles + 1;
     k_csr2_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts);
     NB200_CUDA(cudaGetLastError());
-    k_csr2_tile<VT_CSR2, OP_UNION, MODE_FUSED><<<num_tiles, NT + 32, csr2_smem_bytes<VT_CSR2>(), stream>>>(
-        A, B, cuts, col_bits(a->cols), nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val});
+    k_csr2_tile<V_CSR2, OP_UNION, MODE_FUSED><<<num_tiles, NT + 32, csr2_smem_bytes(), stream>>>(
+        A, B, cuts, col_bits(a->cols), nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, 0, LOOKBACK_POLL_LIMIT);
     NB200_CUDA(cudaGetLastError());
     FusedCtl h;  // read back into ordinary host memory: no pinned buffer is taken for this
     NB200_CUDA(cudaMemcpyAsync(&h, ctl, sizeof(h), cudaMemcpyDeviceToHost, stream));
@@ -1136,6 +1084,27 @@ int nb200_csr_add_3_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200
 
 int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {
     return csr_add_noalloc(a, b, z, capacity, stream);
+}
+
+int nb200_csr_add_f32_async(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, int64_t *device_result,
+                            void *stream) {
+    if (!device_result) return NB200_E_BADARG;
+    return csr2_run<OP_UNION>(a, b, z, false, capacity, stream, device_result);
+}
+
+int nb200_csr_mul_f32_async(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, int64_t *device_result,
+                            void *stream) {
+    if (!device_result) return NB200_E_BADARG;
+    return csr2_run<OP_INTERSECT>(a, b, z, false, capacity, stream, device_result);
+}
+
+int nb200_selftest_lookback_timeout(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, int32_t polls,
+                                    void *stream) {
+    if (polls < 1 || !a || !b || capacity < (int64_t)a->nnz + b->nnz) return NB200_E_BADARG;
+    LaunchKnobs knobs;
+    knobs.first_tile = 1;
+    knobs.poll_limit = polls;
+    return csr2_run<OP_UNION>(a, b, z, false, capacity, stream, nullptr, knobs);
 }
 
 }  // extern "C"

@@ -33,6 +33,7 @@ struct Pipeline {
     cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
     cudaEvent_t loaded[SLOTS] = {}, merged[SLOTS] = {}, drained[SLOTS] = {};
     bool ready = false;
+    std::mutex busy;  // held for a whole call: the streams, events and device buffers serve one call at a time
 };
 
 std::mutex g_pipe_mutex;
@@ -77,7 +78,30 @@ struct SlotArrays {
 
 typedef int (*into_fn)(const nb200_csr *, const nb200_csr *, nb200_csr *, int64_t, void *);
 
+int csr2_host_locked(Pipeline *pipe, into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity);
+
+// Validates, takes the device's pipeline for the whole call (concurrent callers on one device queue
+// up here), runs, and on any failure waits for every copy already queued on the three streams:
+// those copies read and write the caller's host buffers, which the caller may release as soon as
+// the call has returned.
 int csr2_host(into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity) {
+    if (!a || !b || !z || a->rows != b->rows || a->cols != b->cols || a->rows < 0 || capacity < 0) return NB200_E_BADARG;
+    if (!a->row_ptr || !b->row_ptr || !z->row_ptr) return NB200_E_BADARG;
+    Pipeline *pipe = nullptr;
+    int st;
+    if ((st = get_pipeline(&pipe))) return st;
+    std::lock_guard<std::mutex> busy(pipe->busy);
+    st = csr2_host_locked(pipe, op, is_union, a, b, z, capacity);
+    if (st != NB200_OK) {
+        cudaStreamSynchronize(pipe->in);
+        cudaStreamSynchronize(pipe->compute);
+        cudaStreamSynchronize(pipe->out);
+        cudaGetLastError();
+    }
+    return st;
+}
+
+int csr2_host_locked(Pipeline *pipe, into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity) {
     if (!a || !b || !z || a->rows != b->rows || a->cols != b->cols || a->rows < 0 || capacity < 0) return NB200_E_BADARG;
     if (!a->row_ptr || !b->row_ptr || !z->row_ptr) return NB200_E_BADARG;
     const int32_t rows = a->rows;
@@ -106,9 +130,7 @@ int csr2_host(into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b,
     }
     const int64_t max_z = is_union ? max_a + max_b : std::min(max_a, max_b);
 
-    Pipeline *pipe = nullptr;
     int st;
-    if ((st = get_pipeline(&pipe))) return st;
     Carver sizes;
     for (int s = 0; s < SLOTS; ++s) {
         for (int q = 0; q < 3; ++q) sizes.take<int32_t>((size_t)max_rows + 1);
@@ -162,9 +184,7 @@ int csr2_host(into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b,
         nb200_csr vz{0, 0, 0, d.z_rp, d.z_col, d.z_val};
         if ((st = op(&va, &vb, &vz, max_z, pipe->compute))) return st;  // returns once the block's length is known
         const int64_t n = vz.nnz;
-        if (produced + n > capacity || produced + n > INT32_MAX) {
-            cudaStreamSynchronize(pipe->in);
-            cudaStreamSynchronize(pipe->out);
+        if (produced + n > capacity || produced + n > INT32_MAX) {  // the caller drains the streams
             z->nnz = (int32_t)std::min<int64_t>(produced + n, INT32_MAX);
             return produced + n > INT32_MAX ? NB200_E_OVERFLOW : NB200_E_CAPACITY;
         }

@@ -810,13 +810,15 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
 
 // The plan of the latest symbolic pass, kept for the numeric pass that normally follows it on the
 // same operands: the bins, the window pointer table and the bitmaps are then not computed again.
-// It is used only if the operand arrays, sizes, device and stream are the same and neither pool
-// block was handed out to anyone in between (their generations are unchanged).
+// It is used only if the operand arrays, sizes, device and stream are the same, the result's row
+// offsets are the array that symbolic pass filled (with the length it reported), and neither pool
+// block was handed out to anyone in between (their generations are unchanged). The patterns of A
+// and B must not have been rewritten in place between the two passes; their values may change.
 struct SavedPlan {
     bool valid = false;
     EscPlan plan{};
-    const void *a_rp = nullptr, *a_col = nullptr, *b_rp = nullptr, *b_col = nullptr;
-    int32_t a_rows = 0, a_nnz = 0, b_rows = 0, b_cols = 0, b_nnz = 0;
+    const void *a_rp = nullptr, *a_col = nullptr, *b_rp = nullptr, *b_col = nullptr, *c_rp = nullptr;
+    int32_t a_rows = 0, a_nnz = 0, b_rows = 0, b_cols = 0, b_nnz = 0, c_nnz = 0;
     cudaStream_t stream = nullptr;
     int device = -1;
     uint64_t gen_main = 0, gen_cache = 0, epoch = 0;
@@ -824,11 +826,12 @@ struct SavedPlan {
 std::mutex g_saved_mutex;
 SavedPlan g_saved;
 
-void save_plan(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, cudaStream_t stream) {
+void save_plan(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, const EscPlan &plan, cudaStream_t stream) {
     std::lock_guard<std::mutex> g(g_saved_mutex);
     g_saved.valid = cudaGetDevice(&g_saved.device) == cudaSuccess;
     g_saved.plan = plan;
     g_saved.a_rp = a->row_ptr, g_saved.a_col = a->col, g_saved.b_rp = b->row_ptr, g_saved.b_col = b->col;
+    g_saved.c_rp = c->row_ptr, g_saved.c_nnz = c->nnz;
     g_saved.a_rows = a->rows, g_saved.a_nnz = a->nnz, g_saved.b_rows = b->rows, g_saved.b_cols = b->cols, g_saved.b_nnz = b->nnz;
     g_saved.stream = stream;
     g_saved.epoch = workspace_epoch();
@@ -836,12 +839,13 @@ void save_plan(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, cuda
     g_saved.gen_cache = plan.cache_ws ? plan.cache_ws->generation : 0;
 }
 
-bool take_saved_plan(const nb200_csr *a, const nb200_csr *b, cudaStream_t stream, EscPlan *out) {
+bool take_saved_plan(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, cudaStream_t stream, EscPlan *out) {
     std::lock_guard<std::mutex> g(g_saved_mutex);
     int dev = -1;
     if (!g_saved.valid || g_saved.epoch != workspace_epoch()) return false;  // the pool blocks may be gone
     if (cudaGetDevice(&dev) != cudaSuccess || dev != g_saved.device || stream != g_saved.stream) return false;
     if (a->row_ptr != g_saved.a_rp || a->col != g_saved.a_col || b->row_ptr != g_saved.b_rp || b->col != g_saved.b_col) return false;
+    if (c->row_ptr != g_saved.c_rp || c->nnz != g_saved.c_nnz) return false;  // row offsets obtained elsewhere: recompute
     if (a->rows != g_saved.a_rows || a->nnz != g_saved.a_nnz || b->rows != g_saved.b_rows || b->cols != g_saved.b_cols ||
         b->nnz != g_saved.b_nnz)
         return false;
@@ -891,7 +895,7 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
     const int64_t nnz = h.total;
     if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
     c->nnz = (int32_t)nnz;
-    save_plan(a, b, plan, stream);
+    save_plan(a, b, c, plan, stream);
     return NB200_OK;
 }
 
@@ -904,7 +908,7 @@ int spgemm_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, void *s
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (kept) return esc_run_bins<true>(a, b, *kept, c, stream);
     EscPlan plan{};
-    if (take_saved_plan(a, b, stream, &plan)) return esc_run_bins<true>(a, b, plan, c, stream);
+    if (take_saved_plan(a, b, c, stream, &plan)) return esc_run_bins<true>(a, b, plan, c, stream);
     if ((st = esc_prepare(a, b, false, false, stream, &plan))) return st;
     return esc_run_bins<true>(a, b, plan, c, stream);
 }

@@ -33,14 +33,25 @@ _F32P = C.POINTER(C.c_float)
 _F64P = C.POINTER(C.c_double)
 
 
+def reference_root() -> str | None:
+    """Where the reference checkout lies: ``$NACHO_REF_ROOT``, else a folder ``reference`` beside
+    this repository. None if neither holds the reference's sources."""
+    for cand in (os.environ.get("NACHO_REF_ROOT"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src")) and os.path.exists(os.path.join(cand, "compiler.cpp")):
+            return cand
+    return None
+
+
 def build(ref: bool | None = None) -> None:
     """Compile ``liboracle.so`` and, if the reference checkout is present (or ``ref`` is
     true), ``_ref/libnacho_ref_cpu.so``."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    ref_root = os.environ.get("NACHO_REF_ROOT", "/root/reference")
+    ref_root = reference_root()
     if ref is None:
-        ref = os.path.isdir(os.path.join(ref_root, "src"))
+        ref = ref_root is not None
     if ref:
+        if ref_root is None:
+            raise FileNotFoundError("the reference checkout was not found: set NACHO_REF_ROOT")
         subprocess.run(["make", "-s", "-j8", "-C", HERE, "ref", f"REF={ref_root}"], check=True)
 
 

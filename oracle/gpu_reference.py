@@ -28,7 +28,10 @@ _F32P = C.POINTER(C.c_float)
 
 def build() -> None:
     """Compile ``_ref/libnacho_ref_gpu.so`` (needs the reference checkout and nvcc)."""
-    ref_root = os.environ.get("NACHO_REF_ROOT", "/root/reference")
+    from .cpu_oracle import reference_root
+    ref_root = reference_root()
+    if ref_root is None:
+        raise FileNotFoundError("the reference checkout was not found: set NACHO_REF_ROOT")
     subprocess.run(["make", "-s", "-j8", "-C", HERE, "ref_gpu", f"REF={ref_root}"], check=True)
 
 

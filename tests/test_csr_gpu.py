@@ -168,6 +168,77 @@ def test_allocating_entry_points(nacho, csr_golden):
                 check(lib.nb200_free_async(p, None), "free")
 
 
+def test_allocating_add_3_entry_point(nacho, csr_golden):
+    """nb200_csr_add_3_f32 allocates its own result arrays (freed one by one afterwards)."""
+    import torch
+    from nacho_b200._capi import CsrStruct, check, lib
+    for case in ("smoke", "medium", "all_empty", "cancel"):
+        ops = [csr_to_gpu(golden_csr(csr_golden, case, tag)) for tag in ("a", "b", "c")]
+        structs = [g._struct() for g in ops]
+        z = CsrStruct()
+        check(lib.nb200_csr_add_3_f32(*[C.byref(x) for x in structs], C.byref(z), 256, 256, None), "add3")
+        torch.cuda.synchronize()
+        got = CSR(z.rows, z.cols, _d2h(z.row_ptr, z.rows + 1, np.int32), _d2h(z.col, z.nnz, np.int32),
+                  _d2h(z.val, z.nnz, np.float32))
+        assert_same(got, golden_csr(csr_golden, case, "add3"), f"{case} add3 (allocating)")
+        if z.nnz == 0:
+            assert not z.col and not z.val
+        for p in (z.row_ptr, z.col, z.val):
+            check(lib.nb200_free_async(p, None), "free")
+
+
+def test_async_entry_points_leave_the_length_on_the_device(nacho, csr_golden):
+    """nb200_csr_{add,mul}_f32_async return without waiting; length and status arrive in two device words."""
+    import torch
+    from nacho_b200 import _capi
+    from nacho_b200._capi import CsrStruct, check, lib
+    for case in ("medium", "giant_row", "all_empty"):
+        a, b = golden_csr(csr_golden, case, "a"), golden_csr(csr_golden, case, "b")
+        ga, gb = csr_to_gpu(a), csr_to_gpu(b)
+        for fn, tag, cap in ((lib.nb200_csr_add_f32_async, "add", len(a.col) + len(b.col)),
+                             (lib.nb200_csr_mul_f32_async, "mul", min(len(a.col), len(b.col)))):
+            want = golden_csr(csr_golden, case, tag)
+            rp = torch.empty(a.rows + 1, dtype=torch.int32, device="cuda")
+            col = torch.empty(max(cap, 1), dtype=torch.int32, device="cuda")
+            val = torch.empty(max(cap, 1), dtype=torch.float32, device="cuda")
+            res = torch.full((2,), -1, dtype=torch.int64, device="cuda")
+            z = CsrStruct(a.rows, a.cols, 0, rp.data_ptr(), col.data_ptr(), val.data_ptr())
+            sa, sb = ga._struct(), gb._struct()
+            check(fn(C.byref(sa), C.byref(sb), C.byref(z), cap, res.data_ptr(), None), tag)
+            n, status = (int(x) for x in res.cpu())
+            assert status == _capi.OK and n == len(want.col)
+            got = CSR(a.rows, a.cols, rp.cpu().numpy(), col[:n].cpu().numpy(), val[:n].cpu().numpy())
+            assert_same(got, want, f"{case} {tag} (async)")
+            if cap > 0:  # a capacity below the worst case is refused: this form cannot count first
+                assert fn(C.byref(sa), C.byref(sb), C.byref(z), cap - 1, res.data_ptr(), None) == _capi.E_CAPACITY
+
+
+def test_bounded_wait_gives_up_and_reports(nacho, oracle):
+    """The look-back of the single-pass kernel, made to wait for a tile that never runs: the wait
+    ends after its poll limit, the call reports NB200_E_TIMEOUT, and the context keeps working."""
+    import time
+    import torch
+    from nacho_b200 import _capi, synth
+    from nacho_b200._capi import CsrStruct, lib
+    ta, tb = synth.random_csr(4000, 30000, 0.004, 71), synth.random_csr(4000, 30000, 0.004, 72)
+    ga, gb = synth_to_gpu(ta), synth_to_gpu(tb)
+    cap = ga.values.numel() + gb.values.numel()
+    assert cap > 5 * 5200, "needs several tiles"
+    rp = torch.zeros(4001, dtype=torch.int32, device="cuda")
+    col = torch.empty(cap, dtype=torch.int32, device="cuda")
+    val = torch.empty(cap, dtype=torch.float32, device="cuda")
+    z = CsrStruct(4000, 30000, 0, rp.data_ptr(), col.data_ptr(), val.data_ptr())
+    sa, sb = ga._struct(), gb._struct()
+    t0 = time.perf_counter()
+    status = lib.nb200_selftest_lookback_timeout(C.byref(sa), C.byref(sb), C.byref(z), cap, 50, None)
+    torch.cuda.synchronize()
+    assert status == _capi.E_TIMEOUT
+    assert time.perf_counter() - t0 < 5.0, "the give-up must come after a short, bounded wait"
+    assert "wait" in lib.nb200_strerror(status).decode()
+    # the same context, stream and scratch pool still give exact results
+    assert_same(csr_from_gpu(nacho.gpu_csr_add_f32(ga, gb)), oracle.csr_add(synth_csr(ta), synth_csr(tb), 8), "add after a give-up")
+
+
 @pytest.mark.parametrize("case", ["smoke", "medium", "identical", "giant_row"])
 def test_two_pass_route_with_exact_capacity(nacho, csr_golden, case):
     """A capacity below the worst-case bound but large enough for the result takes the
@@ -207,6 +278,10 @@ def test_capacity_and_argument_errors(nacho, csr_golden):
     assert lib.nb200_csr_add_f32_into(None, C.byref(sb), C.byref(z), 8, None) == _capi.E_BADARG
     bad = CsrStruct(a.rows + 1, a.cols, sb.nnz, sb.row_ptr, sb.col, sb.val)
     assert lib.nb200_csr_add_f32_into(C.byref(sa), C.byref(bad), C.byref(z), 8, None) == _capi.E_BADARG
+    # a stated capacity without the arrays behind it is refused before anything is launched
+    hollow = CsrStruct(a.rows, a.cols, 0, rp.data_ptr(), None, None)
+    assert lib.nb200_csr_add_f32_into(C.byref(sa), C.byref(sb), C.byref(hollow), 1 << 20, None) == _capi.E_BADARG
+    assert lib.nb200_csr_mul_f32_into(C.byref(sa), C.byref(sb), C.byref(hollow), 1 << 20, None) == _capi.E_BADARG
     with pytest.raises(TypeError):
         nacho.CSR_gpu(ga.dim_j_offsets.cpu(), ga.dim_j_indices, ga.values, ga.shape)
     with pytest.raises(TypeError):

@@ -1,0 +1,133 @@
+"""GPU suite: the benchmark configurations at their stated sizes, bit-for-bit against the CPU
+checker (the reference's own emitted CPU kernels where that library was built, else the C oracle
+with every host thread). Operands are generated on the GPU, copied to the host once for the
+checker, and the result arrays are compared one at a time.
+
+  configuration 2   CSR multiply, 2^20 x 2^20, Zipf rows, 16 entries per row on average
+  configuration 3   CSR add (sigma 0 and 3) and the three-operand add (sigma 0), 64 M entries per operand
+  configuration 4a  SpGEMM on R-MAT scale 16 (B = A^T): structure exact, values against a float64 product
+  configuration 5   COO3 and CSF3 add, 100 M entries per operand
+"""
+import numpy as np
+import pytest
+
+from helpers import assert_same, csf3_levels, csr_from_gpu, synth_csr, synth_to_gpu
+from oracle.cpu_oracle import COO3, CSF3, CSR
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nacho():
+    import torch
+    assert torch.cuda.is_available(), "GPU suite needs a CUDA device"
+    from nacho_b200 import nacho as mod
+    return mod
+
+
+@pytest.fixture(scope="module")
+def checker():
+    """name -> function over oracle-style tuples; says which checker it is."""
+    from oracle.cpu_oracle import Oracle, Reference, default_threads
+    if Reference.available():
+        ref = Reference()
+        return {"kind": "reference", "csr_add": ref.csr_add, "csr_mul": ref.csr_mul, "csr_add_3": ref.csr_add_3,
+                "coo3_add": ref.coo3_add, "csf3_add": ref.csf3_add}
+    orc, n = Oracle(), default_threads()
+    return {"kind": "port", "csr_add": lambda a, b: orc.csr_add(a, b, n), "csr_mul": lambda a, b: orc.csr_mul(a, b, n),
+            "csr_add_3": lambda a, b, c: orc.csr_add_3(a, b, c, n), "coo3_add": lambda a, b: orc.coo3_add(a, b, n),
+            "csf3_add": orc.csf3_add}
+
+
+def test_config2_mul_full_size(nacho, checker):
+    from nacho_b200 import synth
+    ta, tb = synth.c2_pair(device="cuda")
+    assert ta[0] == 1 << 20
+    got = csr_from_gpu(nacho.gpu_csr_mul_f32(synth_to_gpu(ta), synth_to_gpu(tb)))
+    assert_same(got, checker["csr_mul"](synth_csr(ta), synth_csr(tb)), f"config 2 at full size vs {checker['kind']}")
+    got = csr_from_gpu(nacho.gpu_csr_add_f32(synth_to_gpu(ta), synth_to_gpu(tb)))
+    assert_same(got, checker["csr_add"](synth_csr(ta), synth_csr(tb)), f"config 2 operands, add, vs {checker['kind']}")
+
+
+@pytest.mark.parametrize("sigma", [0, 3])
+def test_config3_add_full_size(nacho, checker, sigma):
+    from nacho_b200 import synth
+    ta, tb = synth.c3_csr(0, sigma, device="cuda"), synth.c3_csr(1, sigma, device="cuda")
+    assert ta[0] == 1 << 20 and ta[3].numel() > 40_000_000
+    got = csr_from_gpu(nacho.gpu_csr_add_f32(synth_to_gpu(ta), synth_to_gpu(tb)))
+    want = checker["csr_add"](synth_csr(ta), synth_csr(tb))
+    assert_same(got, want, f"config 3 sigma={sigma} at full size vs {checker['kind']}")
+
+
+def test_config3_add_3_full_size(nacho, checker):
+    from nacho_b200 import synth
+    ts = [synth.c3_csr(k, 0, device="cuda") for k in range(3)]
+    got = csr_from_gpu(nacho.gpu_csr_add_3_f32(*[synth_to_gpu(t) for t in ts]))
+    want = checker["csr_add_3"](*[synth_csr(t) for t in ts])
+    assert_same(got, want, f"config 3 add_3 at full size vs {checker['kind']}")
+
+
+def test_config5_coo3_and_csf3_full_size(nacho, checker):
+    import torch
+    from nacho_b200 import synth
+    ta, tb = synth.c5_pair(device="cuda")
+    assert ta[1].numel() > 90_000_000
+    mk = lambda t: nacho.COO3_gpu(t[1], t[2], t[3], t[4], torch.tensor(list(t[0]), dtype=torch.int32))
+    z = nacho.gpu_coo3d_add_f32(mk(ta), mk(tb))
+    torch.cuda.synchronize()
+    to_np = lambda t: COO3(*synth.to_numpy(t))
+    a, b = to_np(ta), to_np(tb)
+    want = checker["coo3_add"](a, b)
+    for name, arr in (("i", z.dim_i_indices), ("j", z.dim_j_indices), ("k", z.dim_k_indices), ("val", z.values)):
+        got = arr.cpu().numpy()
+        ref = getattr(want, name)
+        assert got.shape == ref.shape, f"config 5 coo3 {name}: {got.shape} vs {ref.shape}"
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), f"config 5 coo3 {name} differs from {checker['kind']}"
+    del z, want
+    # CSF3: the same coordinates as level arrays
+    def levels(t):
+        c = np.stack([t.i, t.j, t.k], axis=1)
+        return CSF3(t.dims, *csf3_levels(c), t.val)
+    fa, fb = levels(a), levels(b)
+    del a, b
+    shape = torch.tensor(list(fa.dims), dtype=torch.int32)
+    gpu = lambda f: nacho.CSF3_gpu(*[torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in f[1:]], shape)
+    f = nacho.gpu_csf_add_f32(gpu(fa), gpu(fb))
+    torch.cuda.synchronize()
+    want = checker["csf3_add"](fa, fb)
+    for name, arr in (("i_idx", f.dim_i_indices), ("j_ptr", f.dim_j_offsets), ("j_idx", f.dim_j_indices),
+                      ("k_ptr", f.dim_k_offsets), ("k_idx", f.dim_k_indices), ("val", f.values)):
+        got = arr.cpu().numpy()
+        ref = getattr(want, name)
+        assert got.shape == ref.shape, f"config 5 csf3 {name}: {got.shape} vs {ref.shape}"
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), f"config 5 csf3 {name} differs from {checker['kind']}"
+
+
+def test_config4a_rmat_scale16(nacho, oracle, capsys):
+    """SpGEMM on R-MAT scale 16 (65536 rows, about 4e8 products): the structure must equal the
+    oracle's. Values are float32 sums of float32 products, so a pure relative error per entry is
+    only meaningful where the sum does not cancel; both criteria are computed and reported:
+      bound     |x - x64| <= 1e-5 * sum|a b|   asserted for every entry
+      relative  |x - x64| <= 1e-5 * |x64|      asserted wherever |x64| >= sum|a b| / 2, and the share of
+                                                 all entries that meets it is reported (and must be >= 99 %)
+    """
+    from nacho_b200 import synth
+    from oracle.cpu_oracle import default_threads
+    ta = synth.rmat_csr(scale=16, seed=4000, device="cuda")
+    tb = synth.transpose_csr(ta)
+    got = csr_from_gpu(nacho.gpu_spgemm_f32(synth_to_gpu(ta), synth_to_gpu(tb)))
+    want, v64, abs64, products = oracle.spgemm(synth_csr(ta), synth_csr(tb), default_threads(), extras=True)
+    assert np.array_equal(got.row_ptr, want.row_ptr), "row offsets differ"
+    assert np.array_equal(got.col, want.col), "columns differ"
+    err = np.abs(got.val.astype(np.float64) - v64)
+    bound_ratio = float((err / np.maximum(abs64, 1e-300)).max())
+    rel_ok = err <= 1e-5 * np.abs(v64)
+    well = np.abs(v64) >= 0.5 * abs64
+    rel_well = float((err[well] / np.abs(v64[well])).max())
+    with capsys.disabled():
+        print(f"\n[config 4a, R-MAT scale 16] products {products}, nnz(C) {len(want.col)}: max |x-x64| / sum|ab| = {bound_ratio:.3e}; "
+              f"entries within 1e-5 relative: {rel_ok.mean():.4%}; max relative error where |x64| >= sum|ab|/2 "
+              f"({well.mean():.1%} of the entries): {rel_well:.3e}")
+    assert bound_ratio <= 1e-5
+    assert rel_well <= 1e-5
+    assert rel_ok.mean() >= 0.99

@@ -201,6 +201,42 @@ def test_full_size_laplacian_properties(nacho):
     assert bool((c.values == c.values.round()).all())
 
 
+def test_allocating_entry_point(nacho, oracle):
+    """nb200_spgemm_f32 allocates the three result arrays itself (released one by one)."""
+    import ctypes as C
+    import torch
+    from nacho_b200 import synth
+    from nacho_b200._capi import CsrStruct, check as ck, lib
+    rt = C.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+
+    def d2h(ptr, count, dtype):
+        out = np.empty(count, dtype)
+        if count:
+            assert rt.cudaMemcpy(out.ctypes.data, ptr, out.nbytes, 2) == 0
+        return out
+
+    cases = [(synth.random_csr(500, 400, 0.03, 21), synth.random_csr(400, 300, 0.03, 22)),
+             (synth.random_csr(64, 50, 0.0, 1), synth.random_csr(50, 70, 0.2, 2))]
+    ta = synth.rmat_csr(scale=10, seed=4210)
+    cases.append((ta, synth.transpose_csr(ta)))
+    for ta, tb in cases:
+        want, v64, abs64, _ = oracle.spgemm(synth_csr(ta), synth_csr(tb), 4, extras=True)
+        ga, gb = synth_to_gpu(ta), synth_to_gpu(tb)
+        sa, sb, c = ga._struct(), gb._struct(), CsrStruct()
+        ck(lib.nb200_spgemm_f32(C.byref(sa), C.byref(sb), C.byref(c), 256, 256, None), "spgemm")
+        torch.cuda.synchronize()
+        assert (c.rows, c.cols, c.nnz) == (want.rows, want.cols, len(want.col))
+        assert np.array_equal(d2h(c.row_ptr, c.rows + 1, np.int32), want.row_ptr)
+        assert np.array_equal(d2h(c.col, c.nnz, np.int32), want.col)
+        val = d2h(c.val, c.nnz, np.float32)
+        assert np.all(np.abs(val.astype(np.float64) - v64) <= REL_TOL * abs64 + 1e-30)
+        if c.nnz == 0:
+            assert not c.col and not c.val
+        for p in (c.row_ptr, c.col, c.val):
+            ck(lib.nb200_free_async(p, None), "free")
+
+
 def test_symbolic_reports_products(nacho, oracle):
     import ctypes as C
     import torch

@@ -113,15 +113,60 @@ def test_coo3_properties_at_scale(nacho):
     assert torch.equal(key(z2), kz)
 
 
-def test_too_wide_extents_are_refused(nacho):
+@pytest.mark.parametrize("dims,n,seed", [((1 << 30, 1 << 30, 1 << 30), 40_000, 61), ((2**31 - 1, 5, 2**31 - 1), 30_000, 62),
+                                          ((7, 2**31 - 1, 1 << 29), 9_000, 63), ((1 << 22, 1 << 21, 1 << 21), 60_000, 64)])
+def test_wide_extents_vs_oracle(nacho, oracle, dims, n, seed):
+    """Extents whose coordinates do not pack into 64 bits (more than 63 bits together) take the
+    kernel that compares (i, j) and k as two words; COO3 and CSF3 results equal the oracle's."""
+    (ca, va), (cb, vb) = _seeded(dims, n, seed)
+    a, b = COO3(dims, ca[:, 0], ca[:, 1], ca[:, 2], va), COO3(dims, cb[:, 0], cb[:, 1], cb[:, 2], vb)
+    z = nacho.gpu_coo3d_add_f32(nacho.to_coo3(ca, va, dims, "cuda"), nacho.to_coo3(cb, vb, dims, "cuda"))
+    assert_same(coo3_from_gpu(z), oracle.coo3_add(a, b, 8), "coo3, wide extents")
+    fa, fb = CSF3(dims, *csf3_levels(ca), va), CSF3(dims, *csf3_levels(cb), vb)
+    f = nacho.gpu_csf_add_f32(nacho.to_csf3(ca, va, dims, "cuda"), nacho.to_csf3(cb, vb, dims, "cuda"))
+    assert_same(csf3_from_gpu(f), oracle.csf3_add(fa, fb), "csf3, wide extents")
+    # identical operands: every coordinate is in both
+    z2 = nacho.gpu_coo3d_add_f32(nacho.to_coo3(ca, va, dims, "cuda"), nacho.to_coo3(ca, va, dims, "cuda"))
+    assert_same(coo3_from_gpu(z2), oracle.coo3_add(a, a, 8), "coo3, wide extents, identical operands")
+
+
+def test_allocating_tensor_entry_points(nacho, oracle):
+    """nb200_coo3d_add_f32 and nb200_csf_add_f32 allocate their own result arrays, each released
+    separately with nb200_free_async, as an adopting binding would."""
+    import ctypes as C
     import torch
-    from nacho_b200._capi import NachoB200Error
-    dims = (1 << 30, 1 << 30, 1 << 30)
-    c = np.array([[1, 2, 3]], np.int32)
-    v = np.ones(1, np.float32)
-    t = nacho.to_coo3(c, v, dims, "cuda")
-    with pytest.raises(NachoB200Error):
-        nacho.gpu_coo3d_add_f32(t, t)
+    from nacho_b200._capi import Coo3Struct, Csf3Struct, check, lib
+    rt = C.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+
+    def d2h(ptr, count, dtype):
+        out = np.empty(count, dtype)
+        if count:
+            assert rt.cudaMemcpy(out.ctypes.data, ptr, out.nbytes, 2) == 0
+        return out
+
+    for dims, n, seed in (((40, 30, 25), 900, 1), ((1 << 12, 1 << 10, 1 << 8), 50_000, 2), ((1 << 30, 1 << 30, 1 << 30), 20_000, 3)):
+        (ca, va), (cb, vb) = _seeded(dims, n, seed)
+        a, b = COO3(dims, ca[:, 0], ca[:, 1], ca[:, 2], va), COO3(dims, cb[:, 0], cb[:, 1], cb[:, 2], vb)
+        ga, gb = nacho.to_coo3(ca, va, dims, "cuda"), nacho.to_coo3(cb, vb, dims, "cuda")
+        sa, sb, z = ga._struct(), gb._struct(), Coo3Struct()
+        check(lib.nb200_coo3d_add_f32(C.byref(sa), C.byref(sb), C.byref(z), 256, 256, None), "coo3d_add")
+        torch.cuda.synchronize()
+        got = COO3(tuple(z.dims), d2h(z.i, z.nnz, np.int32), d2h(z.j, z.nnz, np.int32), d2h(z.k, z.nnz, np.int32),
+                   d2h(z.val, z.nnz, np.float32))
+        assert_same(got, oracle.coo3_add(a, b, 4), f"coo3 allocating, dims {dims}")
+        for p in (z.i, z.j, z.k, z.val):
+            check(lib.nb200_free_async(p, None), "free")
+        fa, fb = nacho.to_csf3(ca, va, dims, "cuda"), nacho.to_csf3(cb, vb, dims, "cuda")
+        ta, tb, f = fa._struct(), fb._struct(), Csf3Struct()
+        check(lib.nb200_csf_add_f32(C.byref(ta), C.byref(tb), C.byref(f), 256, 256, None), "csf_add")
+        torch.cuda.synchronize()
+        got = CSF3(tuple(f.dims), d2h(f.i_idx, f.n_i, np.int32), d2h(f.j_ptr, f.n_i + 1, np.int32), d2h(f.j_idx, f.n_j, np.int32),
+                   d2h(f.k_ptr, f.n_j + 1, np.int32), d2h(f.k_idx, f.n_k, np.int32), d2h(f.val, f.n_k, np.float32))
+        want = oracle.csf3_add(CSF3(dims, *csf3_levels(ca), va), CSF3(dims, *csf3_levels(cb), vb))
+        assert_same(got, want, f"csf3 allocating, dims {dims}")
+        for p in (f.i_idx, f.j_ptr, f.j_idx, f.k_ptr, f.k_idx, f.val):
+            check(lib.nb200_free_async(p, None), "free")
 
 
 def test_csf3_blocks_through_the_gpu_operator(nacho):
