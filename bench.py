@@ -21,10 +21,20 @@ entries per operand, uniform rows). Rank 0 prints one JSON line:
              null where that library was not built, "unavailable" where the input exceeds the
              reference's int32 product counters
 
-With N > 1 (launched by torch.distributed.run) every rank holds its own row block of the same
-size (weak scaling); the only exchange is the all-gather of (rows, nnz) per block that stitches
-the global row offsets, and it is inside the timed region. SpGEMM's B is replicated by a
-broadcast before the timed region.
+CSR add / multiply run through the row-block operator of nacho_b200.shard at every N: the operator
+is queued without a wait on the host (result length and status stay on the device) and, with
+N > 1 (launched by torch.distributed.run), the all-gather of (rows, nnz) per block that stitches
+the global row offsets is an asynchronous collective inside the timed region. With N > 1 the
+default is STRONG scaling: one fixed operand pair (the N = 1 workload, same seed on every rank)
+cut into N row blocks of equal stored entries by shard.row_block_cuts_device; every rank's block
+result is checked, outside the timed region, against the unsharded result. `--scaling weak` gives
+every rank its own operand pair of the N = 1 size instead, as do the other operators (SpGEMM's B
+is replicated by a broadcast before the timed region).
+
+Timing: W >= 3 warm-up steps, then windows of exactly K steps each (barrier + synchronize on both
+sides, CUDA events on the launching stream, maximum over ranks) repeated until at least half a
+second has been timed; the reported ms_per_step is the median window's. Workloads smaller than
+twice the L2 are timed step by step with the L2 flushed (a 256 MiB fill) before every step.
 """
 from __future__ import annotations
 
@@ -253,8 +263,9 @@ def cpu_baseline(name: str, operands, steps: int = 3, warmup: int = 1):
         nbytes = algorithmic_bytes(spec, [size(m) for m in operands], size(out))
         nnz_in = sum(len(m.val) for m in operands)
     t = statistics.mean(times)
+    rows = operands[0].rows if spec["fmt"] == "csr" else int(operands[0].dims[0])
     return {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": cores, "kind": "reference" if use_ref else "port",
-            "nnz_per_s": nnz_in / t, "ms": t * 1e3}
+            "nnz_per_s": nnz_in / t, "ms": t * 1e3, "rows": rows, "nnz_in": nnz_in, "nnz_out": len(out.val), "bytes": nbytes}
 
 
 def ref_gpu_baseline(spec, tensors, nbytes, products=None, runs: int = 3):
@@ -289,31 +300,63 @@ def ref_gpu_baseline(spec, tensors, nbytes, products=None, runs: int = 3):
             "kind": "reference GPU kernels as emitted by its compiler, recompiled for sm_100a; whole driver call"}
 
 
-def cpu_sample_scale(name: str, requested: float) -> float:
-    """Fraction of the workload used for CPU timing: about 10-30 s of CPU work in total."""
-    if name == "c1_csr_add" or name.startswith("c4"):
-        return 1.0
-    return requested
+def cpu_sample_scale(name: str, requested: float | None) -> float:
+    """Fraction of the workload's rows / entries the CPU legs run: the whole workload wherever a
+    CPU step takes a second or two (configurations 1, 2, 3, 4b), one eighth for configuration 5
+    (100 M entries per operand) unless --cpu-scale says otherwise."""
+    if requested is not None:
+        return requested
+    return 0.125 if name.startswith("c5") else 1.0
+
+
+def job_config(args, world: int, scaling: str, rows: int, nnz_in: int, nnz_out: int, nbytes: int, extra=None) -> dict:
+    """The `config` object of a result line. Whole-job figures only (nothing per rank), so that the
+    reference arm, which runs the same job on the host cores, prints the same object."""
+    cfg = {"workload": args.workload, "rows_scale": args.rows_scale, "scaling": scaling, "rows": rows,
+           "operand_nnz": nnz_in, "result_nnz": nnz_out, "algorithmic_bytes": nbytes,
+           "l2_policy": ("inputs_larger_than_L2" if nbytes / max(world, 1) > 2 * 126e6
+                         else "L2 flushed (256 MiB fill) before every timed step"),
+           "parallelism": (f"{world} row blocks of equal stored entries, all-gather of (rows, nnz) per step" if scaling == "strong"
+                           else f"one operand set per rank x{world}, all-gather of (rows, nnz) per step")}
+    if args.workload == "c4a_spgemm_rmat":
+        cfg["rmat_scale"] = args.rmat_scale
+    cfg.update(extra or {})
+    return cfg
+
+
+def default_scaling(args, spec) -> str:
+    if args.gpus > 1 and spec["op"] in ("csr_add", "csr_mul"):
+        return args.scaling or "strong"
+    return "weak"
 
 
 def run_reference(args):
-    """`--impl reference`: the reference's CPU implementation of the path on the host cores,
-    each step one bounded sample of the workload. Rank 0 only."""
+    """`--impl reference`: the reference's CPU implementation of the path on the host cores, on
+    the same workload as the other arm (the whole job: under strong scaling that is the one fixed
+    operand pair whatever N is). Rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     import torch
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     spec = WORKLOADS[args.workload]
-    scale = cpu_sample_scale(args.workload, args.cpu_scale)
-    ops = make_operands(args.workload, 0, dev, scale=scale, rmat_scale=min(args.rmat_scale, 14))
+    scale = cpu_sample_scale(args.workload, args.cpu_scale) * args.rows_scale
+    cpu_rmat = min(args.rmat_scale, 14)  # the CPU port sorts every product; keep its sample bounded
+    ops = make_operands(args.workload, 0, dev, scale=scale, rmat_scale=cpu_rmat)
     ops_np = [to_oracle(spec, t) for t in ops]
+    del ops
     base = cpu_baseline(args.workload, ops_np, steps=args.steps, warmup=args.warmup)
-    sample = f"{args.workload} at scale {scale:g} of its rows/entries"
+    whole = scale == args.rows_scale and (args.workload != "c4a_spgemm_rmat" or cpu_rmat == args.rmat_scale)
+    sample = ("the whole workload" if whole else f"{args.workload} at scale {scale:g} of its rows/entries"
+              + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" else ""))
+    scaling = default_scaling(args, spec)
+    config = job_config(args, args.gpus, scaling, base["rows"], base["nnz_in"], base["nnz_out"], base["bytes"])
+    if not whole:
+        config["sample"] = sample
     line = {
         "impl": "reference", "metric": f"{spec['op']} effective HBM GB/s (operand + result bytes)",
         "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": base["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": args.workload, "sample": sample},
+        "ms_per_step": base["ms"], "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config,
         "cpu_baseline": {"value": base["value"], "unit": "GB/s", "cores": base["cores"], "kind": base["kind"],
                          "sample": sample},
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -361,6 +404,14 @@ def result_meta(spec, z):
     return sum(b.numel() * 4 for b in buffers_of(z))
 
 
+def row_block(t, r0: int, r1: int):
+    """Rows [r0, r1) of a CSR synth tuple on the device: row offsets rebased to 0 (a new array),
+    columns and values as views."""
+    rows, cols, rp, col, val = t
+    lo, hi = int(rp[r0]), int(rp[r1])
+    return r1 - r0, cols, (rp[r0:r1 + 1] - rp[r0]).contiguous(), col[lo:hi], val[lo:hi]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,8 +419,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c3_csr_add_sigma0", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-scale", type=float, default=0.125,
-                    help="fraction of the workload's rows/entries in the CPU-baseline sample")
+    ap.add_argument("--cpu-scale", type=float, default=None,
+                    help="fraction of the workload's rows/entries in the CPU legs (default: 1 = the same workload, "
+                         "except configuration 5)")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default=None,
+                    help="N > 1, CSR add / multiply: one fixed operand pair cut into N row blocks (strong, default) "
+                         "or one pair of the N = 1 size per rank (weak)")
+    ap.add_argument("--min-seconds", type=float, default=0.5, help="timed K-step windows are repeated until this much is timed")
     ap.add_argument("--rows-scale", type=float, default=1.0,
                     help="shrink the workload by this factor (profiling captures only; a line printed with a "
                          "factor other than 1 is not a benchmark result)")
@@ -399,8 +455,20 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     spec = WORKLOADS[args.workload]
+    args.gpus = world
+    scaling = default_scaling(args, spec)
+    block_op = spec["op"] in ("csr_add", "csr_mul")
     op_fn = getattr(nacho, f"gpu_{spec['op']}_f32")
-    ops = make_operands(args.workload, rank, dev, scale=args.rows_scale, rmat_scale=args.rmat_scale)
+    full_ops = None
+    cuts = None
+    if scaling == "strong":
+        # one fixed operand pair, the same on every rank (same seed, same device type), cut into
+        # `world` row blocks of equal stored entries; each rank keeps its block resident
+        full_ops = make_operands(args.workload, 0, dev, scale=args.rows_scale, rmat_scale=args.rmat_scale)
+        cuts = shard.row_block_cuts_device([t[2] for t in full_ops], world)
+        ops = [row_block(t, cuts[rank], cuts[rank + 1]) for t in full_ops]
+    else:
+        ops = make_operands(args.workload, rank, dev, scale=args.rows_scale, rmat_scale=args.rmat_scale)
     if spec["op"] == "spgemm" and world > 1:
         # B is replicated: rank 0's B goes to every rank (A stays a per-rank row block)
         rows_b, cols_b, rp_b, col_b, val_b = ops[1]
@@ -410,12 +478,20 @@ def main():
     tensors, metas = build_device_operands(spec, ops, dev)
     nnz_in = sum(t.values.numel() for t in tensors)
     rows_local = int(tensors[0].shape[0])
+    oper = shard.CsrRowBlockOp("add" if spec["op"] == "csr_add" else "mul", tensors[0], tensors[1]) if block_op else None
 
     def step():
+        if block_op:  # queued without a host wait; the stitch is an asynchronous collective
+            oper.launch()
+            return None
         z = op_fn(*tensors)
         if world > 1:  # stitch: every block's (rows, nnz) -> global row-offset bases, left on the device
             shard.stitch_on_device(rows_local, z.values.numel(), device=dev)
         return z
+
+    def finish():
+        if block_op:
+            oper.drain()  # the launching stream waits for the collectives still in flight
 
     def barrier():
         if world > 1:
@@ -425,29 +501,98 @@ def main():
     z = None
     for _ in range(args.warmup):
         z = step()
+    finish()
+    if block_op:
+        z, _, _ = oper.result()
+    torch.cuda.synchronize()
     zmeta = result_meta(spec, z)
     nbytes = algorithmic_bytes(spec, metas, zmeta)
     nnz_out = z.values.numel()
+    flush = nbytes < 2 * 126e6
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
 
-    # keep the timed region long enough for the clock sampler (about half a second at least)
+    # ---- timed windows of exactly K steps each, repeated until min-seconds are timed
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
     stream = torch.cuda.current_stream()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+
+    def window():
+        """One window of K steps; returns its device time in ms (this rank)."""
+        barrier()
+        if flush:  # L2-resident workload: every step starts from a flushed L2, timed on its own
+            total = 0.0
+            for _ in range(args.steps):
+                flush_buf.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                step()
+                finish()
+                e1.record(stream)
+                e1.synchronize()
+                total += e0.elapsed_time(e1)
+            barrier()
+            return total
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        finish()
+        e1.record(stream)
+        barrier()
+        return e0.elapsed_time(e1)
+
     launches0 = _capi.launch_count()
     t_wall0 = time.perf_counter()
-    start.record(stream)
-    for _ in range(args.steps):
-        z = step()
-    stop.record(stream)
-    barrier()
-    t_wall1 = time.perf_counter()
+    first = window()
     launches = _capi.launch_count() - launches0
-    elapsed_ms = start.elapsed_time(stop)
+    n_windows = max(1, min(500, int(args.min_seconds * 1e3 / max(first, 1e-3)) + 1))
+    if world > 1:  # every rank runs the same number of windows
+        nw = torch.tensor([n_windows], dtype=torch.int64, device=dev)
+        dist.all_reduce(nw, op=dist.ReduceOp.MAX)
+        n_windows = int(nw[0])
+    window_ms = [first] + [window() for _ in range(n_windows - 1)]
+    t_wall1 = time.perf_counter()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    if world > 1:  # a window's time is the slowest rank's
+        wm = torch.tensor(window_ms, dtype=torch.float64, device=dev)
+        dist.all_reduce(wm, op=dist.ReduceOp.MAX)
+        window_ms = wm.cpu().tolist()
+    elapsed_ms = statistics.median(window_ms)
+
+    # ---- strong scaling: the blocks of all ranks together must be the unsharded result
+    verified = None
+    if scaling == "strong":
+        full_tensors, _ = build_device_operands(spec, full_ops, dev)
+        whole = op_fn(*full_tensors)
+        rows_base, nnz_base, counts = oper.bases()
+        zb, n_blk, _ = oper.result()
+        lo, r0, r1 = int(nnz_base), cuts[rank], cuts[rank + 1]
+        ok = (int(rows_base) == r0 and int(counts[:, 1].sum()) == whole.values.numel()
+              and torch.equal(whole.dim_j_offsets[r0:r1 + 1], zb.dim_j_offsets + lo)
+              and torch.equal(whole.dim_j_indices[lo:lo + n_blk], zb.dim_j_indices)
+              and torch.equal(whole.values[lo:lo + n_blk].view(torch.int32), zb.values.view(torch.int32)))
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        verified = bool(int(flag[0]))
+        del full_tensors, whole
+
+    # ---- the drop-in operator (allocates its result, reads the length back) on the same operands
+    dropin_ms = None
+    if block_op:
+        for _ in range(3):
+            op_fn(*tensors)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k = max(3, min(args.steps, 20))
+        e0.record(stream)
+        for _ in range(k):
+            op_fn(*tensors)
+        e1.record(stream)
+        barrier()
+        dropin_ms = e0.elapsed_time(e1) / k
 
     # ---- per-kernel timing, same workload, events on the launching stream
     prof_steps = max(3, min(args.steps, 10))
@@ -455,6 +600,7 @@ def main():
     _capi.profile_enable(True)
     for _ in range(prof_steps):
         step()
+    finish()
     torch.cuda.synchronize()
     _capi.profile_enable(False)
     kernels = {}
@@ -504,15 +650,17 @@ def main():
 
     # ---- reduce over ranks: max time, summed bytes
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e["seconds"] if e2e else 0.0], dtype=torch.float64, device=dev)
+        t = torch.tensor([e2e["seconds"] if e2e else 0.0, dropin_ms or 0.0], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_s = float(t[0]), float(t[1])
-        b = torch.tensor([nbytes, nnz_in, launches], dtype=torch.int64, device=dev)
+        e2e_s, dropin_ms = float(t[0]), (float(t[1]) if dropin_ms is not None else None)
+        b = torch.tensor([nbytes, nnz_in, launches, rows_local, nnz_out, e2e["h2d"] if e2e else 0, e2e["d2h"] if e2e else 0],
+                         dtype=torch.int64, device=dev)
         dist.all_reduce(b, op=dist.ReduceOp.SUM)
-        total_bytes, total_nnz_in, launches = int(b[0]), int(b[1]), int(b[2])
+        total_bytes, total_nnz_in, launches, total_rows, total_nnz_out, h2d, d2h = (int(x) for x in b)
     else:
         e2e_s = e2e["seconds"] if e2e else 0.0
-        total_bytes, total_nnz_in = nbytes, nnz_in
+        total_bytes, total_nnz_in, total_rows, total_nnz_out = nbytes, nnz_in, rows_local, nnz_out
+        h2d, d2h = (e2e["h2d"], e2e["d2h"]) if e2e else (0, 0)
 
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
@@ -528,7 +676,7 @@ def main():
                 roof_bytes = bytes_csr(*metas[0]) + 8 * products + bytes_csr(*zmeta)
                 extra = {"products": products, "esc_model_bytes": roof_bytes}
             roof_ms, roof_kernel = kernels[top]["ms_per_step"], top
-            if spec["op"] in ("spgemm", "csf_add"):
+            if spec["op"] in ("spgemm", "csf_add", "csr_add_3"):
                 # several kernels share the step's bytes (row bins; expand / merge / compress):
                 # the fraction is taken over all of them, not over the longest one alone
                 roof_ms = sum(k["ms_per_step"] for k in kernels.values())
@@ -538,16 +686,17 @@ def main():
                     "frac": achieved / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth",
                     "traffic": (TRAFFIC_PER_ALGORITHMIC_BYTE[top] * roof_bytes / max(kernels[top]["launches_per_step"], 1)
                                 if top in TRAFFIC_PER_ALGORITHMIC_BYTE else None),
-                    "kernel_ms_per_step": roof_ms, "frac_of_nominal_8TBs": achieved / 8000.0}
+                    "kernel_ms_per_step": roof_ms, "frac_of_nominal_8TBs": achieved / 8000.0,
+                    "scope": "this rank's block" if world > 1 else "the whole workload"}
         base = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             scale = cpu_sample_scale(args.workload, args.cpu_scale) * args.rows_scale
             cpu_rmat = min(args.rmat_scale, 14)  # the CPU port sorts every product; keep its sample bounded
             same = scale == args.rows_scale and (args.workload != "c4a_spgemm_rmat" or cpu_rmat == args.rmat_scale)
             cpu_ops = ops if same else make_operands(args.workload, 0, dev, scale=scale, rmat_scale=cpu_rmat)
             base = cpu_baseline(args.workload, [to_oracle(spec, t) for t in cpu_ops])
-            base["sample"] = (f"{args.workload} at scale {scale:g} of its rows/entries"
-                              + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" else "")
+            base["sample"] = (("the whole workload" if same else f"{args.workload} at scale {scale:g} of its rows/entries")
+                              + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" and not same else "")
                               + ", mean of 3 runs")
         ref_gpu = None
         if world == 1 and not args.no_ref_gpu:
@@ -555,17 +704,19 @@ def main():
         line = {
             "metric": f"{spec['op']} effective HBM GB/s (operand + result bytes)",
             "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict({"workload": args.workload, "rows_scale": args.rows_scale, "rows_per_gpu": rows_local,
-                            "operand_nnz_per_gpu": nnz_in, "result_nnz_per_gpu": nnz_out,
-                            "algorithmic_bytes_per_gpu": nbytes,
-                            "l2_policy": "inputs_larger_than_L2" if nbytes > 2 * 126e6 else "inputs fit L2 (latency-bound case)",
-                            "parallelism": f"row blocks x{world}, all-gather of (rows, nnz) per step"}, **extra),
+            "config": job_config(args, world, scaling, total_rows, total_nnz_in, total_nnz_out, total_bytes, extra),
             "nnz_per_s": total_nnz_in / (ms_per_step * 1e-3),
+            "timing": {"windows": len(window_ms), "window_ms_median": elapsed_ms, "window_ms_min": min(window_ms),
+                       "window_ms_max": max(window_ms), "timed_seconds": sum(window_ms) / 1e3,
+                       "operator": ("shard.CsrRowBlockOp: nb200_csr_*_f32_async + asynchronous all-gather" if block_op
+                                    else f"nacho.gpu_{spec['op']}_f32"),
+                       "dropin_operator_ms_per_step": dropin_ms},
+            "verified_against_unsharded": verified,
             "roofline": roof, "kernels": kernels, "cpu_baseline": base, "ref_gpu_baseline": ref_gpu,
-            "e2e": ({"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e["h2d"],
-                     "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e_s * 1e3} if e2e else None),
+            "e2e": ({"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3} if e2e else None),
             "gpu_launches": launches, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -93,6 +93,26 @@ typedef struct nb200_csf3 {
     float *val;            /* values, n_k */
 } nb200_csf3;
 
+/* 2-D coordinate list: the field set of nacho's emitted COO structs (Compressed_non_unique +
+ * Singleton_unique levels, compiler.cpp:50-53): parallel row / column arrays sorted by (i, j). */
+typedef struct nb200_coo {
+    int32_t rows, cols;
+    int32_t nnz;
+    int32_t *i, *j; /* dim_{i,j}_indices, nnz entries each */
+    float *val;
+} nb200_coo;
+
+/* DCSR matrix: both levels compressed (compiler.cpp:38-42): only the rows that hold entries are
+ * stored, with their row numbers. */
+typedef struct nb200_dcsr {
+    int32_t rows, cols;
+    int32_t n_i, nnz; /* dim_i_length, dim_j_length */
+    int32_t *i_idx;   /* dim_i_indices, n_i */
+    int32_t *j_ptr;   /* dim_j_offsets, n_i + 1 */
+    int32_t *j_idx;   /* dim_j_indices, nnz */
+    float *val;       /* values, nnz */
+} nb200_dcsr;
+
 /* ---- library -------------------------------------------------------------------------- */
 
 int nb200_version(void);
@@ -246,6 +266,39 @@ int nb200_csf_add_f32(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z,
                       int32_t num_blocks, int32_t threads_per_block, void *stream);
 int nb200_csf_add_f32_into(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z,
                            int64_t cap_i, int64_t cap_j, int64_t cap_k, void *stream);
+
+/* ---- the rest of the element-wise family, and the inner products ------------------------- */
+
+/* The kernels nacho declares beside the six above over 2-D coordinate lists and doubly compressed
+ * rows (compiler.cpp:118-126) and the two full reductions (compiler.cpp:141-143), in the
+ * caller-owned-memory form only. Results are bit-identical to nacho's CPU kernels: sorted union /
+ * intersection, explicit zeros kept.
+ *   coo_add / coo_mul    Z = A (+|.*) B over sorted unique (i, j) lists; `capacity` entries in
+ *                        z->i / z->j / z->val (always enough: nnz(A)+nnz(B), min(nnz(A), nnz(B))).
+ *   coo_csr_add          Z = A + B with A in CSR and B a coordinate list; Z in CSR.
+ *   dcsr_add / dcsr_mul  DCSR operands and result. `cap_i` entries in z->i_idx (z->j_ptr one more)
+ *                        must cover the worst case, min(n_i(A)+n_i(B), rows) for the sum and
+ *                        min(n_i(A), n_i(B)) for the product; `capacity` as for CSR. The product
+ *                        keeps every row that BOTH operands store, with an empty column range where
+ *                        their columns do not meet, as nacho's level-by-level intersection does.
+ * These run the CSR merge kernels on the operands' own column / value arrays after rebuilding the
+ * row offsets, so they need scratch of a few int32 per matrix ROW (not per stored row). */
+int nb200_coo_add_f32_into(const nb200_coo *a, const nb200_coo *b, nb200_coo *z, int64_t capacity, void *stream);
+int nb200_coo_mul_f32_into(const nb200_coo *a, const nb200_coo *b, nb200_coo *z, int64_t capacity, void *stream);
+int nb200_coo_csr_add_f32_into(const nb200_csr *a, const nb200_coo *b, nb200_csr *z, int64_t capacity, void *stream);
+int nb200_dcsr_add_f32_into(const nb200_dcsr *a, const nb200_dcsr *b, nb200_dcsr *z, int64_t cap_i, int64_t capacity,
+                            void *stream);
+int nb200_dcsr_mul_f32_into(const nb200_dcsr *a, const nb200_dcsr *b, nb200_dcsr *z, int64_t cap_i, int64_t capacity,
+                            void *stream);
+
+/* z[0] = sum over the coordinates both tensors hold of a * b, one float32 in DEVICE memory (nacho
+ * returns a one-element tensor). Replaces inner_prod::inner_prod_gpu_i32_f32 (CSF3 operands) and
+ * inner_prod_coo::inner_prod_coo_gpu_i32_f32 (COO3 operands); append-reduction
+ * src/backend/compute.cpp:498-525. Each product is a float32 multiply as in nacho; the products
+ * are summed in double and rounded once, where nacho adds float32 atomically in arrival order, so
+ * the two agree to float32 rounding of the sum, not bit for bit. Extents must pack into 63 bits. */
+int nb200_inner_prod_f32(const nb200_csf3 *a, const nb200_csf3 *b, float *z, void *stream);
+int nb200_inner_prod_coo_f32(const nb200_coo3 *a, const nb200_coo3 *b, float *z, void *stream);
 
 /* ---- self-test -------------------------------------------------------------------------- */
 

@@ -35,6 +35,18 @@ class Csf3Struct(C.Structure):
                 ("k_ptr", C.c_void_p), ("k_idx", C.c_void_p), ("val", C.c_void_p)]
 
 
+class CooStruct(C.Structure):
+    """``nb200_coo``."""
+    _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("nnz", C.c_int32),
+                ("i", C.c_void_p), ("j", C.c_void_p), ("val", C.c_void_p)]
+
+
+class DcsrStruct(C.Structure):
+    """``nb200_dcsr``."""
+    _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("n_i", C.c_int32), ("nnz", C.c_int32),
+                ("i_idx", C.c_void_p), ("j_ptr", C.c_void_p), ("j_idx", C.c_void_p), ("val", C.c_void_p)]
+
+
 OK, E_BADARG, E_CUDA, E_OVERFLOW, E_CAPACITY, E_TIMEOUT, E_NOMEM, E_UNSUPPORTED = range(8)
 
 # name -> (restype, argtypes); every symbol include/nacho_b200.h declares.
@@ -69,6 +81,13 @@ PROTOTYPES = {
     "nb200_coo3d_add_f32_into": (C.c_int, [_P(Coo3Struct)] * 3 + [C.c_int64, C.c_void_p]),
     "nb200_csf_add_f32": (C.c_int, [_P(Csf3Struct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),
     "nb200_csf_add_f32_into": (C.c_int, [_P(Csf3Struct)] * 3 + [C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "nb200_coo_add_f32_into": (C.c_int, [_P(CooStruct)] * 3 + [C.c_int64, C.c_void_p]),
+    "nb200_coo_mul_f32_into": (C.c_int, [_P(CooStruct)] * 3 + [C.c_int64, C.c_void_p]),
+    "nb200_coo_csr_add_f32_into": (C.c_int, [_P(CsrStruct), _P(CooStruct), _P(CsrStruct), C.c_int64, C.c_void_p]),
+    "nb200_dcsr_add_f32_into": (C.c_int, [_P(DcsrStruct)] * 3 + [C.c_int64, C.c_int64, C.c_void_p]),
+    "nb200_dcsr_mul_f32_into": (C.c_int, [_P(DcsrStruct)] * 3 + [C.c_int64, C.c_int64, C.c_void_p]),
+    "nb200_inner_prod_f32": (C.c_int, [_P(Csf3Struct)] * 2 + [C.c_void_p, C.c_void_p]),
+    "nb200_inner_prod_coo_f32": (C.c_int, [_P(Coo3Struct)] * 2 + [C.c_void_p, C.c_void_p]),
 }
 
 

@@ -372,6 +372,33 @@ __global__ void __launch_bounds__(NT + 32, COO3_MIN_CTAS) k_coo3_tile(Coo3In A, 
         }
     }
 
+    if (MODE == MODE_REDUCE) {
+        // ---- inner product: sum a * b over the coordinates both operands hold, in double; one
+        // atomic per tile into the control block (the order of the tiles' sums is not fixed, as
+        // with the reference's atomic accumulation, src/backend/compute.cpp:498-525)
+        double sum = 0.0;
+        int xi = x0, yi = y0;
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = (from_a >> i) & 1u;
+            if ((twin >> i) & 1u && i < min(VT, n - diag)) sum += (double)(vx[xi] * vy[yi]);
+            xi += tx;
+            yi += !tx;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(FULL_MASK, sum, o);
+        double *partial = reinterpret_cast<double *>(scan_tmp);  // 72 ints = room for 8 doubles and more
+        WorkerBar::sync();
+        if (lane_id() == 0) partial[warp_id()] = sum;
+        WorkerBar::sync();
+        if (tid == 0) {
+            double s = 0.0;
+            for (int w = 0; w < NT / 32; ++w) s += partial[w];
+            atomicAdd(reinterpret_cast<double *>(&ctl->total), s);
+        }
+        return;
+    }
+
     // ---- rank the survivors inside the tile
     int total;
     const int mine = __popc(emit);
@@ -647,7 +674,7 @@ cudaError_t launch_coo3_tile(const Coo3In &A, const Coo3In &B, const Packing &pk
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    static const char *const names[3] = {"coo3_add_count", "coo3_add_fill", "coo3_add_fused"};
+    static const char *const names[4] = {"coo3_add_count", "coo3_add_fill", "coo3_add_fused", "coo3_inner_prod"};
     LaunchScope scope(CSF_OUT ? "coo3_add_fused_csf" : names[MODE], stream);
     kernel<<<num_tiles, NT + 32, coo3_smem_bytes(), stream>>>(A, B, pk, cuts, tile_count, tile_state, ctl, Z, csf);
     return cudaGetLastError();
@@ -819,6 +846,66 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     return NB200_OK;
 }
 
+__global__ void k_store_scalar(const FusedCtl *ctl, float *out) {
+    out[0] = (float)__longlong_as_double(ctl->total);
+}
+
+// Inner product of two COO3 tensors: sum over the coordinates both hold of a * b, written as one
+// float32 to the device word `z` (the reference returns a one-element tensor: compiler.cpp:141-143,
+// append-reduction src/backend/compute.cpp:498-525). The same partition and tile kernel as the add,
+// in a mode that writes no tensor. Products are float32 (as the reference's), their sum is kept in
+// double until the end. Extents that do not pack into 64 bits are not supported here.
+// `scratch` / `host_slot` as for coo3_add_run.
+int coo3_inner_run(const nb200_coo3 *a, const nb200_coo3 *b, float *z, void *stream_v, void *scratch, int64_t *host_slot) {
+    int st;
+    if ((st = check_coo3(a)) || (st = check_coo3(b))) return st;
+    if (!z || a->dims[0] != b->dims[0] || a->dims[1] != b->dims[1] || a->dims[2] != b->dims[2]) return NB200_E_BADARG;
+    const int bi = bits_for(a->dims[0]), bj = bits_for(a->dims[1]), bk = bits_for(a->dims[2]);
+    if (bi + bj + bk > 63) return NB200_E_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int64_t total = (int64_t)a->nnz + b->nnz;
+    constexpr int tile_step = CAP - 1;
+    const int64_t tiles64 = (total + tile_step - 1) / tile_step;
+    if (tiles64 > INT32_MAX - 1) return NB200_E_OVERFLOW;
+    const int num_tiles = (int)tiles64;
+    if (a->nnz == 0 || b->nnz == 0) {
+        NB200_CUDA(cudaMemsetAsync(z, 0, sizeof(float), stream));
+        return NB200_OK;
+    }
+    if (!scratch) {
+        Workspace *ws = nullptr;
+        if ((st = acquire_workspace(stream, coo3_add_scratch_bytes(total), &ws))) return st;
+        scratch = ws->dev;
+        host_slot = ws->host;
+    }
+    Carver carve(scratch);
+    Cuts2 cuts;
+    cuts.a = carve.take<int32_t>((size_t)num_tiles + 1);
+    cuts.b = carve.take<int32_t>((size_t)num_tiles + 1);
+    carve.take<int32_t>((size_t)num_tiles + 1);
+    carve.take<int64_t>(1);
+    FusedCtl *ctl = reinterpret_cast<FusedCtl *>(carve.take<uint64_t>((size_t)num_tiles + 8));
+    const Coo3In A{a->i, a->j, a->k, a->val, a->nnz}, B{b->i, b->j, b->k, b->val, b->nnz};
+    const Packing pk{bj, bk};
+    NB200_CUDA(cudaMemsetAsync(ctl, 0, 4 * sizeof(uint64_t), stream));
+    {
+        LaunchScope scope("coo3_partition", stream);
+        const int warps = num_tiles / COARSE + 2;
+        k_coo3_partition_coarse<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        k_coo3_partition_fine<<<(num_tiles + NT - 1) / NT, NT, 0, stream>>>(A, B, pk, total, tile_step, num_tiles, cuts);
+        NB200_CUDA(cudaGetLastError());
+    }
+    cudaError_t e = launch_coo3_tile<MODE_REDUCE>(A, B, pk, cuts, nullptr, nullptr, ctl, Coo3Out{}, num_tiles, stream);
+    if (e != cudaSuccess) return note_cuda_error(e, "k_coo3_tile<reduce>");
+    k_store_scalar<<<1, 1, 0, stream>>>(ctl, z);
+    NB200_CUDA(cudaGetLastError());
+    NB200_CUDA(cudaMemcpyAsync(host_slot, ctl, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaStreamSynchronize(stream));
+    FusedCtl h;
+    std::memcpy(&h, host_slot, sizeof(h));
+    return h.status.error != 0 ? NB200_E_TIMEOUT : NB200_OK;
+}
+
 }  // namespace nb200
 
 using namespace nb200;
@@ -831,6 +918,10 @@ int nb200_coo3d_add_f32(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z,
 
 int nb200_coo3d_add_f32_into(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, int64_t capacity, void *stream) {
     return coo3_add_run(a, b, z, false, capacity, stream, nullptr, nullptr, nullptr, nullptr);
+}
+
+int nb200_inner_prod_coo_f32(const nb200_coo3 *a, const nb200_coo3 *b, float *z, void *stream) {
+    return coo3_inner_run(a, b, z, stream, nullptr, nullptr);
 }
 
 }  // extern "C"

@@ -24,6 +24,7 @@ namespace nb200 {
 
 int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool alloc, int64_t capacity, void *stream_v,
                  void *scratch, int64_t *host_slot, const CsfLevelsOut *csf, bool *csf_done);
+int coo3_inner_run(const nb200_coo3 *a, const nb200_coo3 *b, float *z, void *stream_v, void *scratch, int64_t *host_slot);
 size_t coo3_add_scratch_bytes(int64_t total_entries);
 int64_t coo3_add_tiles(int64_t total_entries);
 
@@ -333,6 +334,46 @@ int csf_add_run(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, bool al
     return NB200_OK;
 }
 
+// Inner product of two CSF3 tensors (compiler.cpp:141): every entry gets its (i, j) written out
+// next to its k (k_csf_expand), then the coordinate lists go through the inner-product mode of the
+// COO3 tile kernel.
+int csf_inner_run(const nb200_csf3 *a, const nb200_csf3 *b, float *z, void *stream_v) {
+    int st;
+    if ((st = check_csf3(a)) || (st = check_csf3(b))) return st;
+    if (!z || a->dims[0] != b->dims[0] || a->dims[1] != b->dims[1] || a->dims[2] != b->dims[2]) return NB200_E_BADARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (a->n_k == 0 || b->n_k == 0) {
+        NB200_CUDA(cudaMemsetAsync(z, 0, sizeof(float), stream));
+        return NB200_OK;
+    }
+    const int64_t total = (int64_t)a->n_k + b->n_k;
+    if (total > INT32_MAX) return NB200_E_OVERFLOW;
+    Carver sizes;
+    sizes.take<int32_t>((size_t)a->n_k);
+    sizes.take<int32_t>((size_t)a->n_k);
+    sizes.take<int32_t>((size_t)b->n_k);
+    sizes.take<int32_t>((size_t)b->n_k);
+    const size_t own = sizes.used();
+    Workspace *ws = nullptr;
+    if ((st = acquire_workspace(stream, own + coo3_add_scratch_bytes(total) + 256, &ws))) return st;
+    Carver carve(ws->dev);
+    int32_t *ai = carve.take<int32_t>((size_t)a->n_k), *aj = carve.take<int32_t>((size_t)a->n_k);
+    int32_t *bi = carve.take<int32_t>((size_t)b->n_k), *bj = carve.take<int32_t>((size_t)b->n_k);
+    void *merge_scratch = static_cast<unsigned char *>(ws->dev) + own;
+    {
+        LaunchScope scope("csf_expand", stream);
+        k_csf_expand<<<(int)(((int64_t)a->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
+    }
+    {
+        LaunchScope scope("csf_expand", stream);
+        k_csf_expand<<<(int)(((int64_t)b->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
+    }
+    NB200_CUDA(cudaGetLastError());
+    nb200_coo3 ca{{a->dims[0], a->dims[1], a->dims[2]}, a->n_k, ai, aj, a->k_idx, a->val};
+    nb200_coo3 cb{{b->dims[0], b->dims[1], b->dims[2]}, b->n_k, bi, bj, b->k_idx, b->val};
+    return coo3_inner_run(&ca, &cb, z, stream_v, merge_scratch, ws->host);
+}
+
 }  // namespace
 
 }  // namespace nb200
@@ -348,6 +389,10 @@ int nb200_csf_add_f32(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
 int nb200_csf_add_f32_into(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, int64_t cap_i, int64_t cap_j,
                            int64_t cap_k, void *stream) {
     return csf_add_run(a, b, z, false, cap_i, cap_j, cap_k, stream);
+}
+
+int nb200_inner_prod_f32(const nb200_csf3 *a, const nb200_csf3 *b, float *z, void *stream) {
+    return csf_inner_run(a, b, z, stream);
 }
 
 }  // extern "C"

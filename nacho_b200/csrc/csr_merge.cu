@@ -31,11 +31,15 @@ namespace nb200 {
 
 namespace {
 
-// Tuning knobs (compile-time): register slots per lane of a worker warp (a warp merges up to
-// 32 * V entries at a time), and the number of CTAs per SM the register allocator is asked to
-// leave room for. The CTA always has 256 worker threads and one scan warp.
+// Tuning knobs (compile-time): which of the two tile bodies runs, its entries per thread (or
+// register slots per lane of a worker warp: a warp merges up to 32 * V entries at a time), and
+// the number of CTAs per SM the register allocator is asked to leave room for. The CTA always has
+// 256 worker threads and one scan warp.
+#ifndef CSR2_BODY
+#define CSR2_BODY 0          // 0: thread-blocked tile body (VT entries per thread), 1: warp-striped body (V slots per lane)
+#endif
 #ifndef CSR2_V
-#define CSR2_V 20
+#define CSR2_V (CSR2_BODY == 0 ? 19 : 16)
 #endif
 #ifndef CSR2_LB_DEPTH
 #define CSR2_LB_DEPTH 1      // predecessors read per round of the look-back, in units of 32
@@ -154,10 +158,20 @@ struct WarpPlan {
     static_assert(V <= 32, "slot masks are 32 bits wide");
 };
 
+// The plan of the body that is compiled in.
+template <int V>
+struct TilePlan {
+#if CSR2_BODY == 0
+    static constexpr int TILE_STEP = NT * V - 1, CAP = NT * V;
+#else
+    static constexpr int TILE_STEP = WarpPlan<V>::TILE_STEP, CAP = WarpPlan<V>::CAP;
+#endif
+};
+
 // Merged entries per thread of the wide-key body, so that its CTA covers a whole tile.
 template <int V>
 struct WideVt {
-    static constexpr int value = (WarpPlan<V>::CAP + NT - 1) / NT;
+    static constexpr int value = (TilePlan<V>::CAP + NT - 1) / NT;
 };
 
 // Tiles whose rows do not fit a 32-bit composite key (long runs of empty rows) take this body:
@@ -351,7 +365,356 @@ __device__ __forceinline__ int head_elems(const void *p) {
     return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
 }
 
-// The common tile body. Keys are 32-bit composites (row in tile, column, operand bit):
+// Shared-memory plan of the thread-blocked tile body, in 4-byte words. Keys and values use the
+// same word positions: A's entry e sits at word oa + e and B's at word obv + e, where oa and obv
+// are chosen so that a global address on a 16-byte boundary lands on a 16-byte boundary in
+// shared memory too (what a bulk copy needs). The (column, value) staging pairs of the result reuse
+// the key words (the keys live in registers by then) and run on into extra words.
+template <int VT>
+struct BlockedPlan {
+    static constexpr int CAP = NT * VT;
+    static constexpr int NETV = VT + 1;                          // merge-network slots in use
+    static constexpr int CH = (VT + 1 + 3) & ~3;                 // words each thread scans
+    static constexpr int SLOTS = NT * CH + ((NETV + 4 + 3) & ~3);  // key words = value words
+    static constexpr int OUT = CAP + 8;                          // staging words per array
+    static constexpr size_t BYTES = 4 * (size_t)(2 * SLOTS + OUT);
+    // A thread's CH-word chunk is read and written as 16-byte vectors; an odd number of
+    // vectors per chunk keeps those accesses free of shared-memory bank conflicts.
+    static_assert((CH / 4) % 2 == 1, "choose VT so that (VT + 1) rounded up to 4 is an odd multiple of 4");
+    static_assert(NT * CH >= CAP + 12, "scan range must cover the padded tile");
+    static_assert(OUT <= SLOTS, "column staging must fit the key words it reuses");
+};
+
+// The common tile body, thread-blocked form. Keys are 32-bit composites (row in tile, column, operand bit):
+//     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
+// so that one unsigned compare orders entries by (row, column) with A first on ties, and
+// two entries are the same position exactly when their keys differ in the last bit only.
+//
+// The CTA has NT worker threads and one more warp, the scan warp. Workers stage the operands
+// with bulk copies, build keys (row marks, then a running maximum that every warp runs over its
+// own words), split the tile by merge-path, merge VT entries each in registers with a bitonic
+// network, rank the survivors (warp scans, one barrier) and compact them into shared memory. In
+// the single-pass mode the scan warp meanwhile turns the tile's count into its output base by
+// look-back over earlier tiles, so that this wait overlaps the workers' compaction. Six CTA-wide
+// barriers per tile.
+template <int VT, int OP, int MODE>
+__device__ __forceinline__ void csr2_tile_blocked(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits, const int t,
+                                                  const int num_tiles, int32_t *tile_count, volatile uint64_t *tile_state,
+                                                  FusedCtl *ctl, const CsrOut &Z, unsigned char *smem_raw, uint64_t *mbar,
+                                                  const int poll_limit) {
+    using P = BlockedPlan<VT>;
+    constexpr int W = NT / 32;
+    __shared__ int thread_rank[NT];
+    __shared__ unsigned thread_emit[NT];
+    __shared__ int s_wtotal[W];  // survivors of each warp
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr int NETV = P::NETV;
+    constexpr bool WRITES = MODE != MODE_COUNT;
+    constexpr uint32_t INF = 0xffffffffu;
+    __shared__ long long s_base;
+    __shared__ int s_total;
+    __shared__ int s_hurry;  // set once the tile's count is out: from then on the tile waits for its base
+    const int tid = threadIdx.x;
+    const bool scan_warp = tid >= NT;
+    const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
+    const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
+    const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
+    const int n = na + nb;
+    const uint32_t cmask = (1u << cbits) - 1u;
+
+    // layout: values | keys | extra words. The (column, value) staging pairs of the result
+    // reuse the keys (in registers by then) and run on into the extra words.
+    float *vals = reinterpret_cast<float *>(smem_raw);
+    uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw) + P::SLOTS;
+    uint2 *out_pair = reinterpret_cast<uint2 *>(keys);
+    static_assert(P::SLOTS % 2 == 0 && P::SLOTS + P::OUT >= 2 * P::OUT, "staging pairs must fit keys + extra words, 8-byte aligned");
+
+    const int32_t *ga_col = A.col + a0, *gb_col = B.col + b0;
+    const float *ga_val = A.val + a0, *gb_val = B.val + b0;
+    const int ha = head_elems(ga_col), hb = head_elems(gb_col);
+    const int oa = (4 - ha) & 3;                 // word of A's entry 0
+    const int ob = (oa + na + 1 + 3) & ~3;       // first word of B's region (A's sentinel before it)
+    const int obv = ob + ((4 - hb) & 3);         // word of B's entry 0
+    const int scan_end = (obv + nb + 3) & ~3;
+    uint32_t *kx = keys + oa, *ky = keys + obv;
+
+    // ---- stage the tile. One thread hands the 16-byte-aligned interior of each array to the
+    // copy engine; a few other threads load the ragged ends (at most 3 entries each side).
+    // Value arrays whose alignment differs from their column arrays' take plain loads.
+    const bool va_bulk = !WRITES || head_elems(ga_val) == ha, vb_bulk = !WRITES || head_elems(gb_val) == hb;
+    const int head_a = min(na, ha), head_b = min(nb, hb);
+    const int nva = (na - head_a) >> 2, nvb = (nb - head_b) >> 2;  // 16-byte vectors in the interior
+    if (tid == 0) {
+        s_hurry = 0;
+        uint32_t bytes = 16u * (uint32_t)(nva + nvb);
+        if (WRITES) bytes += (va_bulk ? 16u * nva : 0u) + (vb_bulk ? 16u * nvb : 0u);
+        mbar_arrive_expect_tx(mbar, bytes);
+        if (nva) bulk_load(kx + head_a, ga_col + head_a, 16u * nva, mbar);
+        if (nvb) bulk_load(ky + head_b, gb_col + head_b, 16u * nvb, mbar);
+        if (WRITES && va_bulk && nva) bulk_load(vals + oa + head_a, ga_val + head_a, 16u * nva, mbar);
+        if (WRITES && vb_bulk && nvb) bulk_load(vals + obv + head_b, gb_val + head_b, 16u * nvb, mbar);
+    }
+    if (tid >= 32 && tid < 32 + 12) {  // ragged ends: 3 head + 3 tail slots for A, then for B
+        const int k = tid - 32;
+        const bool is_b = k >= 6;
+        const int e = is_b ? k - 6 : k;
+        const int count = is_b ? nb : na, head = is_b ? head_b : head_a, nv = is_b ? nvb : nva;
+        const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
+        const bool live = e < 3 ? e < head : idx < count;
+        if (live) {
+            const int w = (is_b ? obv : oa) + idx;
+            keys[w] = (uint32_t)ld_nc((is_b ? gb_col : ga_col) + idx);
+            if (WRITES && (is_b ? vb_bulk : va_bulk)) vals[w] = ld_nc((is_b ? gb_val : ga_val) + idx);
+        }
+    }
+    if (WRITES && !va_bulk && !scan_warp) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
+    if (WRITES && !vb_bulk && !scan_warp) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
+    // padding words that precede live keys must read as "no row mark"; the end-of-list
+    // sentinels are all-ones, which the row spreading below keeps above every live key
+    if (tid >= 64 && tid < 64 + 3) { if (tid - 64 < oa) keys[tid - 64] = 0u; }
+    if (tid >= 68 && tid < 68 + 3) { if (ob + (tid - 68) < obv) keys[ob + (tid - 68)] = 0u; }
+    if (tid == 72) keys[oa + na] = INF;
+    if (tid >= 76 && tid < 76 + NETV + 1) keys[obv + nb + (tid - 76)] = INF;
+    static_assert(76 + NETV + 1 <= NT, "sentinel writers must be worker threads");
+
+    // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over the
+    // workers); kept in registers for the row-offset pass at the end
+    const int64_t my_row = (int64_t)i0 + 1 + tid;
+    int32_t my_sa = 0, my_sb = 0;
+    if (!scan_warp && my_row <= i1) {
+        my_sa = ld_nc(A.rp + my_row) - a0;
+        my_sb = ld_nc(B.rp + my_row) - b0;
+    }
+    // ---- the row (relative to i0) that the first key word of this warp's scan region belongs to:
+    // the last row that starts at or before it. Regions that begin with an operand's first entry,
+    // or in padding before it, start from row 0 of the tile. (Found while the copies fly.)
+    const int w0 = wid * 32 * P::CH;
+    const bool region_in_a = w0 < ob;
+    unsigned carry = 0;
+    if (!scan_warp) {
+        const int pos = region_in_a ? w0 - oa : w0 - obv;
+        if (pos > 0 && i1 > i0) {
+            const int32_t *rp = region_in_a ? A.rp : B.rp;
+            const int32_t start = region_in_a ? a0 : b0;
+            carry = (unsigned)(warp_last_true(i0, i1, [&](int64_t r) { return ld_nc(rp + r) - start <= pos; }) - i0);
+        }
+    }
+    const bool landed = mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);
+    if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
+        if (tid == 0) {
+            if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
+            if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;  // successors must not wait on this tile
+            mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
+        }
+        return;
+    }
+
+    if (scan_warp) {
+        // ---- scan warp: the output base of the tile is the sum of the counts of all earlier
+        // tiles, which does not depend on this tile's own count. So the walk over the
+        // predecessors' words starts now, while the workers are still merging, and is usually
+        // over by the time they know their count.
+        if (MODE != MODE_FUSED) return;
+        const int64_t bse = t == 0 ? 0 : lookback_predecessors<CSR2_LB_DEPTH>(tile_state, t, &ctl->status, CSR2_LB_SLEEP, &s_hurry,
+                                                                             CSR2_LB_HURRY, poll_limit);
+        CountBar::sync();  // the workers have published the tile's count by now
+        const int total = s_total;
+        if (lane_id() == 0) {
+            if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
+            s_base = bse;
+            if (bse >= 0 && t == num_tiles - 1) ctl->total = bse + total;
+        }
+        __syncthreads();
+        return;
+    }
+
+    // ---- mark the first entry of every row that starts inside the tile with its row number
+    // relative to i0, in the bits above the column (max wins where empty rows share a start)
+    for (int64_t r = my_row; r <= i1; r += NT) {
+        const uint32_t rr = (uint32_t)(r - i0);
+        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
+        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
+        if (sa < na) atomicMax(kx + sa, (rr << cbits) | (kx[sa] & cmask));
+        if (sb < nb) atomicMax(ky + sb, (rr << cbits) | (ky[sb] & cmask));
+    }
+    WorkerBar::sync();
+
+    // ---- spread the marks forward (running maximum) so that every key carries its row, and
+    // append the operand bit. Each thread owns CH consecutive words, each warp 32 * CH, and a warp
+    // needs nothing from the other warps (its region's first row came from the search above); A's
+    // words and B's words run separately.
+    {
+        constexpr int NV = P::CH / 4;
+        const int w_base = tid * P::CH;
+        uint4 q[NV];
+        unsigned ma = 0, mb = 0;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int w = w_base + 4 * j;
+            q[j] = w < scan_end ? *reinterpret_cast<const uint4 *>(keys + w) : make_uint4(0, 0, 0, 0);
+            const unsigned m = max(max(q[j].x & ~cmask, q[j].y & ~cmask), max(q[j].z & ~cmask, q[j].w & ~cmask));
+            if (w < ob) ma = max(ma, m); else mb = max(mb, m);
+        }
+        // running maximum over the lanes before this one, on top of the row the warp's region starts in
+        unsigned ea = __shfl_up_sync(FULL_MASK, warp_incl_max(ma), 1), eb = __shfl_up_sync(FULL_MASK, warp_incl_max(mb), 1);
+        if (lane == 0) ea = eb = 0u;
+        if (region_in_a) ea = max(ea, carry << cbits); else eb = max(eb, carry << cbits);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int w = w_base + 4 * j;
+            const bool in_a = w < ob;
+            const unsigned src = in_a ? 0u : 1u;
+            unsigned run = in_a ? ea : eb;
+            uint4 v = q[j];
+            run = max(run, v.x & ~cmask); v.x = ((run | (v.x & cmask)) << 1) | src;
+            run = max(run, v.y & ~cmask); v.y = ((run | (v.y & cmask)) << 1) | src;
+            run = max(run, v.z & ~cmask); v.z = ((run | (v.z & cmask)) << 1) | src;
+            run = max(run, v.w & ~cmask); v.w = ((run | (v.w & cmask)) << 1) | src;
+            if (in_a) ea = run; else eb = run;
+            if (w < scan_end) *reinterpret_cast<uint4 *>(keys + w) = v;
+        }
+    }
+    WorkerBar::sync();
+
+    // ---- split the tile among threads: merge-path diagonal tid * VT (the operand bit makes
+    // an A entry smaller than the B entry at the same position, so ties take A first)
+    const int diag = min(tid * VT, n);
+    int x0;
+    {
+        int lo = max(0, diag - nb), hi = min(diag, na);
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (kx[mid] < ky[diag - 1 - mid]) lo = mid + 1; else hi = mid;
+        }
+        x0 = lo;
+    }
+    const int y0 = diag - x0;
+    const int cnt = min(VT, n - diag);
+    // the next thread's split: from the next lane; the warp's last lane takes the split of the
+    // warp's end diagonal, which the 32 lanes find together
+    int x1 = __shfl_down_sync(FULL_MASK, x0, 1);
+    {
+        const int x_end = warp_count_cut(kx, na, ky, nb, min((wid + 1) * 32 * VT, n));
+        if (lane == 31) x1 = x_end;
+    }
+    const int a = min(x1, x0 + cnt) - x0, b = cnt - a;
+
+    // ---- merge in registers: A's entries ascending, the successor of the thread's range, an
+    // all-ones plateau, B's entries descending -- a bitonic sequence -- through a merge network
+    uint32_t r[NETV];
+    {
+        const uint32_t succ = min(kx[x0 + a], ky[y0 + b]);  // next merged key after this thread's range
+#pragma unroll
+        for (int i = 0; i < NETV; ++i) {
+            const bool is_a = i < a, is_b = i >= NETV - b;
+            const uint32_t *p = is_a ? kx + x0 + i : ky + y0 + (NETV - 1 - i);
+            const uint32_t v = *p;  // stays inside the slack-padded key array either way
+            r[i] = (is_a || is_b) ? v : (i == a ? succ : INF);
+        }
+    }
+    const uint32_t prev_a = x0 > 0 ? kx[x0 - 1] : 0u;  // only an A entry can pair with a B entry
+    bitonic_merge<NETV>(r);
+
+    // Bit i of `from_a`: entry i came from A; of `same`: entries i and i+1 are one position (an A
+    // entry and its B twin); of `emit`: entry i goes to the result.
+    unsigned from_a = 0, same = 0;
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+        from_a |= (~r[i] & 1u) << i;
+        same |= (unsigned)((r[i] ^ r[i + 1]) == 1u) << i;
+    }
+    const unsigned live = (1u << cnt) - 1u;
+    const unsigned dup = (same << 1) | (unsigned)(x0 > 0 && (prev_a ^ r[0]) == 1u);  // B entries whose A twin precedes them
+    const unsigned twin = same & from_a & live;
+    const unsigned emit = OP == OP_UNION ? (live & ~dup) : twin;
+    static_assert(VT < 32, "entry masks are 32 bits wide");
+
+    // ---- rank the survivors inside the tile
+    const int mine = __popc(emit);
+    const int incl = warp_incl_sum(mine);
+    if (lane == 31) s_wtotal[wid] = incl;
+    WorkerBar::sync();  // also retires every thread's key reads: the staging pairs may overwrite the keys
+    int total = 0, wbase = 0;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+        const int c = s_wtotal[w];
+        wbase += w < wid ? c : 0;
+        total += c;
+    }
+    const int rank = wbase + incl - mine;
+    if (MODE == MODE_COUNT) {
+        if (tid == 0) tile_count[t] = total;
+        return;
+    }
+    thread_rank[tid] = rank;
+    thread_emit[tid] = emit;
+    if (MODE == MODE_FUSED) {
+        if (tid == 0) {
+            // successors can add this tile's count from here on
+            st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
+            s_total = total;
+            *(volatile int *)&s_hurry = 1;
+        }
+        __threadfence_block();
+        CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
+    }
+
+    // ---- compact (column, value) pairs of the survivors into the staging array. Entry i of the
+    // thread came from A iff its key's operand bit is clear; its value sits at A's start + (A
+    // entries before it) or B's start + (B entries before it), and an A entry's twin is the
+    // next B entry.
+    {
+        const float *pa = vals + oa + x0, *pb = vals + obv + y0;
+        uint2 *po = out_pair + rank;
+        int ca = 0;  // A entries among the thread's first i entries
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            const bool tx = (r[i] & 1u) == 0u;
+            if (OP == OP_UNION) {
+                float v = *(tx ? pa + ca : pb + (i - ca));
+                if ((twin >> i) & 1u) v = v + pb[i - ca];  // an A entry whose twin is the next B entry
+                if ((emit >> i) & 1u) {
+                    *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(v));
+                    ++po;
+                }
+            } else if ((emit >> i) & 1u) {  // intersection: only the twins need their values
+                *po = make_uint2((r[i] >> 1) & cmask, __float_as_uint(pa[ca] * pb[i - ca]));
+                ++po;
+            }
+            ca += tx;
+        }
+    }
+
+    // ---- output base of the tile
+    if (MODE == MODE_FUSED) __syncthreads(); else WorkerBar::sync();
+    const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
+    if (base < 0) return;  // a bounded wait gave up; the host reports it
+
+    // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
+    // tile those are the survivors among the first d = (A entries before row r) + (B entries
+    // before row r) merged entries, read off the per-thread ranks. The tile owns rows
+    // i0+1 .. i1 (the next tile's first row).
+    for (int64_t rw = my_row; rw <= i1; rw += NT) {
+        const int sa = rw == my_row ? my_sa : ld_nc(A.rp + rw) - a0;
+        const int sb = rw == my_row ? my_sb : ld_nc(B.rp + rw) - b0;
+        const int d = sa + sb;
+        const int owner = d / VT, off = d - owner * VT;
+        const int before = owner >= NT ? total : thread_rank[owner] + __popc(thread_emit[owner] & ((1u << off) - 1u));
+        Z.rp[rw] = (int32_t)(base + before);
+    }
+    if (t == 0 && tid == 0) Z.rp[0] = 0;
+
+    // ---- store the compacted tile, coalesced
+    int32_t *gz_col = Z.col + base;
+    float *gz_val = Z.val + base;
+    for (int i = tid; i < total; i += NT) {
+        const uint2 p = out_pair[i];
+        gz_col[i] = (int32_t)p.x;
+        gz_val[i] = __uint_as_float(p.y);
+    }
+}
+
+// The common tile body, warp-striped form. Keys are 32-bit composites (row in tile, column, operand bit):
 //     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
 // so that one unsigned compare orders entries by (row, column) with A first on ties, and
 // two entries are the same position exactly when their keys differ in the last bit only.
@@ -709,7 +1072,11 @@ __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __gr
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
     const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
     if (narrow) {
+#if CSR2_BODY == 0
+        csr2_tile_blocked<V, OP, MODE>(A, B, cuts, cbits, t, num_tiles, tile_count, tile_state, ctl, Z, smem_raw, &mbar, poll_limit);
+#else
         csr2_tile_warp<V, OP, MODE>(A, B, cuts, cbits, t, num_tiles, tile_count, tile_state, ctl, Z, smem_raw, &mbar, poll_limit);
+#endif
     } else {
         if (threadIdx.x >= NT) return;  // the wide-key body works with the NT worker threads alone
         csr2_tile_wide<WideVt<V>::value, OP, MODE>(A, B, cuts, t, tile_count, tile_state, ctl, Z, smem_raw, num_tiles, poll_limit);
@@ -719,12 +1086,17 @@ __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __gr
 // ------------------------------------------------------------------------ host driver ----
 
 constexpr int V_CSR2 = CSR2_V;
-constexpr int TILE_STEP = WarpPlan<V_CSR2>::TILE_STEP;
+constexpr int TILE_STEP = TilePlan<V_CSR2>::TILE_STEP;
 
 // Dynamic shared memory of the tile kernel: the staging arrays of the common body, or the 64-bit
 // keys of the wide-key body, whichever is larger.
 constexpr size_t csr2_smem_bytes() {
-    return std::max<size_t>(WarpPlan<V_CSR2>::BYTES, 8 * (size_t)(NT * WideVt<V_CSR2>::value + 2 + WideVt<V_CSR2>::value));
+#if CSR2_BODY == 0
+    constexpr size_t body = BlockedPlan<V_CSR2>::BYTES;
+#else
+    constexpr size_t body = WarpPlan<V_CSR2>::BYTES;
+#endif
+    return std::max<size_t>(body, 8 * (size_t)(NT * WideVt<V_CSR2>::value + 2 + WideVt<V_CSR2>::value));
 }
 
 int col_bits(int32_t cols) {

@@ -14,13 +14,15 @@ enum SetOp { OP_UNION = 0, OP_INTERSECT = 1 };
 //   MODE_COUNT  count the tile's result entries (first pass of the two-pass scheme)
 //   MODE_FILL   write the result; the tile's output base comes from the scanned counts
 //   MODE_FUSED  single pass: count, obtain the base by look-back over earlier tiles, write
-enum Mode { MODE_COUNT = 0, MODE_FILL = 1, MODE_FUSED = 2 };
+//   MODE_REDUCE no result tensor: the products of the entries both operands hold are summed
+//               (inner product); the tile's partial sum is added to a double in the control block
+enum Mode { MODE_COUNT = 0, MODE_FILL = 1, MODE_FUSED = 2, MODE_REDUCE = 3 };
 
 // Device-side control block of a fused launch.
 struct FusedCtl {
     int ticket;           // next tile number to hand out
     DeviceStatus status;  // bounded-wait failures
-    long long total;      // result entries, written by the last tile
+    long long total;      // result entries, written by the last tile (MODE_REDUCE: the bits of a double, the running sum)
 };
 
 // Optional second result form of the coordinate merge: the CSF3 levels above k. When a fused

@@ -58,15 +58,11 @@ __device__ __forceinline__ void warp_bitonic_merge(uint32_t (&r)[V]) {
 // Merge-path cut of diagonal d (0 <= d) between the sorted lists kx[0, na) and ky[0, nb): the
 // x entries of kx and y = d - x entries of ky that come first in merged order. Keys carry the
 // operand in their last bit (kx even, ky odd), so the kx entry of a position orders before the ky
-// entry of the same position; such a pair is never separated (y grows by one instead). All 32
-// lanes call this together and get the same answer.
-__device__ __forceinline__ void warp_merge_cut(const uint32_t *kx, const int na, const uint32_t *ky, const int nb, const int d,
-                                               int &x, int &y) {
-    if (d >= na + nb) {
-        x = na;
-        y = nb;
-        return;
-    }
+// entry of the same position. All 32 lanes call these together and get the same answer.
+// warp_count_cut returns x; warp_merge_cut also returns y, one larger where the cut would
+// otherwise separate the two entries of one position.
+__device__ __forceinline__ int warp_count_cut(const uint32_t *kx, const int na, const uint32_t *ky, const int nb, const int d) {
+    if (d >= na + nb) return na;
     int lo = max(0, d - nb), hi = min(d, na);
     while (lo < hi) {  // number of leading m in [lo, hi) with kx[m] < ky[d - 1 - m]
         const int step = (hi - lo + 31) >> 5;
@@ -76,8 +72,13 @@ __device__ __forceinline__ void warp_merge_cut(const uint32_t *kx, const int na,
         lo += c * step;
         hi = min(lo + step - 1, hi);
     }
-    x = lo;
-    y = d - lo;
+    return lo;
+}
+
+__device__ __forceinline__ void warp_merge_cut(const uint32_t *kx, const int na, const uint32_t *ky, const int nb, const int d,
+                                               int &x, int &y) {
+    x = warp_count_cut(kx, na, ky, nb, d);
+    y = min(d, na + nb) - x;
     if (x > 0 && y < nb && (kx[x - 1] ^ ky[y]) == 1u) ++y;
 }
 

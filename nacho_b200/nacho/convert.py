@@ -35,13 +35,35 @@ def to_csr(csr, device="cuda"):
 
 
 def to_dcsr(csr, device="cuda"):
-    """DCSR is outside the kernels this package implements (python/nacho/convert.py:34-56)."""
-    raise NotImplementedError("DCSR tensors are not part of the nacho_b200 hot path")
+    """torch CSR -> DCSR_gpu: empty rows are dropped and the surviving row numbers stored
+    (python/nacho/convert.py:34-56). The row selection runs on the tensor's own device."""
+    dev = _gpu_only(device)
+    indptr = csr.crow_indices().to(dtype=torch.int64)
+    per_row = indptr[1:] - indptr[:-1]
+    present = torch.nonzero(per_row > 0).squeeze(-1)
+    offsets = torch.zeros(present.numel() + 1, dtype=torch.int64, device=indptr.device)
+    offsets[1:] = torch.cumsum(per_row[present], 0)
+    return _ext.DCSR_gpu(
+        present.to(dtype=torch.int32, device=dev),
+        offsets.to(dtype=torch.int32, device=dev),
+        csr.col_indices().to(dtype=torch.int32, device=dev),
+        csr.values().to(dtype=torch.float32, device=dev),
+        _shape(csr.shape[0], csr.shape[1]),
+    )
 
 
 def to_coo(coo, device="cuda"):
-    """2-D COO is outside the kernels this package implements (python/nacho/convert.py:58-67)."""
-    raise NotImplementedError("2-D COO tensors are not part of the nacho_b200 hot path")
+    """torch COO -> COO_gpu; coalesced first so that the coordinates are sorted and unique
+    (python/nacho/convert.py:58-67)."""
+    dev = _gpu_only(device)
+    coo = coo.coalesce()
+    indices = coo.indices()
+    return _ext.COO_gpu(
+        indices[0].to(dtype=torch.int32, device=dev).contiguous(),
+        indices[1].to(dtype=torch.int32, device=dev).contiguous(),
+        coo.values().to(dtype=torch.float32, device=dev),
+        _shape(coo.shape[0], coo.shape[1]),
+    )
 
 
 def _tensor(array, dtype, dev):

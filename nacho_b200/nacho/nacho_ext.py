@@ -16,10 +16,12 @@ import ctypes as C
 import torch
 
 from .. import _capi
-from .._capi import Coo3Struct, CsrStruct, Csf3Struct, lib
+from .._capi import Coo3Struct, CooStruct, CsrStruct, Csf3Struct, DcsrStruct, lib
 
-__all__ = ["CSR_gpu", "COO3_gpu", "CSF3_gpu", "gpu_csr_add_f32", "gpu_csr_add_3_f32", "gpu_csr_mul_f32", "gpu_spgemm_f32", "gpu_coo3d_add_f32",
-           "gpu_csf_add_f32"]
+__all__ = ["CSR_gpu", "COO3_gpu", "CSF3_gpu", "COO_gpu", "DCSR_gpu", "Scalar_gpu", "gpu_csr_add_f32", "gpu_csr_add_3_f32",
+           "gpu_csr_mul_f32", "gpu_spgemm_f32", "gpu_coo3d_add_f32", "gpu_csf_add_f32", "gpu_coo_add_f32", "gpu_coo_mul_f32",
+           "gpu_coo_csr_add_f32", "gpu_dcsr_add_f32", "gpu_dcsr_mul_f32", "gpu_dcsr_mul_without_recursive_partitioning_f32",
+           "gpu_inner_prod_f32", "gpu_inner_prod_coo_f32", "gpu_sssmm_f32"]
 
 
 def _dev_array(t, dtype, name):
@@ -272,3 +274,194 @@ def gpu_csf_add_f32(a: CSF3_gpu, b: CSF3_gpu, num_blocks: int = 256, threads_per
     ni, nj, nk = int(sz.n_i), int(sz.n_j), int(sz.n_k)
     return CSF3_gpu(zi[:ni], zjp[:ni + 1], zj[:nj], zkp[:nj + 1], zk[:nk], zv[:nk],
                     torch.tensor(list(sz.dims), dtype=torch.int32))
+
+
+# ---- the rest of the element-wise family: 2-D COO, DCSR, inner products, masked SpGEMM ----
+
+class COO_gpu:
+    """2-D coordinate list sorted by (i, j): ``COO_gpu(dim_i_indices, dim_j_indices, values, shape)``."""
+
+    __slots__ = ("_i", "_j", "_values", "_shape")
+
+    def __init__(self, dim_i_indices, dim_j_indices, values, shape):
+        self._i = _dev_array(dim_i_indices, torch.int32, "dim_i_indices")
+        self._j = _dev_array(dim_j_indices, torch.int32, "dim_j_indices")
+        self._values = _dev_array(values, torch.float32, "values")
+        self._shape = _shape_array(shape, 2)
+        if not (self._i.numel() == self._j.numel() == self._values.numel()):
+            raise ValueError("coordinate arrays and values differ in length")
+
+    dim_i_indices = property(lambda self: self._i)
+    dim_j_indices = property(lambda self: self._j)
+    values = property(lambda self: self._values)
+    shape = property(lambda self: self._shape)
+
+    @property
+    def device(self):
+        return self._values.device
+
+    def _struct(self) -> CooStruct:
+        return CooStruct(int(self._shape[0]), int(self._shape[1]), self._values.numel(), self._i.data_ptr(),
+                         self._j.data_ptr(), self._values.data_ptr())
+
+    def __repr__(self):
+        return f"COO_gpu(shape=({int(self._shape[0])}, {int(self._shape[1])}), nnz={self._values.numel()})"
+
+
+class DCSR_gpu:
+    """CSR with a compressed row level: ``DCSR_gpu(dim_i_indices, dim_j_offsets, dim_j_indices, values,
+    shape)``; ``dim_i_indices`` lists the rows that hold entries, ``dim_j_offsets`` has one entry more."""
+
+    __slots__ = ("_i", "_jp", "_j", "_values", "_shape")
+
+    def __init__(self, dim_i_indices, dim_j_offsets, dim_j_indices, values, shape):
+        self._i = _dev_array(dim_i_indices, torch.int32, "dim_i_indices")
+        self._jp = _dev_array(dim_j_offsets, torch.int32, "dim_j_offsets")
+        self._j = _dev_array(dim_j_indices, torch.int32, "dim_j_indices")
+        self._values = _dev_array(values, torch.float32, "values")
+        self._shape = _shape_array(shape, 2)
+        if self._jp.numel() != self._i.numel() + 1:
+            raise ValueError("dim_j_offsets must hold one entry more than dim_i_indices")
+        if self._j.numel() != self._values.numel():
+            raise ValueError("dim_j_indices and values differ in length")
+
+    dim_i_indices = property(lambda self: self._i)
+    dim_j_offsets = property(lambda self: self._jp)
+    dim_j_indices = property(lambda self: self._j)
+    values = property(lambda self: self._values)
+    shape = property(lambda self: self._shape)
+
+    @property
+    def device(self):
+        return self._values.device
+
+    def _struct(self) -> DcsrStruct:
+        return DcsrStruct(int(self._shape[0]), int(self._shape[1]), self._i.numel(), self._values.numel(),
+                          self._i.data_ptr(), self._jp.data_ptr(), self._j.data_ptr(), self._values.data_ptr())
+
+    def __repr__(self):
+        return f"DCSR_gpu(shape=({int(self._shape[0])}, {int(self._shape[1])}), rows_stored={self._i.numel()}, nnz={self._values.numel()})"
+
+
+class Scalar_gpu:
+    """Result of a full reduction: ``values`` is a one-element float32 CUDA tensor."""
+
+    __slots__ = ("_values",)
+
+    def __init__(self, values):
+        self._values = _dev_array(values, torch.float32, "values")
+
+    values = property(lambda self: self._values)
+
+    @property
+    def device(self):
+        return self._values.device
+
+
+def _coo_binary(entry, where, a: COO_gpu, b: COO_gpu, capacity: int) -> COO_gpu:
+    if not isinstance(a, COO_gpu) or not isinstance(b, COO_gpu):
+        raise TypeError(f"{where}: operands must be COO_gpu")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    with torch.cuda.device(dev):
+        zi, zj = (torch.empty(max(capacity, 1), dtype=torch.int32, device=dev) for _ in range(2))
+        zv = torch.empty(max(capacity, 1), dtype=torch.float32, device=dev)
+        sz = CooStruct(sa.rows, sa.cols, 0, zi.data_ptr(), zj.data_ptr(), zv.data_ptr())
+        status = entry(C.byref(sa), C.byref(sb), C.byref(sz), capacity, _stream_for(zv))
+    _capi.check(status, where)
+    n = int(sz.nnz)
+    return COO_gpu(zi[:n], zj[:n], zv[:n], torch.tensor([sz.rows, sz.cols], dtype=torch.int32))
+
+
+def gpu_coo_add_f32(a: COO_gpu, b: COO_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> COO_gpu:
+    """Z = A + B over sorted unique (i, j) lists."""
+    return _coo_binary(lib.nb200_coo_add_f32_into, "gpu_coo_add_f32", a, b, a.values.numel() + b.values.numel())
+
+
+def gpu_coo_mul_f32(a: COO_gpu, b: COO_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> COO_gpu:
+    """Z = A .* B over sorted unique (i, j) lists."""
+    return _coo_binary(lib.nb200_coo_mul_f32_into, "gpu_coo_mul_f32", a, b, min(a.values.numel(), b.values.numel()))
+
+
+def gpu_coo_csr_add_f32(a: CSR_gpu, b: COO_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSR_gpu:
+    """Z = A + B with A in CSR and B a coordinate list; the result is CSR."""
+    if not isinstance(a, CSR_gpu) or not isinstance(b, COO_gpu):
+        raise TypeError("gpu_coo_csr_add_f32: operands must be (CSR_gpu, COO_gpu)")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    capacity = sa.nnz + sb.nnz
+    with torch.cuda.device(dev):
+        row_ptr = _csr_result(sa.rows, sa.cols, dev)
+        col = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+        val = torch.empty(max(capacity, 1), dtype=torch.float32, device=dev)
+        sz = CsrStruct(sa.rows, sa.cols, 0, row_ptr.data_ptr(), col.data_ptr(), val.data_ptr())
+        status = lib.nb200_coo_csr_add_f32_into(C.byref(sa), C.byref(sb), C.byref(sz), capacity, _stream_for(row_ptr))
+    _capi.check(status, "gpu_coo_csr_add_f32")
+    n = int(sz.nnz)
+    return CSR_gpu(row_ptr, col[:n], val[:n], torch.tensor([sz.rows, sz.cols], dtype=torch.int32))
+
+
+def _dcsr_binary(entry, where, a: DCSR_gpu, b: DCSR_gpu, cap_i: int, capacity: int) -> DCSR_gpu:
+    if not isinstance(a, DCSR_gpu) or not isinstance(b, DCSR_gpu):
+        raise TypeError(f"{where}: operands must be DCSR_gpu")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    with torch.cuda.device(dev):
+        zi = torch.empty(max(cap_i, 1), dtype=torch.int32, device=dev)
+        zjp = torch.empty(cap_i + 1, dtype=torch.int32, device=dev)
+        zj = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+        zv = torch.empty(max(capacity, 1), dtype=torch.float32, device=dev)
+        sz = DcsrStruct(sa.rows, sa.cols, 0, 0, zi.data_ptr(), zjp.data_ptr(), zj.data_ptr(), zv.data_ptr())
+        status = entry(C.byref(sa), C.byref(sb), C.byref(sz), cap_i, capacity, _stream_for(zv))
+    _capi.check(status, where)
+    ni, n = int(sz.n_i), int(sz.nnz)
+    return DCSR_gpu(zi[:ni], zjp[:ni + 1], zj[:n], zv[:n], torch.tensor([sz.rows, sz.cols], dtype=torch.int32))
+
+
+def gpu_dcsr_add_f32(a: DCSR_gpu, b: DCSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> DCSR_gpu:
+    """Z = A + B for DCSR operands."""
+    rows = int(a.shape[0])
+    return _dcsr_binary(lib.nb200_dcsr_add_f32_into, "gpu_dcsr_add_f32", a, b,
+                        min(a.dim_i_indices.numel() + b.dim_i_indices.numel(), rows), a.values.numel() + b.values.numel())
+
+
+def gpu_dcsr_mul_f32(a: DCSR_gpu, b: DCSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> DCSR_gpu:
+    """Z = A .* B for DCSR operands; a row both operands store stays, even with no common column."""
+    return _dcsr_binary(lib.nb200_dcsr_mul_f32_into, "gpu_dcsr_mul_f32", a, b,
+                        min(a.dim_i_indices.numel(), b.dim_i_indices.numel()), min(a.values.numel(), b.values.numel()))
+
+
+def gpu_dcsr_mul_without_recursive_partitioning_f32(a: DCSR_gpu, b: DCSR_gpu, num_blocks: int = 256,
+                                                    threads_per_block: int = 256) -> DCSR_gpu:
+    """The reference emits the DCSR product twice to compare two partitioning strategies of its code
+    generator (compiler.cpp:128-133); both compute the same tensor, and so does this alias."""
+    return gpu_dcsr_mul_f32(a, b, num_blocks, threads_per_block)
+
+
+def _inner(entry, where, a, b, cls) -> Scalar_gpu:
+    if not isinstance(a, cls) or not isinstance(b, cls):
+        raise TypeError(f"{where}: operands must be {cls.__name__}")
+    dev = _same_device(a, b)
+    sa, sb = a._struct(), b._struct()
+    with torch.cuda.device(dev):
+        z = torch.empty(1, dtype=torch.float32, device=dev)
+        status = entry(C.byref(sa), C.byref(sb), z.data_ptr(), _stream_for(z))
+    _capi.check(status, where)
+    return Scalar_gpu(z)
+
+
+def gpu_inner_prod_f32(a: CSF3_gpu, b: CSF3_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> Scalar_gpu:
+    """sum_ijk a_ijk * b_ijk for CSF3 operands."""
+    return _inner(lib.nb200_inner_prod_f32, "gpu_inner_prod_f32", a, b, CSF3_gpu)
+
+
+def gpu_inner_prod_coo_f32(a: COO3_gpu, b: COO3_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> Scalar_gpu:
+    """sum_ijk a_ijk * b_ijk for COO3 operands."""
+    return _inner(lib.nb200_inner_prod_coo_f32, "gpu_inner_prod_coo_f32", a, b, COO3_gpu)
+
+
+def gpu_sssmm_f32(a: CSR_gpu, b: CSR_gpu, c: CSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSR_gpu:
+    """Z_ik = c_ik * sum_j a_ij * b_jk on the positions C stores (masked SpGEMM, compiler.cpp:150-153):
+    the expand-sort-compress product followed by the intersection with the mask, both on the GPU.
+    (Two calls of the library, not one fused kernel: the product is formed in full first.)"""
+    return gpu_csr_mul_f32(gpu_spgemm_f32(a, b), c)

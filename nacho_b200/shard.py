@@ -51,6 +51,24 @@ def row_block_cuts(row_ptrs: Sequence, parts: int) -> list[int]:
     return cuts
 
 
+def row_block_cuts_device(row_ptrs: Sequence[torch.Tensor], parts: int) -> list[int]:
+    """``row_block_cuts`` for row offsets that live on a GPU: the summed offsets and the ``parts - 1``
+    searches run on the device (``torch.searchsorted``); only the cut rows come back to the host."""
+    work = None
+    for rp in row_ptrs:
+        w = rp.to(torch.int64)
+        w = w - w[0]
+        work = w if work is None else work + w
+    rows = work.numel() - 1
+    total = int(work[-1])
+    targets = torch.tensor([(total * g) // parts for g in range(1, parts)], dtype=torch.int64, device=work.device)
+    inner = torch.searchsorted(work, targets, right=False).cpu().tolist() if parts > 1 else []
+    cuts = [0] + [int(c) for c in inner] + [rows]
+    for g in range(1, parts + 1):
+        cuts[g] = min(max(cuts[g], cuts[g - 1]), rows)
+    return cuts
+
+
 def product_balanced_cuts(a_row_ptr, a_col, b_row_ptr, parts: int) -> list[int]:
     """Row cuts of A that balance the SpGEMM product counts sum_j nnz(B_j) over the blocks."""
     a_rp, b_rp = _np(a_row_ptr).astype(np.int64), _np(b_row_ptr).astype(np.int64)
@@ -232,6 +250,95 @@ def stitch(rows_local: int, nnz_local: int, group=None, device=None):
     pairs = gathered.view(world, 2).cpu()
     rows_all, nnz_all = pairs[:, 0].tolist(), pairs[:, 1].tolist()
     return sum(rows_all[:rank]), sum(nnz_all[:rank]), rows_all, nnz_all
+
+
+class CsrRowBlockOp:
+    """CSR add or multiply of one rank's row block, run without any wait on the host: the operator
+    is queued with ``nb200_csr_{add,mul}_f32_async`` (result length and status stay in device
+    words) and the stitch -- the all-gather of every block's (rows, nnz) whose exclusive prefix is
+    the block's global row base and the amount to add to its row offsets -- is issued as an
+    asynchronous collective that reads those device words, so that it overlaps the next step's
+    kernels. Result arrays are allocated once, at the worst-case length.
+
+        op = CsrRowBlockOp("add", a_block, b_block)      # CSR_gpu row blocks of this rank
+        op.launch()                                      # queue operator + stitch; returns at once
+        rows_base, nnz_base, counts = op.bases()         # device tensors; waits on the device only
+        z, nnz, status = op.result()                     # host read-back (tests, end of a job)
+    """
+
+    def __init__(self, op: str, a, b, group=None, slots: int = 4):
+        import ctypes as C
+        from . import _capi
+        from ._capi import CsrStruct, lib
+        self._C, self._capi, self._CsrStruct = C, _capi, CsrStruct
+        self._entry = {"add": lib.nb200_csr_add_f32_async, "mul": lib.nb200_csr_mul_f32_async}[op]
+        self.a, self.b, self.group = a, b, group
+        dev = a.values.device
+        na, nb = a.values.numel(), b.values.numel()
+        self.capacity = na + nb if op == "add" else min(na, nb)
+        self.rows = int(a.shape[0])
+        self.row_ptr = torch.empty(self.rows + 1, dtype=torch.int32, device=dev)
+        self.col = torch.empty(max(self.capacity, 1), dtype=torch.int32, device=dev)
+        self.val = torch.empty(max(self.capacity, 1), dtype=torch.float32, device=dev)
+        self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        # per launch: [nnz, status] written by the library, and [rows, nnz] sent to the other ranks
+        self._result = [torch.zeros(2, dtype=torch.int64, device=dev) for _ in range(slots)]
+        self._mine = [torch.zeros(2, dtype=torch.int64, device=dev) for _ in range(slots)]
+        self._gathered = [torch.zeros(2 * self.world, dtype=torch.int64, device=dev) for _ in range(slots)]
+        self._pending = [None] * slots
+        self._n = 0
+        self._rows_t = torch.tensor([self.rows], dtype=torch.int64, device=dev)
+
+    def launch(self):
+        C = self._C
+        k = self._n % len(self._result)
+        if self._pending[k] is not None:  # the slot's previous collective must be done before its buffers are reused
+            self._pending[k].wait()
+            self._pending[k] = None
+        sa, sb = self.a._struct(), self.b._struct()
+        sz = self._CsrStruct(self.rows, sa.cols, 0, self.row_ptr.data_ptr(), self.col.data_ptr(), self.val.data_ptr())
+        stream = torch.cuda.current_stream(self.val.device).cuda_stream
+        with torch.cuda.device(self.val.device):
+            status = self._entry(C.byref(sa), C.byref(sb), C.byref(sz), self.capacity, self._result[k].data_ptr(), stream)
+        self._capi.check(status, "CsrRowBlockOp.launch")
+        if self.distributed:
+            self._mine[k][0:1].copy_(self._rows_t)
+            self._mine[k][1:2].copy_(self._result[k][0:1])
+            self._pending[k] = dist.all_gather_into_tensor(self._gathered[k], self._mine[k], group=self.group, async_op=True)
+        self._n += 1
+        return k
+
+    def bases(self, slot: int | None = None):
+        """(row_base, nnz_base, counts) of the latest launch (or of ``slot``) as device tensors;
+        the current stream waits for the collective, the host does not."""
+        k = (self._n - 1) % len(self._result) if slot is None else slot
+        if not self.distributed:
+            z = torch.zeros(1, dtype=torch.int64, device=self.val.device)
+            return z, z, torch.stack([self._rows_t[0], self._result[k][0]]).view(1, 2)
+        if self._pending[k] is not None:
+            self._pending[k].wait()
+            self._pending[k] = None
+        counts = self._gathered[k].view(self.world, 2)
+        base = counts[: self.rank].sum(dim=0)
+        return base[0:1], base[1:2], counts
+
+    def drain(self):
+        for k, w in enumerate(self._pending):
+            if w is not None:
+                w.wait()
+                self._pending[k] = None
+
+    def result(self):
+        """Host read-back of the latest launch: (CSR_gpu of this block, nnz, status)."""
+        from .nacho import nacho_ext
+        k = (self._n - 1) % len(self._result)
+        self.drain()
+        nnz, status = (int(x) for x in self._result[k].cpu())
+        self._capi.check(status, "CsrRowBlockOp.result")
+        z = nacho_ext.CSR_gpu(self.row_ptr, self.col[:nnz], self.val[:nnz], self.a.shape.clone())
+        return z, nnz, status
 
 
 def broadcast_csr(row_ptr, col, val, shape, src: int = 0, group=None, device=None):

@@ -10,6 +10,7 @@ module; product code never does. Operands and results are plain tuples of numpy 
 * CSR  = (rows, cols, row_ptr[int32 rows+1], col[int32 nnz], val[float32 nnz])
 * COO3 = (dims(3), i, j, k, val)
 * CSF3 = (dims(3), i_idx, j_ptr, j_idx, k_ptr, k_idx, val)
+* COO  = (rows, cols, i, j, val);  DCSR = (rows, cols, i_idx, j_ptr[len(i_idx)+1], j_idx, val)
 """
 from __future__ import annotations
 
@@ -27,6 +28,8 @@ REF_SO = os.path.join(HERE, "_ref", "libnacho_ref_cpu.so")
 CSR = namedtuple("CSR", "rows cols row_ptr col val")
 COO3 = namedtuple("COO3", "dims i j k val")
 CSF3 = namedtuple("CSF3", "dims i_idx j_ptr j_idx k_ptr k_idx val")
+COO = namedtuple("COO", "rows cols i j val")                    # 2-D coordinate list, sorted by (i, j)
+DCSR = namedtuple("DCSR", "rows cols i_idx j_ptr j_idx val")    # CSR whose row level is compressed too
 
 _I32P = C.POINTER(C.c_int32)
 _F32P = C.POINTER(C.c_float)
@@ -210,6 +213,16 @@ class _RefCSF3(C.Structure):
                 ("k_idx", _I32P), ("val", _F32P)]
 
 
+class _RefCOO(C.Structure):
+    _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("nnz", C.c_int32),
+                ("i", _I32P), ("j", _I32P), ("val", _F32P)]
+
+
+class _RefDCSR(C.Structure):
+    _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("n_i", C.c_int32), ("nnz", C.c_int32),
+                ("i_idx", _I32P), ("j_ptr", _I32P), ("j_idx", _I32P), ("val", _F32P)]
+
+
 def _take(ptr, n, dtype):
     if n <= 0 or not ptr:
         return np.empty(0, dtype)
@@ -232,6 +245,16 @@ class Reference:
         L.ref_csr_add_3.argtypes = [P(_RefCSR)] * 4
         L.ref_coo3d_add.argtypes = [P(_RefCOO3)] * 3
         L.ref_csf_add.argtypes = [P(_RefCSF3)] * 3
+        if hasattr(L, "ref_coo_add"):  # the element-wise family beyond the five benchmarked kernels
+            L.ref_coo_add.argtypes = [P(_RefCOO)] * 3
+            L.ref_coo_mul.argtypes = [P(_RefCOO)] * 3
+            L.ref_coo_csr_add.argtypes = [P(_RefCSR), P(_RefCOO), P(_RefCSR)]
+            L.ref_dcsr_add.argtypes = [P(_RefDCSR)] * 3
+            L.ref_dcsr_mul.argtypes = [P(_RefDCSR)] * 3
+            L.ref_inner_prod.argtypes = [P(_RefCSF3)] * 2
+            L.ref_inner_prod.restype = C.c_float
+            L.ref_inner_prod_coo.argtypes = [P(_RefCOO3)] * 2
+            L.ref_inner_prod_coo.restype = C.c_float
 
     @staticmethod
     def available(path: str = REF_SO) -> bool:
@@ -311,3 +334,91 @@ class Reference:
                    _take(z.k_idx, z.n_k, np.int32), _take(z.val, z.n_k, np.float32)) if keep else None
         self._free(z.i_idx, z.j_ptr, z.j_idx, z.k_ptr, z.k_idx, z.val)
         return out
+
+    # ---- the rest of the element-wise family (2-D COO, DCSR, inner products) ----
+
+    @staticmethod
+    def _coo_in(m: COO):
+        arrs = (_i32(m.i), _i32(m.j), _f32(m.val))
+        return _RefCOO(m.rows, m.cols, len(arrs[2]), _p(arrs[0], _I32P), _p(arrs[1], _I32P), _p(arrs[2], _F32P)), arrs
+
+    def _coo_binary(self, fn, a: COO, b: COO) -> COO:
+        sa, ka = self._coo_in(a)
+        sb, kb = self._coo_in(b)
+        z = _RefCOO()
+        fn(C.byref(sa), C.byref(sb), C.byref(z))
+        out = COO(z.rows, z.cols, _take(z.i, z.nnz, np.int32), _take(z.j, z.nnz, np.int32), _take(z.val, z.nnz, np.float32))
+        self._free(z.i, z.j, z.val)
+        return out
+
+    def coo_add(self, a: COO, b: COO) -> COO:
+        return self._coo_binary(self.lib.ref_coo_add, a, b)
+
+    def coo_mul(self, a: COO, b: COO) -> COO:
+        return self._coo_binary(self.lib.ref_coo_mul, a, b)
+
+    def coo_csr_add(self, a: CSR, b: COO) -> CSR:
+        sa, ka = self._csr_in(a)
+        sb, kb = self._coo_in(b)
+        z = _RefCSR()
+        self.lib.ref_coo_csr_add(C.byref(sa), C.byref(sb), C.byref(z))
+        return self._csr_out(z)
+
+    @staticmethod
+    def _dcsr_in(m: DCSR):
+        arrs = (_i32(m.i_idx), _i32(m.j_ptr), _i32(m.j_idx), _f32(m.val))
+        s = _RefDCSR(m.rows, m.cols, len(arrs[0]), len(arrs[3]), _p(arrs[0], _I32P), _p(arrs[1], _I32P),
+                     _p(arrs[2], _I32P), _p(arrs[3], _F32P))
+        return s, arrs
+
+    def _dcsr_binary(self, fn, a: DCSR, b: DCSR) -> DCSR:
+        sa, ka = self._dcsr_in(a)
+        sb, kb = self._dcsr_in(b)
+        z = _RefDCSR()
+        fn(C.byref(sa), C.byref(sb), C.byref(z))
+        out = DCSR(z.rows, z.cols, _take(z.i_idx, z.n_i, np.int32), _take(z.j_ptr, z.n_i + 1, np.int32),
+                   _take(z.j_idx, z.nnz, np.int32), _take(z.val, z.nnz, np.float32))
+        self._free(z.i_idx, z.j_ptr, z.j_idx, z.val)
+        return out
+
+    def dcsr_add(self, a: DCSR, b: DCSR) -> DCSR:
+        return self._dcsr_binary(self.lib.ref_dcsr_add, a, b)
+
+    def dcsr_mul(self, a: DCSR, b: DCSR) -> DCSR:
+        return self._dcsr_binary(self.lib.ref_dcsr_mul, a, b)
+
+    def inner_prod(self, a: CSF3, b: CSF3) -> float:
+        def mk(t):
+            arrs = (_i32(t.i_idx), _i32(t.j_ptr), _i32(t.j_idx), _i32(t.k_ptr), _i32(t.k_idx), _f32(t.val))
+            s = _RefCSF3((C.c_int32 * 3)(*t.dims), len(arrs[0]), len(arrs[2]), len(arrs[4]),
+                         *[_p(x, _I32P) for x in arrs[:5]], _p(arrs[5], _F32P))
+            return s, arrs
+        sa, ka = mk(a)
+        sb, kb = mk(b)
+        return float(self.lib.ref_inner_prod(C.byref(sa), C.byref(sb)))
+
+    def inner_prod_coo(self, a: COO3, b: COO3) -> float:
+        def mk(t):
+            arrs = (_i32(t.i), _i32(t.j), _i32(t.k), _f32(t.val))
+            s = _RefCOO3((C.c_int32 * 3)(*t.dims), len(arrs[3]), _p(arrs[0], _I32P), _p(arrs[1], _I32P),
+                         _p(arrs[2], _I32P), _p(arrs[3], _F32P))
+            return s, arrs
+        sa, ka = mk(a)
+        sb, kb = mk(b)
+        return float(self.lib.ref_inner_prod_coo(C.byref(sa), C.byref(sb)))
+
+
+def csr_to_dcsr(m: CSR) -> DCSR:
+    """Drops the empty rows of a CSR matrix (what the reference's to_dcsr does,
+    python/nacho/convert.py:34-56)."""
+    lens = np.diff(np.asarray(m.row_ptr, np.int64))
+    present = np.flatnonzero(lens > 0)
+    ptr = np.zeros(len(present) + 1, np.int32)
+    ptr[1:] = np.cumsum(lens[present])
+    return DCSR(m.rows, m.cols, present.astype(np.int32), ptr, np.asarray(m.col, np.int32), np.asarray(m.val, np.float32))
+
+
+def csr_to_coo(m: CSR) -> COO:
+    lens = np.diff(np.asarray(m.row_ptr, np.int64))
+    return COO(m.rows, m.cols, np.repeat(np.arange(m.rows, dtype=np.int32), lens), np.asarray(m.col, np.int32),
+               np.asarray(m.val, np.float32))

@@ -37,6 +37,22 @@ typedef struct {
     float *val;      // n_k
 } ref_csf3;
 
+typedef struct {
+    int32_t rows, cols;
+    int32_t nnz;
+    int32_t *i, *j;  // nnz each
+    float *val;
+} ref_coo;
+
+typedef struct {
+    int32_t rows, cols;
+    int32_t n_i, nnz;
+    int32_t *i_idx;  // n_i: the rows that hold entries
+    int32_t *j_ptr;  // n_i + 1
+    int32_t *j_idx;  // nnz
+    float *val;      // nnz
+} ref_dcsr;
+
 int ref_threads(void);
 void ref_free(void *p);
 void ref_csr_add(const ref_csr *a, const ref_csr *b, ref_csr *z);
@@ -44,6 +60,13 @@ void ref_csr_mul(const ref_csr *a, const ref_csr *b, ref_csr *z);
 void ref_csr_add_3(const ref_csr *a, const ref_csr *b, const ref_csr *c, ref_csr *z);
 void ref_coo3d_add(const ref_coo3 *a, const ref_coo3 *b, ref_coo3 *z);
 void ref_csf_add(const ref_csf3 *a, const ref_csf3 *b, ref_csf3 *z);
+void ref_coo_add(const ref_coo *a, const ref_coo *b, ref_coo *z);
+void ref_coo_mul(const ref_coo *a, const ref_coo *b, ref_coo *z);
+void ref_coo_csr_add(const ref_csr *a, const ref_coo *b, ref_csr *z);
+void ref_dcsr_add(const ref_dcsr *a, const ref_dcsr *b, ref_dcsr *z);
+void ref_dcsr_mul(const ref_dcsr *a, const ref_dcsr *b, ref_dcsr *z);
+float ref_inner_prod(const ref_csf3 *a, const ref_csf3 *b);
+float ref_inner_prod_coo(const ref_coo3 *a, const ref_coo3 *b);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,10 @@
+// Wrapper around the reference's emitted dcsr_mul_cpu_i32_f32 (test infrastructure only).
+#include "dcsr_mul_cpu.h"
+#include "ref_common.h"
+
+extern "C" void ref_dcsr_mul(const ref_dcsr *a, const ref_dcsr *b, ref_dcsr *z) {
+    using namespace dcsr_mul;
+    auto Z = dcsr_mul_cpu_i32_f32(dcsr_view<a_tensor_format<index_t, value_t>>(a),
+                                  dcsr_view<b_tensor_format<index_t, value_t>>(b));
+    dcsr_out(Z, z);
+}

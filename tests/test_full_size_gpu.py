@@ -53,7 +53,7 @@ def test_config2_mul_full_size(nacho, checker):
 def test_config3_add_full_size(nacho, checker, sigma):
     from nacho_b200 import synth
     ta, tb = synth.c3_csr(0, sigma, device="cuda"), synth.c3_csr(1, sigma, device="cuda")
-    assert ta[0] == 1 << 20 and ta[3].numel() > 40_000_000
+    assert ta[0] == 1 << 20 and ta[3].numel() > 30_000_000  # high skew ends under the 64 M budget (duplicates removed)
     got = csr_from_gpu(nacho.gpu_csr_add_f32(synth_to_gpu(ta), synth_to_gpu(tb)))
     want = checker["csr_add"](synth_csr(ta), synth_csr(tb))
     assert_same(got, want, f"config 3 sigma={sigma} at full size vs {checker['kind']}")
