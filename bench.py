@@ -113,24 +113,12 @@ def make_operands(name: str, rank: int, device, scale: float = 1.0, rmat_scale: 
 
 
 def csf3_arrays(t, device):
-    """COO3 synth tuple -> the six CSF3 level arrays as torch tensors on `device` (computed
-    with torch so that 100 M entries take seconds)."""
-    import torch
+    """COO3 synth tuple -> the six CSF3 level arrays as torch tensors on `device`, built on the
+    device by the package's own converter (100 M entries take seconds)."""
+    from nacho_b200.nacho.convert import csf3_levels_device
     dims, i, j, k, v = t
-    n = i.numel()
-    new_ij = torch.ones(n, dtype=torch.bool, device=i.device)
-    if n > 1:
-        new_ij[1:] = (i[1:] != i[:-1]) | (j[1:] != j[:-1])
-    ij = torch.nonzero(new_ij).squeeze(1)
-    ii = i[ij]
-    new_i = torch.ones(ij.numel(), dtype=torch.bool, device=i.device)
-    if ij.numel() > 1:
-        new_i[1:] = ii[1:] != ii[:-1]
-    ist = torch.nonzero(new_i).squeeze(1)
-    cat = lambda a, x: torch.cat([a, torch.tensor([x], device=a.device, dtype=a.dtype)])
-    out = (ii[ist], cat(ist, ij.numel()), j[ij], cat(ij, n), k, v)
-    return dims, tuple(x.to(device=device, dtype=torch.float32 if x.dtype.is_floating_point else torch.int32).contiguous()
-                       for x in out)
+    levels = csf3_levels_device(i.to(device), j.to(device), k.to(device))
+    return dims, tuple(levels) + (v.to(device=device).contiguous(),)
 
 
 def bytes_csr(rows: int, nnz: int) -> int:

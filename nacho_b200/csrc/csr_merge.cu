@@ -6,9 +6,9 @@
 // warp-wide 32-ary searches (rows on the summed row offsets, then the merge-path diagonal
 // inside the row). One CTA then owns one tile: the copy engine stages the tile's column indices
 // and values in shared memory, the columns are turned into composite (row-in-tile, column) keys
-// so that row boundaries need no special casing, and each of the CTA's eight worker warps merges
-// its share of the tile in registers (a bitonic network over register slots striped across the
-// warp), ranks the survivors with warp votes and stores them coalesced straight from registers.
+// so that row boundaries need no special casing, the tile is split among the threads with an
+// in-shared-memory merge-path search, every thread merges its entries in registers (a bitonic
+// network), and the survivors are compacted through shared memory and written back coalesced.
 // Row offsets of the result are produced by the same pass: a tile owns the offsets of the rows
 // that begin inside it.
 //
@@ -21,25 +21,18 @@
 #include <cstring>
 #include <mutex>
 
-#include "block_utils.cuh"
-#include "common.cuh"
-#include "merge_common.cuh"
-#include "tma.cuh"
+#include "csr_common.cuh"
 #include "warp_merge.cuh"
 
 namespace nb200 {
 
 namespace {
 
-// Tuning knobs (compile-time): which of the two tile bodies runs, its entries per thread (or
-// register slots per lane of a worker warp: a warp merges up to 32 * V entries at a time), and
-// the number of CTAs per SM the register allocator is asked to leave room for. The CTA always has
-// 256 worker threads and one scan warp.
-#ifndef CSR2_BODY
-#define CSR2_BODY 0          // 0: thread-blocked tile body (VT entries per thread), 1: warp-striped body (V slots per lane)
-#endif
+// Tuning knobs (compile-time): merged entries per worker thread, and the number of CTAs per SM the
+// register allocator is asked to leave room for. The CTA always has 256 worker threads and one
+// scan warp.
 #ifndef CSR2_V
-#define CSR2_V (CSR2_BODY == 0 ? 19 : 16)
+#define CSR2_V 19            // merged entries per worker thread; (V + 1) rounded up to 4 must be an odd multiple of 4
 #endif
 #ifndef CSR2_LB_DEPTH
 #define CSR2_LB_DEPTH 1      // predecessors read per round of the look-back, in units of 32
@@ -54,21 +47,7 @@ namespace {
 #ifndef CSR2_MIN_CTAS
 #define CSR2_MIN_CTAS 3
 #endif
-constexpr int NT = 256;
-
-
-struct CsrIn {
-    const int32_t *rp;
-    const int32_t *col;
-    const float *val;
-    int32_t nnz;
-};
-
-struct CsrOut {
-    int32_t *rp;
-    int32_t *col;
-    float *val;
-};
+constexpr int NT = CSR_NT;
 
 // Tile cuts: for cut t, the row it falls in and the absolute positions in A and B.
 struct Cuts {
@@ -127,57 +106,11 @@ __global__ void __launch_bounds__(NT) k_csr2_partition(CsrIn A, CsrIn B, int32_t
 
 // ------------------------------------------------------------------------ tile kernel ----
 
-// Hardware barriers of the tile kernel: 0 = the whole CTA (__syncthreads), 1 = the NT worker
-// threads, 2 = workers arrive / the scan warp waits ("the tile's count is known").
-using WorkerBar = NamedBarrier<1, NT>;
-using CountBar = NamedBarrier<2, NT + 32>;
-
-// Shared-memory plan of the tile kernel, in 4-byte words. The tile's column indices (turned into
-// keys in place) and values use the same word positions in two arrays of SLOTS words: A's entry e
-// sits at word oa + e and B's at word obv + e, where oa and obv are chosen so that a global address
-// on a 16-byte boundary lands on a 16-byte boundary in shared memory too (what a bulk copy needs).
-//
-// The eight worker warps each take STEP_W merged entries of the tile (one more or less where a cut
-// would separate the two entries of one position), hold them in 32 * V register slots and write
-// them to the result from there, so nothing else is staged.
-template <int V>
-struct WarpPlan {
-    static constexpr int W = NT / 32;                              // worker warps
-    static constexpr int CH = V <= 12 ? 12 : (V <= 20 ? 20 : 28);  // key words each thread scans
-    static constexpr int SLOTS = NT * CH;                          // key words = value words
-    static constexpr int FIT = (SLOTS - 12) / W;                   // entries per warp the staging area has room for
-    static constexpr int STEP_W = 32 * V - 1 < FIT ? 32 * V - 1 : FIT;
-    static constexpr int TILE_STEP = W * STEP_W - 1;               // merged entries between two tile cuts
-    static constexpr int CAP = TILE_STEP + 1;                      // most merged entries of one tile
-    static constexpr size_t BYTES = 8 * (size_t)SLOTS;
-    // A thread's CH-word chunk is read and written as 16-byte vectors; an odd number of vectors
-    // per chunk keeps those accesses free of shared-memory bank conflicts.
-    static_assert((CH / 4) % 2 == 1, "the chunk must be an odd number of 16-byte vectors");
-    static_assert(CAP + 12 <= SLOTS, "the padded tile must fit the staging arrays");
-    static_assert(STEP_W + 1 <= 32 * V, "a warp's entries must fit its register slots");
-    static_assert(V <= 32, "slot masks are 32 bits wide");
-};
-
-// The plan of the body that is compiled in.
-template <int V>
-struct TilePlan {
-#if CSR2_BODY == 0
-    static constexpr int TILE_STEP = NT * V - 1, CAP = NT * V;
-#else
-    static constexpr int TILE_STEP = WarpPlan<V>::TILE_STEP, CAP = WarpPlan<V>::CAP;
-#endif
-};
-
-// Merged entries per thread of the wide-key body, so that its CTA covers a whole tile.
-template <int V>
-struct WideVt {
-    static constexpr int value = (TilePlan<V>::CAP + NT - 1) / NT;
-};
 
 // Tiles whose rows do not fit a 32-bit composite key (long runs of empty rows) take this body:
 // 64-bit keys (row in tile, column), plain loads, a sequential merge of VT entries per thread,
 // values fetched from global memory. It is rarely taken and kept simple; the common case is
-// csr2_tile_warp below.
+// csr2_tile_blocked below.
 template <int VT, int OP, int MODE>
 // (Not inlined, so the structs are taken by address: the kernel declares them __grid_constant__,
 // which lets that address point at the parameter space instead of a per-thread stack copy.)
@@ -355,14 +288,6 @@ __device__ __noinline__ void csr2_tile_wide(const CsrIn &A, const CsrIn &B, cons
         Z.col[base + i] = out_col[i];
         Z.val[base + i] = out_val[i];
     }
-}
-
-constexpr int MBAR_POLL_LIMIT = 1 << 24;
-constexpr int ERR_COPY_TIMEOUT = 2;
-
-// Number of 4-byte elements from `p` up to the next 16-byte boundary (0..3).
-__device__ __forceinline__ int head_elems(const void *p) {
-    return (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2);
 }
 
 // Shared-memory plan of the thread-blocked tile body, in 4-byte words. Keys and values use the
@@ -714,342 +639,6 @@ __device__ __forceinline__ void csr2_tile_blocked(const CsrIn &A, const CsrIn &B
     }
 }
 
-// The common tile body, warp-striped form. Keys are 32-bit composites (row in tile, column, operand bit):
-//     key = ((row << cbits | column) << 1) | (0 for A, 1 for B)
-// so that one unsigned compare orders entries by (row, column) with A first on ties, and
-// two entries are the same position exactly when their keys differ in the last bit only.
-//
-// The CTA has NT worker threads (eight warps) and one more warp, the scan warp.
-//   1. One thread hands the tile's column and value ranges to the copy engine (bulk copies that
-//      complete on an mbarrier). While they fly, each worker warp finds the row of the first key
-//      word it will scan (32-ary search over the row offsets).
-//   2. The workers mark the first entry of every row that starts in the tile with the row number
-//      (one CTA barrier), then every warp spreads the marks over its own 32 * CH words with a
-//      running maximum and appends the operand bit: keys (one CTA barrier).
-//   3. From here each warp works alone: it cuts its STEP_W merged entries out of the tile by
-//      merge-path (32-ary search), loads them as a bitonic sequence striped over its registers,
-//      sorts them with a merge network (register compare-exchanges and butterfly shuffles), flags
-//      pairs, and ranks the survivors with warp votes. No barrier, no shared-memory bank conflict.
-//   4. The warps' counts meet at one barrier. In the single-pass mode the scan warp has meanwhile
-//      walked the predecessors' tile words (bounded decoupled look-back), so the tile's output base
-//      is one addition away; the workers gather the values in the meantime.
-//   5. Every warp stores its survivors straight from registers: the 32 lanes of one register slot
-//      are consecutive result entries. The row offsets of the rows that begin in the tile come
-//      from the warps' vote masks.
-template <int V, int OP, int MODE>
-__device__ __forceinline__ void csr2_tile_warp(const CsrIn &A, const CsrIn &B, const Cuts &cuts, const int cbits, const int t,
-                                               const int num_tiles, int32_t *tile_count, volatile uint64_t *tile_state, FusedCtl *ctl,
-                                               const CsrOut &Z, unsigned char *smem_raw, uint64_t *mbar, const int poll_limit) {
-    using P = WarpPlan<V>;
-    constexpr int W = P::W;
-    constexpr bool WRITES = MODE != MODE_COUNT;
-    __shared__ long long s_base;
-    __shared__ int s_total;
-    __shared__ int s_hurry;  // set once the tile's count is out: from then on the tile waits for its base
-    __shared__ int s_wtotal[W];          // survivors of each warp
-    __shared__ int s_wstart[W];          // merged position (in the tile) of each warp's first entry
-    __shared__ unsigned s_vote[W][V];    // per register slot: the lanes whose entry survives
-    __shared__ unsigned short s_before[W][V];  // per register slot: survivors of the warp in earlier slots
-    const int tid = threadIdx.x;
-    const int lane = tid & 31, wid = tid >> 5;
-    const bool scan_warp = tid >= NT;
-    const int32_t i0 = cuts.row[t], i1 = cuts.row[t + 1];
-    const int32_t a0 = cuts.a[t], b0 = cuts.b[t];
-    const int na = cuts.a[t + 1] - a0, nb = cuts.b[t + 1] - b0;
-    const int n = na + nb;
-    const uint32_t cmask = (1u << cbits) - 1u;
-
-    float *vals = reinterpret_cast<float *>(smem_raw);
-    uint32_t *keys = reinterpret_cast<uint32_t *>(smem_raw) + P::SLOTS;
-
-    const int32_t *ga_col = A.col + a0, *gb_col = B.col + b0;
-    const float *ga_val = A.val + a0, *gb_val = B.val + b0;
-    const int ha = head_elems(ga_col), hb = head_elems(gb_col);
-    const int oa = (4 - ha) & 3;                 // word of A's entry 0
-    const int ob = (oa + na + 3) & ~3;           // first word of B's region
-    const int obv = ob + ((4 - hb) & 3);         // word of B's entry 0
-    const int scan_end = (obv + nb + 3) & ~3;
-    uint32_t *kx = keys + oa, *ky = keys + obv;
-
-    // ---- stage the tile. One thread hands the 16-byte-aligned interior of each array to the
-    // copy engine; a few other threads load the ragged ends (at most 3 entries each side).
-    // Value arrays whose alignment differs from their column arrays' take plain loads.
-    const bool va_bulk = !WRITES || head_elems(ga_val) == ha, vb_bulk = !WRITES || head_elems(gb_val) == hb;
-    const int head_a = min(na, ha), head_b = min(nb, hb);
-    const int nva = (na - head_a) >> 2, nvb = (nb - head_b) >> 2;  // 16-byte vectors in the interior
-    if (tid == 0) {
-        s_hurry = 0;
-        uint32_t bytes = 16u * (uint32_t)(nva + nvb);
-        if (WRITES) bytes += (va_bulk ? 16u * nva : 0u) + (vb_bulk ? 16u * nvb : 0u);
-        mbar_arrive_expect_tx(mbar, bytes);
-        if (nva) bulk_load(kx + head_a, ga_col + head_a, 16u * nva, mbar);
-        if (nvb) bulk_load(ky + head_b, gb_col + head_b, 16u * nvb, mbar);
-        if (WRITES && va_bulk && nva) bulk_load(vals + oa + head_a, ga_val + head_a, 16u * nva, mbar);
-        if (WRITES && vb_bulk && nvb) bulk_load(vals + obv + head_b, gb_val + head_b, 16u * nvb, mbar);
-    }
-    if (tid >= 32 && tid < 32 + 12) {  // ragged ends: 3 head + 3 tail slots for A, then for B
-        const int k = tid - 32;
-        const bool is_b = k >= 6;
-        const int e = is_b ? k - 6 : k;
-        const int count = is_b ? nb : na, head = is_b ? head_b : head_a, nv = is_b ? nvb : nva;
-        const int idx = e < 3 ? e : head + 4 * nv + (e - 3);
-        const bool live = e < 3 ? e < head : idx < count;
-        if (live) {
-            const int w = (is_b ? obv : oa) + idx;
-            keys[w] = (uint32_t)ld_nc((is_b ? gb_col : ga_col) + idx);
-            if (WRITES && (is_b ? vb_bulk : va_bulk)) vals[w] = ld_nc((is_b ? gb_val : ga_val) + idx);
-        }
-    }
-    if (WRITES && !va_bulk && !scan_warp) for (int i = tid; i < na; i += NT) vals[oa + i] = ld_nc(ga_val + i);
-    if (WRITES && !vb_bulk && !scan_warp) for (int i = tid; i < nb; i += NT) vals[obv + i] = ld_nc(gb_val + i);
-    // padding words that precede live keys must read as "no row mark"
-    if (tid >= 64 && tid < 64 + 3) { if (tid - 64 < oa) keys[tid - 64] = 0u; }
-    if (tid >= 68 && tid < 68 + 3) { if (ob + (tid - 68) < obv) keys[ob + (tid - 68)] = 0u; }
-
-    // row offsets of the first row this thread looks after (rows i0+1 .. i1 are spread over the
-    // workers); kept in registers for the row-offset pass at the end
-    const int64_t my_row = (int64_t)i0 + 1 + tid;
-    int32_t my_sa = 0, my_sb = 0;
-    if (!scan_warp && my_row <= i1) {
-        my_sa = ld_nc(A.rp + my_row) - a0;
-        my_sb = ld_nc(B.rp + my_row) - b0;
-    }
-    // ---- the row (relative to i0) that the first key word of this warp's scan region belongs to:
-    // the last row that starts at or before it. Regions that begin with an operand's first entry,
-    // or in padding before it, start from row 0 of the tile.
-    const int w0 = wid * 32 * P::CH;
-    const bool region_in_a = w0 < ob;
-    unsigned carry = 0;
-    if (!scan_warp) {
-        const int pos = region_in_a ? w0 - oa : w0 - obv;
-        if (pos > 0 && i1 > i0) {
-            const int32_t *rp = region_in_a ? A.rp : B.rp;
-            const int32_t start = region_in_a ? a0 : b0;
-            carry = (unsigned)(warp_last_true(i0, i1, [&](int64_t r) { return ld_nc(rp + r) - start <= pos; }) - i0);
-        }
-    }
-    const bool landed = mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);
-    if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
-        if (tid == 0) {
-            if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
-            if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;  // successors must not wait on this tile
-            mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
-        }
-        return;
-    }
-
-    if (scan_warp) {
-        // ---- scan warp: the output base of the tile is the sum of the counts of all earlier
-        // tiles, which does not depend on this tile's own count. So the walk over the
-        // predecessors' words starts now, while the workers are still merging, and is usually
-        // over by the time they know their count.
-        if (MODE != MODE_FUSED) return;
-        const int64_t bse = t == 0 ? 0 : lookback_predecessors<CSR2_LB_DEPTH>(tile_state, t, &ctl->status, CSR2_LB_SLEEP, &s_hurry,
-                                                                             CSR2_LB_HURRY, poll_limit);
-        CountBar::sync();  // the workers have published the tile's count by now
-        const int total = s_total;
-        if (lane == 0) {
-            if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
-            s_base = bse;
-            if (bse >= 0 && t == num_tiles - 1) ctl->total = bse + total;
-        }
-        __syncthreads();
-        return;
-    }
-
-    // ---- mark the first entry of every row that starts inside the tile with its row number
-    // relative to i0, in the bits above the column (max wins where empty rows share a start)
-    for (int64_t r = my_row; r <= i1; r += NT) {
-        const uint32_t rr = (uint32_t)(r - i0);
-        const int sa = r == my_row ? my_sa : ld_nc(A.rp + r) - a0;
-        const int sb = r == my_row ? my_sb : ld_nc(B.rp + r) - b0;
-        if (sa < na) atomicMax(kx + sa, (rr << cbits) | (kx[sa] & cmask));
-        if (sb < nb) atomicMax(ky + sb, (rr << cbits) | (ky[sb] & cmask));
-    }
-    WorkerBar::sync();
-
-    // ---- spread the marks forward (running maximum) so that every key carries its row, and
-    // append the operand bit. Each thread owns CH consecutive words, each warp 32 * CH; A's words
-    // and B's words run separately (a warp's region may hold the end of A and the start of B).
-    {
-        constexpr int NV = P::CH / 4;
-        const int w_base = tid * P::CH;
-        uint4 q[NV];
-        unsigned ma = 0, mb = 0;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int w = w_base + 4 * j;
-            q[j] = w < scan_end ? *reinterpret_cast<const uint4 *>(keys + w) : make_uint4(0, 0, 0, 0);
-            const unsigned m = max(max(q[j].x & ~cmask, q[j].y & ~cmask), max(q[j].z & ~cmask, q[j].w & ~cmask));
-            if (w < ob) ma = max(ma, m); else mb = max(mb, m);
-        }
-        unsigned ea = __shfl_up_sync(FULL_MASK, warp_incl_max(ma), 1), eb = __shfl_up_sync(FULL_MASK, warp_incl_max(mb), 1);
-        if (lane == 0) ea = eb = 0u;
-        if (region_in_a) ea = max(ea, carry << cbits); else eb = max(eb, carry << cbits);
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int w = w_base + 4 * j;
-            const bool in_a = w < ob;
-            const unsigned src = in_a ? 0u : 1u;
-            unsigned run = in_a ? ea : eb;
-            uint4 v = q[j];
-            run = max(run, v.x & ~cmask); v.x = ((run | (v.x & cmask)) << 1) | src;
-            run = max(run, v.y & ~cmask); v.y = ((run | (v.y & cmask)) << 1) | src;
-            run = max(run, v.z & ~cmask); v.z = ((run | (v.z & cmask)) << 1) | src;
-            run = max(run, v.w & ~cmask); v.w = ((run | (v.w & cmask)) << 1) | src;
-            if (in_a) ea = run; else eb = run;
-            if (w < scan_end) *reinterpret_cast<uint4 *>(keys + w) = v;
-        }
-    }
-    WorkerBar::sync();
-
-    // ---- this warp's merged entries [wid STEP_W, (wid + 1) STEP_W) of the tile, as ranges of A
-    // and of B (both cuts keep the two entries of one position together)
-    int x0, y0, x1, y1;
-    warp_merge_cut(kx, na, ky, nb, wid * P::STEP_W, x0, y0);
-    warp_merge_cut(kx, na, ky, nb, (wid + 1) * P::STEP_W, x1, y1);
-    const int ca = x1 - x0, cb = y1 - y0, cnt = ca + cb;
-
-    // ---- merge in registers: slot e of the warp (register e / 32 of lane e % 32) ends up with
-    // the warp's e-th merged key; the all-ones padding collects in the slots from cnt on
-    uint32_t r[V];
-    warp_load_bitonic<V>(r, kx + x0, ca, ky + y0, cb);
-    warp_bitonic_merge<V>(r);
-
-    // Bit j of a mask speaks about slot 32 j + lane. `same`: the slot holds an A entry and the next
-    // slot its B twin; `dup`: the slot holds a B entry whose A twin is the slot before; `from_a`:
-    // the slot holds an A entry (or padding); `live`: the slot holds an entry.
-    const unsigned same = warp_pair_mask<V>(r);
-    const unsigned dup = warp_shift_mask_up(same);
-    unsigned from_a = 0, live = 0;
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        from_a |= (~r[j] & 1u) << j;
-        live |= (unsigned)(32 * j + lane < cnt) << j;
-    }
-    const unsigned emit = OP == OP_UNION ? (live & ~dup) : same;
-
-    // ---- rank the survivors: warp votes per register slot
-    {
-        int run = 0;
-        unsigned my_vote = 0;
-        int my_before = 0;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const unsigned b = __ballot_sync(FULL_MASK, (emit >> j) & 1u);
-            if (lane == j) {
-                my_vote = b;
-                my_before = run;
-            }
-            run += __popc(b);
-        }
-        if (lane < V) {
-            s_vote[wid][lane] = my_vote;
-            s_before[wid][lane] = (unsigned short)my_before;
-        }
-        if (lane == 0) {
-            s_wtotal[wid] = run;
-            s_wstart[wid] = x0 + y0;
-        }
-    }
-    WorkerBar::sync();
-    int total = 0, wbase = 0;  // survivors of the tile, and of the warps before this one
-#pragma unroll
-    for (int w = 0; w < W; ++w) {
-        const int c = s_wtotal[w];
-        wbase += w < wid ? c : 0;
-        total += c;
-    }
-    if (MODE == MODE_COUNT) {
-        if (tid == 0) tile_count[t] = total;
-        return;
-    }
-    if (MODE == MODE_FUSED) {
-        if (tid == 0) {
-            // successors can add this tile's count from here on
-            st_relaxed_gpu(tile_state + t, (t == 0 ? LB_PREFIX : LB_AGGREGATE) | (uint64_t)total);
-            s_total = total;
-            *(volatile int *)&s_hurry = 1;
-        }
-        __threadfence_block();
-        CountBar::arrive();  // the scan warp turns the count into the tile's inclusive prefix
-    }
-
-    // ---- values of the survivors, while the scan warp finishes. A's entries of the warp are in
-    // order, so the A entry of a slot is number (A entries in earlier slots) of the warp's range,
-    // and a slot's B entry -- its own, or the twin of its A entry, which is the next slot -- is
-    // number (slot - A entries before it).
-    float v[V];
-    {
-        const float *pa = vals + oa + x0, *pb = vals + obv + y0;
-        const unsigned lt = (1u << lane) - 1u;
-        int run_a = 0;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const bool fa = (from_a >> j) & 1u, tw = (same >> j) & 1u, em = (emit >> j) & 1u;
-            const unsigned ba = __ballot_sync(FULL_MASK, fa && ((live >> j) & 1u));
-            const int ia = run_a + __popc(ba & lt), ib = 32 * j + lane - ia;
-            run_a += __popc(ba);
-            float x = 0.f;
-            if (em) {
-                if (OP == OP_UNION) {
-                    x = fa ? pa[ia] : pb[ib];
-                    if (tw) x = x + pb[ib];  // an A entry whose twin is the next B entry
-                } else {
-                    x = pa[ia] * pb[ib];
-                }
-            }
-            v[j] = x;
-        }
-    }
-
-    // ---- output base of the tile
-    if (MODE == MODE_FUSED) __syncthreads();
-    const long long base = MODE == MODE_FILL ? (long long)tile_count[t] : s_base;
-    if (base < 0) return;  // a bounded wait gave up; the host reports it
-
-    // ---- store the survivors, coalesced: the emitting lanes of one register slot write
-    // consecutive result entries
-    {
-        int32_t *gz_col = Z.col + base + wbase;
-        float *gz_val = Z.val + base + wbase;
-        const unsigned lt = (1u << lane) - 1u;
-        int run = 0;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const unsigned b = __ballot_sync(FULL_MASK, (emit >> j) & 1u);
-            if ((emit >> j) & 1u) {
-                const int p = run + __popc(b & lt);
-                gz_col[p] = (int32_t)((r[j] >> 1) & cmask);
-                gz_val[p] = v[j];
-            }
-            run += __popc(b);
-        }
-    }
-
-    // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
-    // tile those are the survivors among the first d = (A entries before row r) + (B entries
-    // before row r) merged entries: whole warps, whole register slots of the warp that holds
-    // merged position d, and the lanes below d's in its slot. The tile owns rows i0+1 .. i1 (the
-    // next tile's first row).
-    for (int64_t rw = my_row; rw <= i1; rw += NT) {
-        const int sa = rw == my_row ? my_sa : ld_nc(A.rp + rw) - a0;
-        const int sb = rw == my_row ? my_sb : ld_nc(B.rp + rw) - b0;
-        const int d = sa + sb;
-        int before = total;
-        if (d < n) {
-            int w = min(d / P::STEP_W, W - 1);
-            if (s_wstart[w] > d) --w;  // a cut moved by one to keep a pair together
-            before = 0;
-            for (int q = 0; q < w; ++q) before += s_wtotal[q];
-            const int e = d - s_wstart[w];
-            before += s_before[w][e >> 5] + __popc(s_vote[w][e >> 5] & ((1u << (e & 31)) - 1u));
-        }
-        Z.rp[rw] = (int32_t)(base + before);
-    }
-    if (t == 0 && tid == 0) Z.rp[0] = 0;
-}
-
 template <int V, int OP, int MODE>
 __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __grid_constant__ CsrIn A, const __grid_constant__ CsrIn B,
                                                                          const __grid_constant__ Cuts cuts, int cbits, int32_t *tile_count,
@@ -1072,43 +661,22 @@ __global__ void __launch_bounds__(NT + 32, CSR2_MIN_CTAS) k_csr2_tile(const __gr
     const uint64_t nr = (uint64_t)(cuts.row[t + 1] - cuts.row[t]) + 1;
     const bool narrow = cbits < 31 && (nr << cbits) < 0x7fffffffull;
     if (narrow) {
-#if CSR2_BODY == 0
         csr2_tile_blocked<V, OP, MODE>(A, B, cuts, cbits, t, num_tiles, tile_count, tile_state, ctl, Z, smem_raw, &mbar, poll_limit);
-#else
-        csr2_tile_warp<V, OP, MODE>(A, B, cuts, cbits, t, num_tiles, tile_count, tile_state, ctl, Z, smem_raw, &mbar, poll_limit);
-#endif
     } else {
         if (threadIdx.x >= NT) return;  // the wide-key body works with the NT worker threads alone
-        csr2_tile_wide<WideVt<V>::value, OP, MODE>(A, B, cuts, t, tile_count, tile_state, ctl, Z, smem_raw, num_tiles, poll_limit);
+        csr2_tile_wide<V, OP, MODE>(A, B, cuts, t, tile_count, tile_state, ctl, Z, smem_raw, num_tiles, poll_limit);
     }
 }
 
 // ------------------------------------------------------------------------ host driver ----
 
 constexpr int V_CSR2 = CSR2_V;
-constexpr int TILE_STEP = TilePlan<V_CSR2>::TILE_STEP;
+constexpr int TILE_STEP = NT * V_CSR2 - 1;  // merged entries between two tile cuts
 
 // Dynamic shared memory of the tile kernel: the staging arrays of the common body, or the 64-bit
 // keys of the wide-key body, whichever is larger.
 constexpr size_t csr2_smem_bytes() {
-#if CSR2_BODY == 0
-    constexpr size_t body = BlockedPlan<V_CSR2>::BYTES;
-#else
-    constexpr size_t body = WarpPlan<V_CSR2>::BYTES;
-#endif
-    return std::max<size_t>(body, 8 * (size_t)(NT * WideVt<V_CSR2>::value + 2 + WideVt<V_CSR2>::value));
-}
-
-int col_bits(int32_t cols) {
-    int b = 1;
-    while (b < 32 && (int64_t(1) << b) < (int64_t)cols) ++b;
-    return b;
-}
-
-int check_csr(const nb200_csr *m, bool need_arrays) {
-    if (!m || m->rows < 0 || m->cols < 0 || m->nnz < 0) return NB200_E_BADARG;
-    if (need_arrays && (!m->row_ptr || (m->nnz > 0 && (!m->col || !m->val)))) return NB200_E_BADARG;
-    return NB200_OK;
+    return std::max<size_t>(BlockedPlan<V_CSR2>::BYTES, 8 * (size_t)(NT * V_CSR2 + 2 + V_CSR2));
 }
 
 // Raises the tile kernel's dynamic shared-memory limit once per instantiation and device.
@@ -1305,7 +873,8 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     return NB200_OK;
 }
 
-// Three-operand add Z = (A + B) + C. The association is the reference's
+// Three-operand add Z = (A + B) + C as two chained unions (the fused kernel is in csr_add3.cu; this
+// is its fallback). The association is the reference's
 // (src/backend/compute.cpp:426-432 builds a + b first), so running the two-operand union twice
 // gives bit-identical values to the reference's fused three-way merge: positions present in A
 // and C only hold a + c, in B and C only b + c, in all three (a + b) + c, and explicit zeros
@@ -1422,6 +991,11 @@ int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_
 
 }  // namespace
 
+int csr_add3_chained(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z, bool alloc, int64_t capacity,
+                     void *stream_v) {
+    return csr_add3_run(a, b, c, z, alloc, capacity, stream_v);
+}
+
 }  // namespace nb200
 
 using namespace nb200;
@@ -1442,16 +1016,6 @@ int nb200_csr_mul_f32(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int3
 
 int nb200_csr_mul_f32_into(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {
     return csr2_run<OP_INTERSECT>(a, b, z, false, capacity, stream);
-}
-
-int nb200_csr_add_3_f32(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z, int32_t, int32_t,
-                        void *stream) {
-    return csr_add3_run(a, b, c, z, true, 0, stream);
-}
-
-int nb200_csr_add_3_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z,
-                             int64_t capacity, void *stream) {
-    return csr_add3_run(a, b, c, z, false, capacity, stream);
 }
 
 int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity, void *stream) {

@@ -102,9 +102,40 @@ def csf3_levels(coordinates):
             np.append(ij_starts, n), c[:, 2])
 
 
+def csf3_levels_device(i, j, k):
+    """The same level arrays built on the device from three CUDA coordinate tensors (sorted unique
+    (i, j, k)): neighbour compares, ``nonzero`` and gathers, no host round trip. Returns int32 CUDA
+    tensors (i_idx, j_ptr, j_idx, k_ptr, k_idx)."""
+    n = i.numel()
+    dev = i.device
+    i32 = lambda t: t.to(torch.int32).contiguous()
+    if n == 0:
+        z = torch.zeros(0, dtype=torch.int32, device=dev)
+        one = torch.zeros(1, dtype=torch.int32, device=dev)
+        return z, one, z.clone(), one.clone(), z.clone()
+    new_ij = torch.ones(n, dtype=torch.bool, device=dev)
+    new_ij[1:] = (i[1:] != i[:-1]) | (j[1:] != j[:-1])
+    ij_starts = torch.nonzero(new_ij).squeeze(1)
+    ij_i = i[ij_starts]
+    new_i = torch.ones(ij_starts.numel(), dtype=torch.bool, device=dev)
+    new_i[1:] = ij_i[1:] != ij_i[:-1]
+    i_starts = torch.nonzero(new_i).squeeze(1)
+    end = lambda t, x: torch.cat([t, torch.tensor([x], dtype=t.dtype, device=dev)])
+    return (i32(ij_i[i_starts]), i32(end(i_starts, ij_starts.numel())), i32(j[ij_starts]), i32(end(ij_starts, n)), i32(k))
+
+
 def to_csf3(coordinates, values, shape, device="cuda"):
-    """Sorted, deduplicated (i, j, k) rows -> CSF3_gpu (python/nacho/convert.py:90-118)."""
+    """Sorted, deduplicated (i, j, k) rows -> CSF3_gpu (python/nacho/convert.py:90-118). Coordinates
+    given as a CUDA tensor of shape (n, 3) are turned into level arrays on the device; numpy arrays
+    and CPU tensors take the host path, like the reference."""
     dev = _gpu_only(device)
+    if isinstance(coordinates, torch.Tensor) and coordinates.is_cuda:
+        c = coordinates.to(dev)
+        levels = csf3_levels_device(c[:, 0].contiguous(), c[:, 1].contiguous(), c[:, 2].contiguous())
+        vals = values if isinstance(values, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(values))
+        return _ext.CSF3_gpu(*levels, vals.to(dtype=torch.float32, device=dev).contiguous(), torch.tensor(list(shape), dtype=torch.int32))
+    if isinstance(coordinates, torch.Tensor):
+        coordinates = coordinates.numpy()
     i_idx, j_ptr, j_idx, k_ptr, k_idx = csf3_levels(coordinates)
     return _ext.CSF3_gpu(
         _tensor(i_idx, torch.int32, dev),

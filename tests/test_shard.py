@@ -22,6 +22,18 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def test_device_cuts_equal_host_cuts():
+    """row_block_cuts_device (torch.searchsorted on the tensors' device) returns the host version's cuts."""
+    for sigma, parts in ((0, 2), (2, 3), (3, 8), (3, 1)):
+        ta = synth.c3_csr(0, sigma, rows=4096, cols=1 << 16, nnz=1 << 16)
+        tb = synth.c3_csr(1, sigma, rows=4096, cols=1 << 16, nnz=1 << 16)
+        host = shard.row_block_cuts([ta[2].numpy(), tb[2].numpy()], parts)
+        assert shard.row_block_cuts_device([ta[2], tb[2]], parts) == host
+    # a view that does not start at zero (a block of a larger matrix)
+    rp = torch.arange(100, 1101, 10, dtype=torch.int32)
+    assert shard.row_block_cuts_device([rp, rp], 4) == shard.row_block_cuts([rp.numpy(), rp.numpy()], 4)
+
+
 def test_row_block_cuts_balance_and_edges():
     a = synth_csr(synth.c3_csr(0, 3, rows=4096, cols=1 << 16, nnz=1 << 16))
     b = synth_csr(synth.c3_csr(1, 3, rows=4096, cols=1 << 16, nnz=1 << 16))
