@@ -174,9 +174,10 @@ int nb200_csr_add_f32_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr 
 /* Asynchronous forms of add and multiply: like the _into forms with a capacity of at least the
  * worst case (nnz(A) + nnz(B) for add, min(nnz(A), nnz(B)) for multiply; less returns
  * NB200_E_CAPACITY), but the call returns as soon as its kernels are queued. The result length and
- * the device-side status arrive, in stream order, in two int64 DEVICE words:
+ * the device-side status arrive, in stream order, in three int64 DEVICE words:
  * device_result[0] = nnz(Z), device_result[1] = an nb200_status (NB200_OK, NB200_E_TIMEOUT or
- * NB200_E_OVERFLOW). z->nnz is left 0. For callers that consume the length on the device -- a
+ * NB200_E_OVERFLOW), device_result[2] = the row count (so that the three words are a row block's
+ * whole contribution to a stitch and can be all-gathered as they are). z->nnz is left 0. For callers that consume the length on the device -- a
  * multi-GPU stitch that all-gathers the block lengths, a pipeline that launches the next operator
  * from the same stream -- and must not stall the host once per call. The reference has no
  * counterpart: its drivers read every length back (src/backend/stitch_and_generate_gpu.cpp:660-671). */

@@ -716,11 +716,14 @@ cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cb
     return cudaGetLastError();
 }
 
-// Copies the control block's total and status into two device words the caller reads later
-// ({result entries, device status}), so that a call can return without waiting for the GPU.
-__global__ void k_publish_result(const FusedCtl *ctl, int64_t *out) {
+// Copies the control block's total and status into device words the caller reads later
+// ({result entries, device status, rows}), so that a call can return without waiting for the GPU.
+// The row count rides along so that the three words are a block's whole contribution to a
+// multi-GPU stitch: they can be handed to an all-gather as they are.
+__global__ void k_publish_result(const FusedCtl *ctl, int64_t rows, int64_t *out) {
     out[0] = ctl->total;
     out[1] = ctl->status.error != 0 ? NB200_E_TIMEOUT : (ctl->total > INT32_MAX ? NB200_E_OVERFLOW : NB200_OK);
+    out[2] = rows;
 }
 
 // Shared driver of add and multiply. When `alloc` is set the result arrays are allocated
@@ -772,7 +775,10 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     };
     if (num_tiles == 0) {  // both operands empty: all-zero offsets, nothing else
         cudaError_t e = cudaMemsetAsync(z->row_ptr, 0, sizeof(int32_t) * ((size_t)rows + 1), stream);
-        if (e == cudaSuccess && device_result) e = cudaMemsetAsync(device_result, 0, 2 * sizeof(int64_t), stream);
+        if (e == cudaSuccess && device_result) {
+            const int64_t words[3] = {0, NB200_OK, rows};  // copied before the call returns: pageable source
+            e = cudaMemcpyAsync(device_result, words, sizeof(words), cudaMemcpyHostToDevice, stream);
+        }
         if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
         return NB200_OK;
     }
@@ -802,7 +808,12 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     const int cbits = col_bits(a->cols);
     // NACHO_B200_TWO_PASS=1 forces the count -> scan -> fill route (for comparisons).
     static const bool force_two_pass = [] { const char *e = std::getenv("NACHO_B200_TWO_PASS"); return e && e[0] == '1'; }();
-    const bool fused = alloc || device_result || (capacity >= bound && !force_two_pass);
+    // NACHO_B200_EXACT_ALLOC=1 makes the allocating entry points count first and allocate col / val at
+    // exactly nnz(Z), as the reference's drivers do (src/backend/stitch_and_generate.cpp:438-527),
+    // instead of at the worst case: for callers short of memory, at the price of a second read of
+    // the operands' columns.
+    static const bool exact_alloc = [] { const char *e = std::getenv("NACHO_B200_EXACT_ALLOC"); return e && e[0] == '1'; }();
+    const bool fused = device_result || (alloc ? !exact_alloc : (capacity >= bound && !force_two_pass));
     cudaError_t e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * (fused ? (size_t)num_tiles + 4 : 4), stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
     if (fused && alloc && bound > 0) {
@@ -833,7 +844,8 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
         e = launch_tile<OP, MODE_FUSED>(A, B, cuts, cbits, nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream, knobs);
         if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fused>"));
         if (device_result) {
-            k_publish_result<<<1, 1, 0, stream>>>(ctl, device_result);
+            LaunchScope scope("csr2_publish", stream);
+            k_publish_result<<<1, 1, 0, stream>>>(ctl, rows, device_result);
             e = cudaGetLastError();
             if (e != cudaSuccess) return fail(note_cuda_error(e, "k_publish_result"));
             return NB200_OK;
@@ -865,7 +877,15 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
     if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
     z->nnz = (int32_t)h.total;
-    if (h.total > capacity) return NB200_E_CAPACITY;
+    if (alloc) {
+        if (h.total > 0) {
+            e = cudaMallocAsync(reinterpret_cast<void **>(&z->col), sizeof(int32_t) * (size_t)h.total, stream);
+            if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&z->val), sizeof(float) * (size_t)h.total, stream);
+            if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMallocAsync"));
+        }
+    } else if (h.total > capacity) {
+        return NB200_E_CAPACITY;
+    }
     e = launch_tile<OP, MODE_FILL>(A, B, cuts, cbits, tile_count, nullptr, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fill>"));
     if ((st = read_ctl(h))) return fail(st);

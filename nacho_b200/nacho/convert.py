@@ -67,6 +67,8 @@ def to_coo(coo, device="cuda"):
 
 
 def _tensor(array, dtype, dev):
+    if isinstance(array, torch.Tensor):
+        return array.to(dtype=dtype, device=dev).contiguous()
     return torch.from_numpy(np.ascontiguousarray(array)).to(dtype=dtype, device=dev)
 
 

@@ -262,7 +262,7 @@ class CsrRowBlockOp:
 
         op = CsrRowBlockOp("add", a_block, b_block)      # CSR_gpu row blocks of this rank
         op.launch()                                      # queue operator + stitch; returns at once
-        rows_base, nnz_base, counts = op.bases()         # device tensors; waits on the device only
+        rows_base, nnz_base, counts = op.bases()         # device tensors ((world, 2): rows, nnz); waits on the device only
         z, nnz, status = op.result()                     # host read-back (tests, end of a job)
     """
 
@@ -283,13 +283,12 @@ class CsrRowBlockOp:
         self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.world = dist.get_world_size(group) if self.distributed else 1
         self.rank = dist.get_rank(group) if self.distributed else 0
-        # per launch: [nnz, status] written by the library, and [rows, nnz] sent to the other ranks
-        self._result = [torch.zeros(2, dtype=torch.int64, device=dev) for _ in range(slots)]
-        self._mine = [torch.zeros(2, dtype=torch.int64, device=dev) for _ in range(slots)]
-        self._gathered = [torch.zeros(2 * self.world, dtype=torch.int64, device=dev) for _ in range(slots)]
+        # per launch: [nnz, status, rows] written by the library -- a block's whole contribution to the
+        # stitch, all-gathered as it is -- and every rank's three words
+        self._result = [torch.zeros(3, dtype=torch.int64, device=dev) for _ in range(slots)]
+        self._gathered = [torch.zeros(3 * self.world, dtype=torch.int64, device=dev) for _ in range(slots)]
         self._pending = [None] * slots
         self._n = 0
-        self._rows_t = torch.tensor([self.rows], dtype=torch.int64, device=dev)
 
     def launch(self):
         C = self._C
@@ -304,9 +303,7 @@ class CsrRowBlockOp:
             status = self._entry(C.byref(sa), C.byref(sb), C.byref(sz), self.capacity, self._result[k].data_ptr(), stream)
         self._capi.check(status, "CsrRowBlockOp.launch")
         if self.distributed:
-            self._mine[k][0:1].copy_(self._rows_t)
-            self._mine[k][1:2].copy_(self._result[k][0:1])
-            self._pending[k] = dist.all_gather_into_tensor(self._gathered[k], self._mine[k], group=self.group, async_op=True)
+            self._pending[k] = dist.all_gather_into_tensor(self._gathered[k], self._result[k], group=self.group, async_op=True)
         self._n += 1
         return k
 
@@ -316,11 +313,12 @@ class CsrRowBlockOp:
         k = (self._n - 1) % len(self._result) if slot is None else slot
         if not self.distributed:
             z = torch.zeros(1, dtype=torch.int64, device=self.val.device)
-            return z, z, torch.stack([self._rows_t[0], self._result[k][0]]).view(1, 2)
+            return z, z, torch.stack([self._result[k][2], self._result[k][0]]).view(1, 2)
         if self._pending[k] is not None:
             self._pending[k].wait()
             self._pending[k] = None
-        counts = self._gathered[k].view(self.world, 2)
+        words = self._gathered[k].view(self.world, 3)
+        counts = torch.stack([words[:, 2], words[:, 0]], dim=1)  # (rows, nnz) of every block
         base = counts[: self.rank].sum(dim=0)
         return base[0:1], base[1:2], counts
 
@@ -335,7 +333,7 @@ class CsrRowBlockOp:
         from .nacho import nacho_ext
         k = (self._n - 1) % len(self._result)
         self.drain()
-        nnz, status = (int(x) for x in self._result[k].cpu())
+        nnz, status, _ = (int(x) for x in self._result[k].cpu())
         self._capi.check(status, "CsrRowBlockOp.result")
         z = nacho_ext.CSR_gpu(self.row_ptr, self.col[:nnz], self.val[:nnz], self.a.shape.clone())
         return z, nnz, status

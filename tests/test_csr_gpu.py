@@ -97,6 +97,10 @@ def test_long_runs_of_empty_rows(nacho, oracle):
     ga, gb = csr_to_gpu(a), csr_to_gpu(b)
     assert_same(csr_from_gpu(nacho.gpu_csr_add_f32(ga, gb)), oracle.csr_add(a, b, 8), "empty runs add")
     assert_same(csr_from_gpu(nacho.gpu_csr_mul_f32(ga, ga)), oracle.csr_mul(a, a, 8), "empty runs mul")
+    # the fused three-operand kernel has no wide-key body: it reports the tile and the call reruns
+    # on the chained two-operand route
+    c = make(3)
+    assert_same(csr_from_gpu(nacho.gpu_csr_add_3_f32(ga, gb, csr_to_gpu(c))), oracle.csr_add_3(a, b, c, 8), "empty runs add3")
 
 
 def test_full_size_properties(nacho):
@@ -188,7 +192,7 @@ def test_allocating_add_3_entry_point(nacho, csr_golden):
 
 
 def test_async_entry_points_leave_the_length_on_the_device(nacho, csr_golden):
-    """nb200_csr_{add,mul}_f32_async return without waiting; length and status arrive in two device words."""
+    """nb200_csr_{add,mul}_f32_async return without waiting; length, status and row count arrive in three device words."""
     import torch
     from nacho_b200 import _capi
     from nacho_b200._capi import CsrStruct, check, lib
@@ -201,12 +205,12 @@ def test_async_entry_points_leave_the_length_on_the_device(nacho, csr_golden):
             rp = torch.empty(a.rows + 1, dtype=torch.int32, device="cuda")
             col = torch.empty(max(cap, 1), dtype=torch.int32, device="cuda")
             val = torch.empty(max(cap, 1), dtype=torch.float32, device="cuda")
-            res = torch.full((2,), -1, dtype=torch.int64, device="cuda")
+            res = torch.full((3,), -1, dtype=torch.int64, device="cuda")
             z = CsrStruct(a.rows, a.cols, 0, rp.data_ptr(), col.data_ptr(), val.data_ptr())
             sa, sb = ga._struct(), gb._struct()
             check(fn(C.byref(sa), C.byref(sb), C.byref(z), cap, res.data_ptr(), None), tag)
-            n, status = (int(x) for x in res.cpu())
-            assert status == _capi.OK and n == len(want.col)
+            n, status, rows = (int(x) for x in res.cpu())
+            assert status == _capi.OK and n == len(want.col) and rows == a.rows
             got = CSR(a.rows, a.cols, rp.cpu().numpy(), col[:n].cpu().numpy(), val[:n].cpu().numpy())
             assert_same(got, want, f"{case} {tag} (async)")
             if cap > 0:  # a capacity below the worst case is refused: this form cannot count first
@@ -259,6 +263,46 @@ def test_two_pass_route_with_exact_capacity(nacho, csr_golden, case):
         torch.cuda.synchronize()
         got = CSR(a.rows, a.cols, rp.cpu().numpy(), col[:n].cpu().numpy(), val[:n].cpu().numpy())
         assert_same(got, want, f"{case} {tag} (two-pass)")
+
+
+def test_env_knobs_in_a_child_process(tmp_path):
+    """NACHO_B200_EXACT_ALLOC=1 (the allocating entry points count first and allocate exactly nnz, as
+    the reference's drivers do) and NACHO_B200_ADD3_CHAINED=1 (the three-operand add as two chained
+    unions): both read once per process, both must give the golden results."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "knobs.py"
+    script.write_text(f'''
+import ctypes as C, sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, {os.path.join(root, "tests")!r})
+import numpy as np, torch
+import test_csr_gpu as t
+from helpers import assert_same, csr_from_gpu, csr_to_gpu, golden_csr
+from nacho_b200 import nacho
+from nacho_b200._capi import CsrStruct, check, lib
+from oracle.cpu_oracle import CSR
+g = np.load({os.path.join(root, "tests", "golden", "csr_golden.npz")!r})
+for case in ("smoke", "medium", "all_empty", "giant_row", "cancel"):
+    a, b, c = (golden_csr(g, case, tag) for tag in ("a", "b", "c"))
+    ga, gb, gc = csr_to_gpu(a), csr_to_gpu(b), csr_to_gpu(c)
+    for fn, tag in ((lib.nb200_csr_add_f32, "add"), (lib.nb200_csr_mul_f32, "mul")):
+        z = CsrStruct()
+        sa, sb = ga._struct(), gb._struct()
+        check(fn(C.byref(sa), C.byref(sb), C.byref(z), 256, 256, None), tag)
+        torch.cuda.synchronize()
+        got = CSR(z.rows, z.cols, t._d2h(z.row_ptr, z.rows + 1, np.int32), t._d2h(z.col, z.nnz, np.int32), t._d2h(z.val, z.nnz, np.float32))
+        assert_same(got, golden_csr(g, case, tag), case + " " + tag + " (exact allocation)")
+        assert (z.nnz > 0) == bool(z.col) == bool(z.val)
+        for p in (z.row_ptr, z.col, z.val):
+            check(lib.nb200_free_async(p, None), "free")
+    assert_same(csr_from_gpu(nacho.gpu_csr_add_3_f32(ga, gb, gc)), golden_csr(g, case, "add3"), case + " add3 (chained)")
+print("knobs ok")
+''')
+    env = dict(os.environ, NACHO_B200_EXACT_ALLOC="1", NACHO_B200_ADD3_CHAINED="1")
+    r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "knobs ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
 
 def test_capacity_and_argument_errors(nacho, csr_golden):
