@@ -245,6 +245,17 @@ int nb200_spgemm_f32_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr 
 int nb200_spgemm_f32_numeric(const nb200_csr *a, const nb200_csr *b, nb200_csr *c,
                              void *stream);
 
+/* Masked SpGEMM: Z_ik = sum_j a_ij * b_jk * c_ik on the positions the mask C stores and at least
+ * one product reaches (explicit zeros kept, columns in C's order). Replaces
+ * sssmm::sssmm_gpu_i32_f32 (compiler.cpp:150-153). The mask drives the accumulation: every product
+ * looks its column up in C's row and is added -- as (a * b) * c, the reference's expression -- to
+ * that position or dropped, so nothing outside the mask is formed; float32 atomics in arrival
+ * order, as the reference's compress. z->row_ptr holds rows(A) + 1 entries; `capacity` entries in
+ * z->col / z->val, nnz(C) always suffices (less returns NB200_E_CAPACITY with z->nnz filled in).
+ * Scratch: 8 bytes per entry of C. */
+int nb200_sssmm_f32_into(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_csr *z,
+                         int64_t capacity, void *stream);
+
 /* ---- 3-mode tensor add ------------------------------------------------------------------ */
 
 /* Z = A + B over lexicographically sorted unique (i, j, k). Replaces

@@ -75,6 +75,7 @@ PROTOTYPES = {
     "nb200_csr_add_3_f32": (C.c_int, [_P(CsrStruct)] * 4 + [C.c_int32, C.c_int32, C.c_void_p]),
     "nb200_csr_add_3_f32_into": (C.c_int, [_P(CsrStruct)] * 4 + [C.c_int64, C.c_void_p]),
     "nb200_spgemm_f32": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),
+    "nb200_sssmm_f32_into": (C.c_int, [_P(CsrStruct)] * 4 + [C.c_int64, C.c_void_p]),
     "nb200_spgemm_f32_symbolic": (C.c_int, [_P(CsrStruct)] * 3 + [_P(C.c_int64), C.c_void_p]),
     "nb200_spgemm_f32_numeric": (C.c_int, [_P(CsrStruct)] * 3 + [C.c_void_p]),
     "nb200_coo3d_add_f32": (C.c_int, [_P(Coo3Struct)] * 3 + [C.c_int32, C.c_int32, C.c_void_p]),

@@ -461,7 +461,20 @@ def gpu_inner_prod_coo_f32(a: COO3_gpu, b: COO3_gpu, num_blocks: int = 256, thre
 
 
 def gpu_sssmm_f32(a: CSR_gpu, b: CSR_gpu, c: CSR_gpu, num_blocks: int = 256, threads_per_block: int = 256) -> CSR_gpu:
-    """Z_ik = c_ik * sum_j a_ij * b_jk on the positions C stores (masked SpGEMM, compiler.cpp:150-153):
-    the expand-sort-compress product followed by the intersection with the mask, both on the GPU.
-    (Two calls of the library, not one fused kernel: the product is formed in full first.)"""
-    return gpu_csr_mul_f32(gpu_spgemm_f32(a, b), c)
+    """Z_ik = sum_j a_ij * b_jk * c_ik on the positions C stores and a product reaches (masked SpGEMM,
+    compiler.cpp:150-153): one fused pass in which the mask drives the accumulation."""
+    for t in (a, b, c):
+        if not isinstance(t, CSR_gpu):
+            raise TypeError("gpu_sssmm_f32: operands must be CSR_gpu")
+    dev = _same_device(a, b, c)
+    sa, sb, sc = a._struct(), b._struct(), c._struct()
+    capacity = sc.nnz
+    with torch.cuda.device(dev):
+        row_ptr = torch.empty(sa.rows + 1, dtype=torch.int32, device=dev)
+        col = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+        val = torch.empty(max(capacity, 1), dtype=torch.float32, device=dev)
+        sz = CsrStruct(sa.rows, sb.cols, 0, row_ptr.data_ptr(), col.data_ptr(), val.data_ptr())
+        status = lib.nb200_sssmm_f32_into(C.byref(sa), C.byref(sb), C.byref(sc), C.byref(sz), capacity, _stream_for(row_ptr))
+    _capi.check(status, "gpu_sssmm_f32")
+    n = int(sz.nnz)
+    return CSR_gpu(row_ptr, col[:n], val[:n], torch.tensor([sz.rows, sz.cols], dtype=torch.int32))

@@ -158,10 +158,18 @@ def test_inner_product_at_scale(nacho):
     assert abs(float(z.values.cpu()[0]) - want) <= bound
 
 
-def test_masked_spgemm(nacho, oracle):
-    """gpu_sssmm_f32: c_ik * sum_j a_ij b_jk on the positions the mask stores that the product reaches."""
+@pytest.mark.parametrize("shape", ["uniform", "rmat", "empty_mask"])
+def test_masked_spgemm(nacho, oracle, shape):
+    """gpu_sssmm_f32: sum_j a_ij b_jk c_ik on the positions the mask stores that the product reaches."""
     from nacho_b200 import synth
-    ta, tb, tc = synth.random_csr(400, 300, 0.03, 91), synth.random_csr(300, 400, 0.03, 92), synth.random_csr(400, 400, 0.05, 93)
+    if shape == "uniform":
+        ta, tb, tc = synth.random_csr(400, 300, 0.03, 91), synth.random_csr(300, 400, 0.03, 92), synth.random_csr(400, 400, 0.05, 93)
+    elif shape == "rmat":   # skewed rows: a few rows hold most of the products; the mask is A's own pattern squared-ish
+        ta = synth.rmat_csr(scale=11, seed=4311)
+        tb = synth.transpose_csr(ta)
+        tc = synth.random_csr(1 << 11, 1 << 11, 0.01, 94)
+    else:
+        ta, tb, tc = synth.random_csr(60, 50, 0.1, 95), synth.random_csr(50, 70, 0.1, 96), synth.random_csr(60, 70, 0.0, 97)
     a, b, c = synth_csr(ta), synth_csr(tb), synth_csr(tc)
     full, v64, abs64, _ = oracle.spgemm(a, b, 4, extras=True)
     z = csr_from_gpu(nacho.gpu_sssmm_f32(csr_to_gpu(a), csr_to_gpu(b), csr_to_gpu(c)))
