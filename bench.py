@@ -83,7 +83,9 @@ WORKLOADS = {
     "c4b_spgemm_laplacian": dict(op="spgemm", fmt="csr"),
     "c5_coo3d_add": dict(op="coo3d_add", fmt="coo3"),
     "c5_csf_add": dict(op="csf_add", fmt="csf3"),
+    "n1_sssmm_rmat": dict(op="sssmm", fmt="csr"),
 }
+RMAT_WORKLOADS = ("c4a_spgemm_rmat", "n1_sssmm_rmat")
 
 
 def make_operands(name: str, rank: int, device, scale: float = 1.0, rmat_scale: int = 16):
@@ -107,6 +109,9 @@ def make_operands(name: str, rank: int, device, scale: float = 1.0, rmat_scale: 
     if name == "c4b_spgemm_laplacian":
         a = synth.laplacian_csr(max(8, int(512 * scale ** 0.5)), device=device)
         return [a, a]
+    if name == "n1_sssmm_rmat":  # the product A, A masked by A, as the reference's sssmm benchmark runs square matrices
+        a = synth.rmat_csr(scale=rmat_scale, seed=4000 + shift, device=device)
+        return [a, a, a]
     if name in ("c5_coo3d_add", "c5_csf_add"):
         return list(synth.c5_pair(nnz=max(1000, int(100_000_000 * scale)), seed=5000 + shift, device=device))
     raise SystemExit(f"unknown workload {name}")
@@ -217,7 +222,7 @@ def cpu_baseline(name: str, operands, steps: int = 3, warmup: int = 1):
     spec = WORKLOADS[name]
     op = spec["op"]
     cores = default_threads()
-    use_ref = Reference.available() and op != "spgemm"
+    use_ref = Reference.available() and op not in ("spgemm", "sssmm")
     if use_ref:
         impl = Reference()
         cores = impl.threads()
@@ -228,7 +233,8 @@ def cpu_baseline(name: str, operands, steps: int = 3, warmup: int = 1):
         impl = Oracle()
         run = {"csr_add": lambda: impl.csr_add(*operands, cores), "csr_mul": lambda: impl.csr_mul(*operands, cores),
                "csr_add_3": lambda: impl.csr_add_3(*operands, cores), "coo3d_add": lambda: impl.coo3_add(*operands, cores),
-               "csf_add": lambda: impl.csf3_add(*operands), "spgemm": lambda: impl.spgemm(*operands, cores)}[op]
+               "csf_add": lambda: impl.csf3_add(*operands), "spgemm": lambda: impl.spgemm(*operands, cores),
+               "sssmm": lambda: impl.csr_mul(impl.spgemm(operands[0], operands[1], cores), operands[2], cores)}[op]
         if op == "csf_add":
             cores = 1
     out = None
@@ -266,7 +272,7 @@ def ref_gpu_baseline(spec, tensors, nbytes, products=None, runs: int = 3):
     if not ReferenceGpu.available():
         return None
     op = spec["op"]
-    if op == "spgemm" and (products is None or products >= (1 << 31) - (1 << 24)):
+    if op in ("spgemm", "sssmm") and (products is None or products >= (1 << 31) - (1 << 24)):
         return {"unavailable": f"{products} products do not fit the reference's int32 product counters"}
     ref = ReferenceGpu()
     if spec["fmt"] == "csr":
@@ -277,7 +283,9 @@ def ref_gpu_baseline(spec, tensors, nbytes, products=None, runs: int = 3):
         tup = [(tuple(int(x) for x in t.shape), t.dim_i_indices, t.dim_j_offsets, t.dim_j_indices, t.dim_k_offsets,
                 t.dim_k_indices, t.values) for t in tensors]
     fn = {"csr_add": ref.csr_add, "csr_mul": ref.csr_mul, "csr_add_3": ref.csr_add_3, "spgemm": ref.spgemm,
-          "coo3d_add": ref.coo3_add, "csf_add": ref.csf3_add}[op]
+          "coo3d_add": ref.coo3_add, "csf_add": ref.csf3_add}.get(op)
+    if fn is None:
+        return {"unavailable": f"the reference's {op} GPU kernel is not among the ones built into oracle/_ref"}
     times = []
     for k in range(runs + 1):  # the first call is the warm-up
         fn(*tup, keep=False)
@@ -306,7 +314,7 @@ def job_config(args, world: int, scaling: str, rows: int, nnz_in: int, nnz_out: 
                          else "L2 flushed (256 MiB fill) before every timed step"),
            "parallelism": (f"{world} row blocks of equal stored entries, all-gather of (rows, nnz) per step" if scaling == "strong"
                            else f"one operand set per rank x{world}, all-gather of (rows, nnz) per step")}
-    if args.workload == "c4a_spgemm_rmat":
+    if args.workload in RMAT_WORKLOADS:
         cfg["rmat_scale"] = args.rmat_scale
     cfg.update(extra or {})
     return cfg
@@ -333,9 +341,9 @@ def run_reference(args):
     ops_np = [to_oracle(spec, t) for t in ops]
     del ops
     base = cpu_baseline(args.workload, ops_np, steps=args.steps, warmup=args.warmup)
-    whole = scale == args.rows_scale and (args.workload != "c4a_spgemm_rmat" or cpu_rmat == args.rmat_scale)
+    whole = scale == args.rows_scale and (args.workload not in RMAT_WORKLOADS or cpu_rmat == args.rmat_scale)
     sample = ("the whole workload" if whole else f"{args.workload} at scale {scale:g} of its rows/entries"
-              + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" else ""))
+              + (f", R-MAT scale {cpu_rmat}" if args.workload in RMAT_WORKLOADS else ""))
     scaling = default_scaling(args, spec)
     config = job_config(args, args.gpus, scaling, base["rows"], base["nnz_in"], base["nnz_out"], base["bytes"])
     if not whole:
@@ -582,6 +590,21 @@ def main():
         barrier()
         dropin_ms = e0.elapsed_time(e1) / k
 
+    # ---- masked product: the unfused route (whole product, then the intersection with the mask) beside it
+    unfused_ms = None
+    if spec["op"] == "sssmm":
+        unfused = lambda: nacho.gpu_csr_mul_f32(nacho.gpu_spgemm_f32(tensors[0], tensors[1]), tensors[2])
+        for _ in range(2):
+            unfused()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(5):
+            unfused()
+        e1.record(stream)
+        barrier()
+        unfused_ms = e0.elapsed_time(e1) / 5
+
     # ---- per-kernel timing, same workload, events on the launching stream
     prof_steps = max(3, min(args.steps, 10))
     _capi.profile_reset()
@@ -657,14 +680,18 @@ def main():
         if kernels:
             top = max(kernels, key=lambda k: kernels[k]["ms_per_step"])
             roof_bytes = nbytes
-            if spec["op"] == "spgemm":
-                # expand-sort-compress model: A once, 8 bytes of B per product, C once
+            if spec["op"] in ("spgemm", "sssmm"):
+                # expand-sort-compress model: A once, 8 bytes of B per product, C once (sssmm: the mask once more)
                 b_len = (ops[1][2][1:] - ops[1][2][:-1]).to(torch.int64)
                 products = int(b_len[ops[0][3].to(torch.int64)].sum())
                 roof_bytes = bytes_csr(*metas[0]) + 8 * products + bytes_csr(*zmeta)
+                if spec["op"] == "sssmm":
+                    roof_bytes += bytes_csr(*metas[2])
                 extra = {"products": products, "esc_model_bytes": roof_bytes}
+                if unfused_ms is not None:
+                    extra["unfused_spgemm_then_csr_mul_ms"] = unfused_ms
             roof_ms, roof_kernel = kernels[top]["ms_per_step"], top
-            if spec["op"] in ("spgemm", "csf_add", "csr_add_3"):
+            if spec["op"] in ("spgemm", "sssmm", "csf_add", "csr_add_3"):
                 # several kernels share the step's bytes (row bins; expand / merge / compress):
                 # the fraction is taken over all of them, not over the longest one alone
                 roof_ms = sum(k["ms_per_step"] for k in kernels.values())
@@ -680,11 +707,11 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             scale = cpu_sample_scale(args.workload, args.cpu_scale) * args.rows_scale
             cpu_rmat = min(args.rmat_scale, 14)  # the CPU port sorts every product; keep its sample bounded
-            same = scale == args.rows_scale and (args.workload != "c4a_spgemm_rmat" or cpu_rmat == args.rmat_scale)
+            same = scale == args.rows_scale and (args.workload not in RMAT_WORKLOADS or cpu_rmat == args.rmat_scale)
             cpu_ops = ops if same else make_operands(args.workload, 0, dev, scale=scale, rmat_scale=cpu_rmat)
             base = cpu_baseline(args.workload, [to_oracle(spec, t) for t in cpu_ops])
             base["sample"] = (("the whole workload" if same else f"{args.workload} at scale {scale:g} of its rows/entries")
-                              + (f", R-MAT scale {cpu_rmat}" if args.workload == "c4a_spgemm_rmat" and not same else "")
+                              + (f", R-MAT scale {cpu_rmat}" if args.workload in RMAT_WORKLOADS and not same else "")
                               + ", mean of 3 runs")
         ref_gpu = None
         if world == 1 and not args.no_ref_gpu:

@@ -4,57 +4,293 @@
 // compress machinery as its SpGEMM (src/backend/stitch_and_generate_gpu.cpp:14-139), on the products
 // that survive the three-way intersection.
 //
-// Here the mask drives the accumulation, so nothing outside it is ever formed:
-//   k_sssmm_accumulate  one CTA per row i. Its warps take the entries a_ij of the row, the lanes of
-//                       a warp the entries b_jk of row j of B; each product looks its column k up in
-//                       the (sorted) columns of row i of C by binary search and, if the mask holds
-//                       it, adds (a_ij * b_jk) * c_ik -- the reference's expression, left to right --
-//                       to that position's accumulator and flags the position. Accumulators and
-//                       flags are two scratch arrays of nnz(C) entries.
-//   k_scan_lookback     exclusive scan of the flags: the result position of every mask position.
-//   k_sssmm_compact     flagged positions move to their result slot (column, value); the result's
+// Here the mask drives the accumulation, so nothing outside it is ever formed, sorted or written:
+//   k_sssmm_classify    one warp per row: does the row have fewer than LIGHT_P products (counted
+//                       only until that is known), and how wide (first to last column) and how
+//                       long is its mask row? The row goes on one of five lists.
+//   k_sssmm_bitmap      rows with many products, one CTA per row taken from a ticket: the mask row
+//                       becomes a bitmap over its column span in shared memory plus, per 64-bit
+//                       word, the count of set bits before it. A product tests one bit; a hit finds
+//                       its position in the mask row as rank + popcount and adds
+//                       (a_ij * b_jk) * c_ik -- the reference's expression, left to right -- to a
+//                       shared-memory accumulator (rows whose mask row is too long for that, or
+//                       whose span needs the whole shared memory, accumulate in global memory).
+//                       Three list classes, by the shared memory a row needs.
+//   k_sssmm_search_*    rows with few products (one warp per row) and rows whose span exceeds the
+//                       largest bitmap (one CTA per row): binary search of the product's column in
+//                       the mask row, float atomics on the global accumulators.
+//   k_scan_lookback     exclusive scan of the "reached" flags: the result position of every mask
+//                       position.
+//   k_sssmm_compact     reached positions move to their result slot (column, value); the result's
 //                       row offsets are the scanned flags at the mask's row starts.
 // The sums are float32 atomics in arrival order, as the reference's compress is for every row.
 #include <algorithm>
 #include <cstring>
 
+#include "block_utils.cuh"
 #include "merge_common.cuh"
 
 namespace nb200 {
 
 namespace {
 
-constexpr int NT = 128;
+constexpr int LIGHT_P = 256;    // rows with fewer products than this are searched by one warp
+constexpr int SEARCH_NT = 128;  // threads of a searching CTA
+// lists: bitmap classes 0..2, wide rows (searched by a CTA), light rows (searched by a warp)
+constexpr int LIST_WIDE = 3, LIST_LIGHT = 4;
+constexpr int WARP_ENTRIES = 8; // entries of A's row one warp of a unit takes
+
+// Work classes. A unit of work is a run of `unit` consecutive entries of one row of A (a row with
+// more entries becomes several units, so a hub row spreads over the SMs), worked by one CTA of
+// `nt` threads. The bitmap classes keep `words` 64-bit bitmap words and `entries` accumulators of
+// the mask row in shared memory: bytes = 12 * words + 5 * entries (bitmap, ranks; sums, flags).
+struct WorkClass {
+    int words, entries, nt;
+    __host__ __device__ constexpr int unit() const { return WARP_ENTRIES * (nt / 32); }
+    constexpr size_t smem() const { return size_t(12) * words + size_t(5) * entries + 16; }
+};
+constexpr WorkClass CLASS[4] = {
+    {1024, 2048, 256},    //  65536 columns of span, 22.5 KB: eight CTAs per SM
+    {4096, 8192, 1024},   // 262144 columns, 88 KB: two CTAs per SM
+    {16384, 0, 1024},     // 2^20 columns, 192 KB, sums in global memory: one CTA per SM
+    {0, 0, SEARCH_NT},    // wider still: no bitmap, binary search
+};
 
 struct CsrView {
     const int32_t *rp, *col;
     const float *val;
 };
 
-__global__ void __launch_bounds__(NT) k_sssmm_accumulate(CsrView A, CsrView B, CsrView C, int32_t rows, float *__restrict__ acc,
-                                                        int32_t *__restrict__ hit) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int32_t c0 = ld_nc(C.rp);  // the mask may be a row block of a larger matrix: positions count from its first entry
-    for (int64_t i = blockIdx.x; i < rows; i += gridDim.x) {
+struct SssmmCtl {
+    int count[8];   // units (light list: rows) on each list
+    int ticket[8];  // next list position to hand out
+};
+
+__global__ void __launch_bounds__(256) k_sssmm_classify(CsrView A, CsrView B, CsrView C, int32_t rows, int64_t list_cap,
+                                                       int2 *__restrict__ units, int32_t *__restrict__ light,
+                                                       SssmmCtl *__restrict__ ctl) {
+    const int lane = lane_id();
+    const int64_t warps = (int64_t)gridDim.x * (256 / 32);
+    for (int64_t i = (int64_t)blockIdx.x * (256 / 32) + warp_id(); i < rows; i += warps) {
         const int32_t c_lo = ld_nc(C.rp + i), c_hi = ld_nc(C.rp + i + 1);
         const int32_t a_lo = ld_nc(A.rp + i), a_hi = ld_nc(A.rp + i + 1);
         if (c_lo == c_hi || a_lo == a_hi) continue;
-        for (int32_t p = a_lo + warp; p < a_hi; p += NT / 32) {
+        unsigned products = 0;  // exact below LIGHT_P, a lower bound beyond
+        for (int32_t p0 = a_lo; p0 < a_hi && products < LIGHT_P; p0 += 32) {
+            unsigned mine = 0;
+            if (p0 + lane < a_hi) {
+                const int32_t j = ld_nc(A.col + p0 + lane);
+                mine = min((unsigned)(ld_nc(B.rp + j + 1) - ld_nc(B.rp + j)), (unsigned)LIGHT_P);
+            }
+            products += __reduce_add_sync(0xffffffffu, mine);
+        }
+        if (products == 0) continue;
+        if (products < LIGHT_P) {
+            if (lane == 0) light[atomicAdd(&ctl->count[LIST_LIGHT], 1)] = (int32_t)i;
+            continue;
+        }
+        const int32_t words = (ld_nc(C.col + c_hi - 1) >> 6) - (ld_nc(C.col + c_lo) >> 6) + 1, entries = c_hi - c_lo;
+        int list = LIST_WIDE;
+        if (words <= CLASS[0].words && entries <= CLASS[0].entries) list = 0;
+        else if (words <= CLASS[1].words && entries <= CLASS[1].entries) list = 1;
+        else if (words <= CLASS[2].words) list = 2;
+        const int unit = list == 0 ? CLASS[0].unit() : list == LIST_WIDE ? CLASS[LIST_WIDE].unit() : CLASS[1].unit();
+        const int n_units = (a_hi - a_lo + unit - 1) / unit;
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&ctl->count[list], n_units);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        for (int u = lane; u < n_units; u += 32) units[list * list_cap + base + u] = make_int2((int)i, a_lo + u * unit);
+    }
+}
+
+// One product column k of the mask row [c_lo, c_hi) by binary search; on a hit the product goes to
+// the global sums.
+__device__ __forceinline__ void search_product(const CsrView &B, const CsrView &C, int32_t q, int32_t k, float av, int32_t c_lo,
+                                               int32_t c_hi, int32_t c0, float *__restrict__ acc, int32_t *__restrict__ hit) {
+    int32_t lo = c_lo, hi = c_hi;  // first position of the mask's row with column >= k
+    while (lo < hi) {
+        const int32_t mid = lo + ((hi - lo) >> 1);
+        if (ld_nc(C.col + mid) < k) lo = mid + 1; else hi = mid;
+    }
+    if (lo < c_hi && ld_nc(C.col + lo) == k) {
+        atomicAdd(acc + (lo - c0), (av * ld_nc(B.val + q)) * ld_nc(C.val + lo));
+        hit[lo - c0] = 1;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_sssmm_search_warp(CsrView A, CsrView B, CsrView C, const int32_t *__restrict__ list,
+                                                          SssmmCtl *__restrict__ ctl, float *__restrict__ acc,
+                                                          int32_t *__restrict__ hit) {
+    const int lane = lane_id();
+    const int32_t c0 = ld_nc(C.rp);  // the mask may be a row block of a larger matrix: positions count from its first entry
+    const int count = ctl->count[LIST_LIGHT];
+    for (;;) {
+        int t = 0;
+        if (lane == 0) t = atomicAdd(&ctl->ticket[LIST_LIGHT], 1);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= count) return;
+        const int64_t i = ld_nc(list + t);
+        const int32_t c_lo = ld_nc(C.rp + i), c_hi = ld_nc(C.rp + i + 1);
+        for (int32_t p = ld_nc(A.rp + i), a_hi = ld_nc(A.rp + i + 1); p < a_hi; ++p) {
             const int32_t j = ld_nc(A.col + p);
             const float av = ld_nc(A.val + p);
-            const int32_t b_lo = ld_nc(B.rp + j), b_hi = ld_nc(B.rp + j + 1);
-            for (int32_t q = b_lo + lane; q < b_hi; q += 32) {
-                const int32_t k = ld_nc(B.col + q);
-                int32_t lo = c_lo, hi = c_hi;  // first position of the mask's row with column >= k
-                while (lo < hi) {
-                    const int32_t mid = lo + ((hi - lo) >> 1);
-                    if (ld_nc(C.col + mid) < k) lo = mid + 1; else hi = mid;
-                }
-                if (lo < c_hi && ld_nc(C.col + lo) == k) {
-                    atomicAdd(acc + (lo - c0), (av * ld_nc(B.val + q)) * ld_nc(C.val + lo));
-                    hit[lo - c0] = 1;
-                }
+            for (int32_t q = ld_nc(B.rp + j) + lane, b_hi = ld_nc(B.rp + j + 1); q < b_hi; q += 32)
+                search_product(B, C, q, ld_nc(B.col + q), av, c_lo, c_hi, c0, acc, hit);
+        }
+    }
+}
+
+// Shared memory of unit_products: the entries of the unit whose row of B is long.
+template <int NT>
+struct LongRows {
+    int n;
+    int32_t at[WARP_ENTRIES * (NT / 32)];  // their positions in A
+};
+
+// The entries of A's row a unit covers, WARP_ENTRIES per warp: lane l of warp w fetches entry
+// p_begin + w + l * (warps) -- column, value and the bounds of B's row, all lanes at once. Rows of B
+// with NT entries or more are worked by the whole CTA first, one after the other (a hub row met by
+// one warp alone would keep the CTA waiting for that warp); then every warp walks its remaining
+// entries, its lanes over B's row. `longs.n` must be 0 and visible to the CTA on entry.
+template <int NT, typename Product>
+__device__ __forceinline__ void unit_products(const CsrView &A, const CsrView &B, int32_t p_begin, int32_t p_end, LongRows<NT> &longs,
+                                              Product product) {
+    constexpr int NW = NT / 32;
+    const int lane = lane_id();
+    const int32_t mine = p_begin + warp_id() + lane * NW;
+    int32_t b_lo = 0, b_hi = 0;
+    float av = 0.0f;
+    if (lane < WARP_ENTRIES && mine < p_end) {
+        const int32_t j = ld_nc(A.col + mine);
+        av = ld_nc(A.val + mine);
+        b_lo = ld_nc(B.rp + j);
+        b_hi = ld_nc(B.rp + j + 1);
+        if (b_hi - b_lo >= NT) {
+            longs.at[atomicAdd(&longs.n, 1)] = mine;
+            b_hi = b_lo;
+        }
+    }
+    __syncthreads();
+    for (int d = 0, n = longs.n; d < n; ++d) {
+        const int32_t p = longs.at[d], j = ld_nc(A.col + p);
+        const float a = ld_nc(A.val + p);
+        const int32_t hi = ld_nc(B.rp + j + 1);
+        for (int32_t q0 = ld_nc(B.rp + j) + (int)threadIdx.x; q0 < hi; q0 += 2 * NT) {
+            const int32_t k0 = ld_nc(B.col + q0), k1 = q0 + NT < hi ? ld_nc(B.col + q0 + NT) : -1;
+            product(q0, k0, a);
+            if (k1 >= 0) product(q0 + NT, k1, a);
+        }
+    }
+#pragma unroll 1
+    for (int e = 0; e < WARP_ENTRIES; ++e) {
+        const int32_t lo = __shfl_sync(0xffffffffu, b_lo, e), hi = __shfl_sync(0xffffffffu, b_hi, e);
+        const float a = __shfl_sync(0xffffffffu, av, e);
+        for (int32_t q0 = lo + lane; q0 < hi; q0 += 128) {
+            int32_t k[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) k[u] = q0 + 32 * u < hi ? ld_nc(B.col + q0 + 32 * u) : -1;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (k[u] >= 0) product(q0 + 32 * u, k[u], a);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(SEARCH_NT) k_sssmm_search_cta(CsrView A, CsrView B, CsrView C, const int2 *__restrict__ units,
+                                                               SssmmCtl *__restrict__ ctl, float *__restrict__ acc,
+                                                               int32_t *__restrict__ hit) {
+    __shared__ LongRows<SEARCH_NT> s_long;
+    const int32_t c0 = ld_nc(C.rp);
+    const int count = ctl->count[LIST_WIDE];
+    for (int t = blockIdx.x; t < count; t += gridDim.x) {
+        if (threadIdx.x == 0) s_long.n = 0;
+        __syncthreads();
+        const int2 unit = units[t];
+        const int64_t i = unit.x;
+        const int32_t c_lo = ld_nc(C.rp + i), c_hi = ld_nc(C.rp + i + 1);
+        unit_products<SEARCH_NT>(A, B, unit.y, min(unit.y + CLASS[LIST_WIDE].unit(), ld_nc(A.rp + i + 1)), s_long,
+                                 [&](int32_t q, int32_t k, float av) { search_product(B, C, q, k, av, c_lo, c_hi, c0, acc, hit); });
+        __syncthreads();
+    }
+}
+
+template <int NT, bool SHARED_ACC>
+__global__ void __launch_bounds__(NT) k_sssmm_bitmap(CsrView A, CsrView B, CsrView C, const int2 *__restrict__ units,
+                                                    SssmmCtl *__restrict__ ctl, int which, int words_cap, int entries_cap,
+                                                    float *__restrict__ acc, int32_t *__restrict__ hit) {
+    extern __shared__ uint64_t sm_words[];
+    uint64_t *bm = sm_words;                                         // bit (k - 64 * w0) set: the mask row stores column k
+    uint32_t *bm32 = reinterpret_cast<uint32_t *>(bm);               // the same bits, for 32-bit shared-memory atomics
+    uint32_t *rank = reinterpret_cast<uint32_t *>(bm + words_cap);   // set bits in front of each 64-bit word
+    float *acc_s = reinterpret_cast<float *>(rank + words_cap);
+    unsigned char *flag_s = reinterpret_cast<unsigned char *>(acc_s + entries_cap);
+    __shared__ int2 s_unit;
+    __shared__ int s_tmp[34];
+    __shared__ LongRows<NT> s_long;
+    const int tid = threadIdx.x;
+    const int32_t c0 = ld_nc(C.rp);
+    const int count = ctl->count[which];
+    for (;;) {
+        if (tid == 0) {
+            const int t = atomicAdd(&ctl->ticket[which], 1);
+            s_unit = t < count ? units[t] : make_int2(-1, 0);
+            s_long.n = 0;
+        }
+        __syncthreads();
+        const int2 unit = s_unit;
+        const int64_t i = unit.x;
+        if (i < 0) return;
+        const int32_t c_lo = ld_nc(C.rp + i), c_hi = ld_nc(C.rp + i + 1);
+        const int32_t w0 = ld_nc(C.col + c_lo) >> 6;
+        const int32_t words = (ld_nc(C.col + c_hi - 1) >> 6) - w0 + 1, entries = c_hi - c_lo;
+        for (int w = tid; w < words; w += NT) bm[w] = 0;
+        if (SHARED_ACC)
+            for (int p = tid; p < entries; p += NT) {
+                acc_s[p] = 0.0f;
+                flag_s[p] = 0;
             }
+        __syncthreads();
+        for (int32_t p = c_lo + tid; p < c_hi; p += NT) {
+            const int32_t k = ld_nc(C.col + p) - (w0 << 6);
+            atomicOr(bm32 + (k >> 5), 1u << (k & 31));
+        }
+        __syncthreads();
+        {   // ranks: every thread counts a run of consecutive words, the CTA scans the runs
+            const int per = (words + NT - 1) / NT;
+            const int w_lo = min(tid * per, words), w_hi = min(w_lo + per, words);
+            int mine = 0, total;
+            for (int w = w_lo; w < w_hi; ++w) mine += __popcll(bm[w]);
+            int before = block_excl_sum<NT>(mine, s_tmp, total);
+            for (int w = w_lo; w < w_hi; ++w) {
+                rank[w] = (uint32_t)before;
+                before += __popcll(bm[w]);
+            }
+        }
+        __syncthreads();
+        unit_products<NT>(A, B, unit.y, min(unit.y + WARP_ENTRIES * (NT / 32), ld_nc(A.rp + i + 1)), s_long, [&](int32_t q, int32_t k, float av) {
+            const int32_t w = (k >> 6) - w0;
+            if ((unsigned)w >= (unsigned)words) return;
+            const uint64_t bits = bm[w];
+            const int sh = k & 63;
+            if (!((bits >> sh) & 1)) return;
+            const int32_t pos = (int32_t)rank[w] + __popcll(bits & ((1ull << sh) - 1));
+            const float v = (av * ld_nc(B.val + q)) * ld_nc(C.val + c_lo + pos);
+            if (SHARED_ACC) {
+                atomicAdd(acc_s + pos, v);
+                flag_s[pos] = 1;
+            } else {
+                atomicAdd(acc + (c_lo - c0 + pos), v);
+                hit[c_lo - c0 + pos] = 1;
+            }
+        });
+        __syncthreads();
+        if (SHARED_ACC) {  // other units of the same row add to the same sums
+            for (int p = tid; p < entries; p += NT)
+                if (flag_s[p]) {
+                    atomicAdd(acc + (c_lo - c0 + p), acc_s[p]);
+                    hit[c_lo - c0 + p] = 1;
+                }
+            __syncthreads();
         }
     }
 }
@@ -99,25 +335,67 @@ int sssmm_run(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_
         NB200_CUDA(cudaMemsetAsync(z->row_ptr, 0, sizeof(int32_t) * ((size_t)rows + 1), stream));
         return NB200_OK;
     }
+    // per device, so set on every call: cheap next to the launches that follow
+    NB200_CUDA(cudaFuncSetAttribute(k_sssmm_bitmap<1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CLASS[1].smem()));
+    NB200_CUDA(cudaFuncSetAttribute(k_sssmm_bitmap<1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CLASS[2].smem()));
+    int device = 0, sms = 148;
+    NB200_CUDA(cudaGetDevice(&device));
+    NB200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+
     const int scan_ctas = (int)(((int64_t)nnz + 1 + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT));
+    const int64_t list_cap = (int64_t)rows + a->nnz / CLASS[LIST_WIDE].unit() + 1;  // the smallest unit bounds every list
     Carver sizes;
     sizes.take<float>((size_t)nnz);
     sizes.take<int32_t>((size_t)nnz + 1);
     sizes.take<uint64_t>((size_t)scan_ctas + 8);
+    sizes.take<SssmmCtl>(1);
+    sizes.take<int2>((size_t)4 * list_cap);
+    sizes.take<int32_t>((size_t)rows);
     Workspace *ws = nullptr;
     if ((st = acquire_workspace(stream, sizes.used(), &ws, 1))) return st;
     Carver carve(ws->dev);
     float *acc = carve.take<float>((size_t)nnz);
     int32_t *hit = carve.take<int32_t>((size_t)nnz + 1);
     uint64_t *scan_block = carve.take<uint64_t>((size_t)scan_ctas + 8);
+    SssmmCtl *sctl = carve.take<SssmmCtl>(1);
+    int2 *units = carve.take<int2>((size_t)4 * list_cap);
+    int32_t *light = carve.take<int32_t>((size_t)rows);
     FusedCtl *ctl = reinterpret_cast<FusedCtl *>(scan_block);
     NB200_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)nnz, stream));
     NB200_CUDA(cudaMemsetAsync(hit, 0, sizeof(int32_t) * ((size_t)nnz + 1), stream));
     NB200_CUDA(cudaMemsetAsync(scan_block, 0, sizeof(uint64_t) * ((size_t)scan_ctas + 4), stream));
+    NB200_CUDA(cudaMemsetAsync(sctl, 0, sizeof(SssmmCtl), stream));
     const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val}, C{c->row_ptr, c->col, c->val};
+    const int row_warps_grid = (int)std::min<int64_t>(((int64_t)rows + 7) / 8, (int64_t)sms * 8);
+    const int most = (int)std::min<int64_t>(list_cap, 1 << 30);
     {
-        LaunchScope scope("sssmm_accumulate", stream);
-        k_sssmm_accumulate<<<std::min<int64_t>(rows, 1 << 20), NT, 0, stream>>>(A, B, C, rows, acc, hit);
+        LaunchScope scope("sssmm_classify", stream);
+        k_sssmm_classify<<<row_warps_grid, 256, 0, stream>>>(A, B, C, rows, list_cap, units, light, sctl);
+    }
+    // Every list is worked by resident CTAs that take units from a ticket; a list's length stays on
+    // the device, so an empty list costs one launch of CTAs that leave at once.
+    {
+        LaunchScope scope("sssmm_bitmap_wide", stream);
+        k_sssmm_bitmap<1024, false><<<std::min(sms, most), 1024, CLASS[2].smem(), stream>>>(A, B, C, units + 2 * list_cap, sctl, 2,
+                                                                                           CLASS[2].words, 0, acc, hit);
+    }
+    {
+        LaunchScope scope("sssmm_bitmap_medium", stream);
+        k_sssmm_bitmap<1024, true><<<std::min(2 * sms, most), 1024, CLASS[1].smem(), stream>>>(A, B, C, units + list_cap, sctl, 1,
+                                                                                              CLASS[1].words, CLASS[1].entries, acc, hit);
+    }
+    {
+        LaunchScope scope("sssmm_bitmap_narrow", stream);
+        k_sssmm_bitmap<256, true><<<std::min(8 * sms, most), 256, CLASS[0].smem(), stream>>>(A, B, C, units, sctl, 0, CLASS[0].words,
+                                                                                            CLASS[0].entries, acc, hit);
+    }
+    {
+        LaunchScope scope("sssmm_search_wide", stream);
+        k_sssmm_search_cta<<<std::min(16 * sms, most), SEARCH_NT, 0, stream>>>(A, B, C, units + (size_t)LIST_WIDE * list_cap, sctl, acc, hit);
+    }
+    {
+        LaunchScope scope("sssmm_search_light", stream);
+        k_sssmm_search_warp<<<row_warps_grid, 256, 0, stream>>>(A, B, C, light, sctl, acc, hit);
     }
     {
         LaunchScope scope("scan_lookback", stream);

@@ -158,7 +158,34 @@ def test_inner_product_at_scale(nacho):
     assert abs(float(z.values.cpu()[0]) - want) <= bound
 
 
-@pytest.mark.parametrize("shape", ["uniform", "rmat", "empty_mask"])
+def mask_classes_case():
+    """A, B, mask with one row for every route of the masked product: mask rows of narrow / medium /
+    wide / beyond-bitmap column span, short and long, a row with few products, empty rows."""
+    import torch
+    rng = np.random.default_rng(977)
+    cols, inner = 1 << 22, 64
+    spans = [(0, 60_000, 1_500), (5_000, 200_000, 5_000), (1_000, 900_000, 20_000), (0, cols, 6_000),
+             (70_000, 120_000, 3_000), (0, 0, 0), (10, 50_000, 40), (300_000, 1_300_000, 9_000)]
+    mask_rows = [np.sort(rng.choice(np.arange(lo, hi), n, replace=False)) if n else np.zeros(0, np.int64) for lo, hi, n in spans]
+    rows = len(spans)
+
+    def tup(r, c, lists):
+        rp = np.zeros(r + 1, np.int32)
+        rp[1:] = np.cumsum([len(x) for x in lists])
+        col = np.concatenate(lists).astype(np.int32)
+        val = rng.uniform(-1, 1, col.size).astype(np.float32)
+        return r, c, torch.from_numpy(rp), torch.from_numpy(col), torch.from_numpy(val)
+
+    # B's rows draw half of their columns from the mask rows, so that products land on the mask
+    pool = np.unique(np.concatenate(mask_rows))
+    b_rows = [np.unique(np.concatenate([rng.choice(pool, 1500), rng.integers(0, cols, 1500)])) for _ in range(inner)]
+    a_rows = [np.sort(rng.choice(inner, n, replace=False)) for n in (20, 30, 25, 40, 20, 10, 0, 35)]
+    a_rows[6] = np.array([3], np.int64)                 # the light row: one A entry ...
+    b_rows[3] = np.sort(rng.choice(mask_rows[6], 30, replace=False))  # ... times a short B row
+    return tup(rows, inner, a_rows), tup(inner, cols, b_rows), tup(rows, cols, mask_rows)
+
+
+@pytest.mark.parametrize("shape", ["uniform", "rmat", "empty_mask", "classes"])
 def test_masked_spgemm(nacho, oracle, shape):
     """gpu_sssmm_f32: sum_j a_ij b_jk c_ik on the positions the mask stores that the product reaches."""
     from nacho_b200 import synth
@@ -168,6 +195,8 @@ def test_masked_spgemm(nacho, oracle, shape):
         ta = synth.rmat_csr(scale=11, seed=4311)
         tb = synth.transpose_csr(ta)
         tc = synth.random_csr(1 << 11, 1 << 11, 0.01, 94)
+    elif shape == "classes":
+        ta, tb, tc = mask_classes_case()
     else:
         ta, tb, tc = synth.random_csr(60, 50, 0.1, 95), synth.random_csr(50, 70, 0.1, 96), synth.random_csr(60, 70, 0.0, 97)
     a, b, c = synth_csr(ta), synth_csr(tb), synth_csr(tc)
