@@ -140,75 +140,82 @@ __global__ void __launch_bounds__(256) k_sssmm_search_warp(CsrView A, CsrView B,
     }
 }
 
-// Shared memory of unit_products: the entries of the unit whose row of B is long.
+constexpr int CHUNK = 128;  // products one warp takes at a time: four loads per lane in flight
+
+// Shared memory of unit_products: for every entry of the unit, the bounds of its row of B, its
+// value, and the number of chunks in front of it.
 template <int NT>
-struct LongRows {
-    int n;
-    int32_t at[WARP_ENTRIES * (NT / 32)];  // their positions in A
+struct UnitRows {
+    static constexpr int E = WARP_ENTRIES * (NT / 32);
+    int32_t lo[E], hi[E], first[E];
+    float av[E];
+    int tmp[34];
 };
 
-// The entries of A's row a unit covers, WARP_ENTRIES per warp: lane l of warp w fetches entry
-// p_begin + w + l * (warps) -- column, value and the bounds of B's row, all lanes at once. Rows of B
-// with NT entries or more are worked by the whole CTA first, one after the other (a hub row met by
-// one warp alone would keep the CTA waiting for that warp); then every warp walks its remaining
-// entries, its lanes over B's row. `longs.n` must be 0 and visible to the CTA on entry.
+// The products of the entries [p_begin, p_end) of A's row, spread evenly over the warps of the CTA:
+// the rows of B the entries select are cut into chunks of CHUNK products, the chunks are numbered
+// through (an exclusive sum over the entries) and warp w takes chunks w, w + warps, ...; a chunk
+// finds its entry by binary search in the shared-memory sums. The columns of a warp's next chunk
+// are requested before the current one is worked. The CTA must be in step on entry; `product(q, k,
+// a)` receives the position in B, the column and A's value.
 template <int NT, typename Product>
-__device__ __forceinline__ void unit_products(const CsrView &A, const CsrView &B, int32_t p_begin, int32_t p_end, LongRows<NT> &longs,
+__device__ __forceinline__ void unit_products(const CsrView &A, const CsrView &B, int32_t p_begin, int32_t p_end, UnitRows<NT> &rows,
                                               Product product) {
     constexpr int NW = NT / 32;
-    const int lane = lane_id();
-    const int32_t mine = p_begin + warp_id() + lane * NW;
-    int32_t b_lo = 0, b_hi = 0;
-    float av = 0.0f;
-    if (lane < WARP_ENTRIES && mine < p_end) {
-        const int32_t j = ld_nc(A.col + mine);
-        av = ld_nc(A.val + mine);
-        b_lo = ld_nc(B.rp + j);
-        b_hi = ld_nc(B.rp + j + 1);
-        if (b_hi - b_lo >= NT) {
-            longs.at[atomicAdd(&longs.n, 1)] = mine;
-            b_hi = b_lo;
-        }
+    const int tid = threadIdx.x, lane = lane_id(), n_e = p_end - p_begin;
+    int chunks = 0;
+    if (tid < n_e) {
+        const int32_t j = ld_nc(A.col + p_begin + tid);
+        const int32_t lo = ld_nc(B.rp + j), hi = ld_nc(B.rp + j + 1);
+        rows.av[tid] = ld_nc(A.val + p_begin + tid);
+        rows.lo[tid] = lo;
+        rows.hi[tid] = hi;
+        chunks = (hi - lo + CHUNK - 1) / CHUNK;
     }
+    int total;
+    const int before = block_excl_sum<NT>(chunks, rows.tmp, total);
+    if (tid < n_e) rows.first[tid] = before;
     __syncthreads();
-    for (int d = 0, n = longs.n; d < n; ++d) {
-        const int32_t p = longs.at[d], j = ld_nc(A.col + p);
-        const float a = ld_nc(A.val + p);
-        const int32_t hi = ld_nc(B.rp + j + 1);
-        for (int32_t q0 = ld_nc(B.rp + j) + (int)threadIdx.x; q0 < hi; q0 += 2 * NT) {
-            const int32_t k0 = ld_nc(B.col + q0), k1 = q0 + NT < hi ? ld_nc(B.col + q0 + NT) : -1;
-            product(q0, k0, a);
-            if (k1 >= 0) product(q0 + NT, k1, a);
+
+    struct Fetched {
+        int32_t k[4], q;
+        float a;
+    };
+    auto fetch = [&](int c, Fetched &f) {
+        int e = 0, above = n_e;  // the last entry whose first chunk is <= c
+        while (above - e > 1) {
+            const int mid = (e + above) >> 1;
+            if (rows.first[mid] <= c) e = mid; else above = mid;
         }
-    }
-#pragma unroll 1
-    for (int e = 0; e < WARP_ENTRIES; ++e) {
-        const int32_t lo = __shfl_sync(0xffffffffu, b_lo, e), hi = __shfl_sync(0xffffffffu, b_hi, e);
-        const float a = __shfl_sync(0xffffffffu, av, e);
-        for (int32_t q0 = lo + lane; q0 < hi; q0 += 128) {
-            int32_t k[4];
+        const int32_t hi = rows.hi[e];
+        f.q = rows.lo[e] + (c - rows.first[e]) * CHUNK + lane;
+        f.a = rows.av[e];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) k[u] = q0 + 32 * u < hi ? ld_nc(B.col + q0 + 32 * u) : -1;
+        for (int u = 0; u < 4; ++u) f.k[u] = f.q + 32 * u < hi ? ld_nc(B.col + f.q + 32 * u) : -1;
+    };
+    Fetched cur, next;
+    int c = warp_id();
+    if (c < total) fetch(c, cur);
+    for (; c < total; c += NW) {
+        if (c + NW < total) fetch(c + NW, next);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (k[u] >= 0) product(q0 + 32 * u, k[u], a);
-        }
+        for (int u = 0; u < 4; ++u)
+            if (cur.k[u] >= 0) product(cur.q + 32 * u, cur.k[u], cur.a);
+        cur = next;
     }
 }
 
 __global__ void __launch_bounds__(SEARCH_NT) k_sssmm_search_cta(CsrView A, CsrView B, CsrView C, const int2 *__restrict__ units,
                                                                SssmmCtl *__restrict__ ctl, float *__restrict__ acc,
                                                                int32_t *__restrict__ hit) {
-    __shared__ LongRows<SEARCH_NT> s_long;
+    __shared__ UnitRows<SEARCH_NT> s_rows;
     const int32_t c0 = ld_nc(C.rp);
     const int count = ctl->count[LIST_WIDE];
     for (int t = blockIdx.x; t < count; t += gridDim.x) {
-        if (threadIdx.x == 0) s_long.n = 0;
-        __syncthreads();
         const int2 unit = units[t];
         const int64_t i = unit.x;
         const int32_t c_lo = ld_nc(C.rp + i), c_hi = ld_nc(C.rp + i + 1);
-        unit_products<SEARCH_NT>(A, B, unit.y, min(unit.y + CLASS[LIST_WIDE].unit(), ld_nc(A.rp + i + 1)), s_long,
+        unit_products<SEARCH_NT>(A, B, unit.y, min(unit.y + CLASS[LIST_WIDE].unit(), ld_nc(A.rp + i + 1)), s_rows,
                                  [&](int32_t q, int32_t k, float av) { search_product(B, C, q, k, av, c_lo, c_hi, c0, acc, hit); });
         __syncthreads();
     }
@@ -225,8 +232,7 @@ __global__ void __launch_bounds__(NT) k_sssmm_bitmap(CsrView A, CsrView B, CsrVi
     float *acc_s = reinterpret_cast<float *>(rank + words_cap);
     unsigned char *flag_s = reinterpret_cast<unsigned char *>(acc_s + entries_cap);
     __shared__ int2 s_unit;
-    __shared__ int s_tmp[34];
-    __shared__ LongRows<NT> s_long;
+    __shared__ UnitRows<NT> s_rows;
     const int tid = threadIdx.x;
     const int32_t c0 = ld_nc(C.rp);
     const int count = ctl->count[which];
@@ -234,7 +240,6 @@ __global__ void __launch_bounds__(NT) k_sssmm_bitmap(CsrView A, CsrView B, CsrVi
         if (tid == 0) {
             const int t = atomicAdd(&ctl->ticket[which], 1);
             s_unit = t < count ? units[t] : make_int2(-1, 0);
-            s_long.n = 0;
         }
         __syncthreads();
         const int2 unit = s_unit;
@@ -260,20 +265,20 @@ __global__ void __launch_bounds__(NT) k_sssmm_bitmap(CsrView A, CsrView B, CsrVi
             const int w_lo = min(tid * per, words), w_hi = min(w_lo + per, words);
             int mine = 0, total;
             for (int w = w_lo; w < w_hi; ++w) mine += __popcll(bm[w]);
-            int before = block_excl_sum<NT>(mine, s_tmp, total);
+            int before = block_excl_sum<NT>(mine, s_rows.tmp, total);
             for (int w = w_lo; w < w_hi; ++w) {
                 rank[w] = (uint32_t)before;
                 before += __popcll(bm[w]);
             }
         }
         __syncthreads();
-        unit_products<NT>(A, B, unit.y, min(unit.y + WARP_ENTRIES * (NT / 32), ld_nc(A.rp + i + 1)), s_long, [&](int32_t q, int32_t k, float av) {
-            const int32_t w = (k >> 6) - w0;
-            if ((unsigned)w >= (unsigned)words) return;
-            const uint64_t bits = bm[w];
-            const int sh = k & 63;
-            if (!((bits >> sh) & 1)) return;
-            const int32_t pos = (int32_t)rank[w] + __popcll(bits & ((1ull << sh) - 1));
+        const int32_t col0 = w0 << 6;
+        const uint32_t span = (uint32_t)words << 6;
+        unit_products<NT>(A, B, unit.y, min(unit.y + WARP_ENTRIES * (NT / 32), ld_nc(A.rp + i + 1)), s_rows, [&](int32_t q, int32_t k, float av) {
+            const uint32_t bit = (uint32_t)(k - col0);
+            if (bit >= span || !((bm32[bit >> 5] >> (bit & 31)) & 1)) return;  // most products end here
+            const uint32_t w = bit >> 6, sh = bit & 63;
+            const int32_t pos = (int32_t)rank[w] + __popcll(bm[w] & ((1ull << sh) - 1));
             const float v = (av * ld_nc(B.val + q)) * ld_nc(C.val + c_lo + pos);
             if (SHARED_ACC) {
                 atomicAdd(acc_s + pos, v);
