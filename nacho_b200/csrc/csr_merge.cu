@@ -777,7 +777,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
         cudaError_t e = cudaMemsetAsync(z->row_ptr, 0, sizeof(int32_t) * ((size_t)rows + 1), stream);
         if (e == cudaSuccess && device_result) {
             const int64_t words[3] = {0, NB200_OK, rows};  // copied before the call returns: pageable source
-            e = cudaMemcpyAsync(device_result, words, sizeof(words), cudaMemcpyHostToDevice, stream);
+            e = cudaMemcpyAsync(device_result, words, sizeof(words), cudaMemcpyDefault, stream);  // the words may be mapped host memory
         }
         if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
         return NB200_OK;

@@ -31,7 +31,11 @@ int64_t block_entries() {
 
 struct Pipeline {
     cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
-    cudaEvent_t loaded[SLOTS] = {}, merged[SLOTS] = {}, drained[SLOTS] = {};
+    cudaEvent_t loaded[SLOTS] = {}, merged[SLOTS] = {}, drained[SLOTS] = {}, counted[SLOTS] = {};
+    // Result words of a block's merge (length, status, rows), four per slot, in pinned host memory
+    // the GPU writes straight into: a length read back with a copy would queue behind the previous
+    // block's device-to-host copy on the copy engine.
+    int64_t *words = nullptr;
     bool ready = false;
     std::mutex busy;  // held for a whole call: the streams, events and device buffers serve one call at a time
 };
@@ -53,7 +57,9 @@ int get_pipeline(Pipeline **out) {
             NB200_CUDA(cudaEventCreateWithFlags(&p.loaded[s], cudaEventDisableTiming));
             NB200_CUDA(cudaEventCreateWithFlags(&p.merged[s], cudaEventDisableTiming));
             NB200_CUDA(cudaEventCreateWithFlags(&p.drained[s], cudaEventDisableTiming));
+            NB200_CUDA(cudaEventCreateWithFlags(&p.counted[s], cudaEventDisableTiming));
         }
+        NB200_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&p.words), sizeof(int64_t) * 4 * SLOTS, cudaHostAllocMapped));
         p.ready = true;
     }
     *out = &p;
@@ -76,7 +82,7 @@ struct SlotArrays {
     float *a_val, *b_val, *z_val;
 };
 
-typedef int (*into_fn)(const nb200_csr *, const nb200_csr *, nb200_csr *, int64_t, void *);
+typedef int (*into_fn)(const nb200_csr *, const nb200_csr *, nb200_csr *, int64_t, int64_t *, void *);  // the asynchronous form
 
 int csr2_host_locked(Pipeline *pipe, into_fn op, bool is_union, const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity);
 
@@ -182,8 +188,14 @@ int csr2_host_locked(Pipeline *pipe, into_fn op, bool is_union, const nb200_csr 
         nb200_csr va{blk.r1 - blk.r0, a->cols, (int32_t)(blk.a1 - blk.a0), d.a_rp, d.a_col - blk.a0, d.a_val - blk.a0};
         nb200_csr vb{blk.r1 - blk.r0, b->cols, (int32_t)(blk.b1 - blk.b0), d.b_rp, d.b_col - blk.b0, d.b_val - blk.b0};
         nb200_csr vz{0, 0, 0, d.z_rp, d.z_col, d.z_val};
-        if ((st = op(&va, &vb, &vz, max_z, pipe->compute))) return st;  // returns once the block's length is known
-        const int64_t n = vz.nnz;
+        volatile int64_t *words = pipe->words + 4 * (k % SLOTS);
+        int64_t *words_dev = nullptr;
+        NB200_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&words_dev), pipe->words + 4 * (k % SLOTS), 0));
+        if ((st = op(&va, &vb, &vz, max_z, words_dev, pipe->compute))) return st;
+        NB200_CUDA(cudaEventRecord(pipe->counted[k % SLOTS], pipe->compute));
+        NB200_CUDA(cudaEventSynchronize(pipe->counted[k % SLOTS]));  // the block's length is known
+        if (words[1] != NB200_OK) return (int)words[1];
+        const int64_t n = words[0];
         if (produced + n > capacity || produced + n > INT32_MAX) {  // the caller drains the streams
             z->nnz = (int32_t)std::min<int64_t>(produced + n, INT32_MAX);
             return produced + n > INT32_MAX ? NB200_E_OVERFLOW : NB200_E_CAPACITY;
@@ -214,11 +226,11 @@ using namespace nb200;
 extern "C" {
 
 int nb200_csr_add_f32_host(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity) {
-    return csr2_host(nb200_csr_add_f32_into, true, a, b, z, capacity);
+    return csr2_host(nb200_csr_add_f32_async, true, a, b, z, capacity);
 }
 
 int nb200_csr_mul_f32_host(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_t capacity) {
-    return csr2_host(nb200_csr_mul_f32_into, false, a, b, z, capacity);
+    return csr2_host(nb200_csr_mul_f32_async, false, a, b, z, capacity);
 }
 
 }  // extern "C"
