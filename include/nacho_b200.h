@@ -117,7 +117,8 @@ typedef struct nb200_dcsr {
 
 int nb200_version(void);
 const char *nb200_strerror(int status);
-/* Text of the last CUDA error seen by the calling thread's most recent failing call. */
+/* Text of the last CUDA error seen by the calling thread's most recent failing call; after
+ * NB200_E_TIMEOUT, which bounded device-side wait gave up and at which tile. */
 const char *nb200_last_cuda_error(void);
 /* Release a result array of an allocating entry point: cudaFreeAsync(p, stream); NULL is
  * ignored. Replaces cudaFreeWrapper (runtime/cuda_utils/cuda_utils.cu:7-11). */

@@ -112,7 +112,7 @@ class NachoB200Error(RuntimeError):
     def __init__(self, status: int, where: str):
         self.status = status
         text = lib.nb200_strerror(status).decode()
-        if status == E_CUDA:
+        if status in (E_CUDA, E_TIMEOUT):
             text += " (" + lib.nb200_last_cuda_error().decode() + ")"
         super().__init__(f"{where}: {text} [status {status}]")
 

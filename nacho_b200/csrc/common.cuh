@@ -15,6 +15,9 @@ namespace nb200 {
 // (NB200_E_NOMEM for allocation failures). Replaces the throwing CHECK_CUDA of
 // runtime/cuda_utils/cuda_utils.h:13-20 with a status code.
 int note_cuda_error(cudaError_t e, const char *what);
+// Records which bounded device-side wait gave up (site code and tile of a DeviceStatus) in the
+// message nb200_last_cuda_error returns; the value is NB200_E_TIMEOUT.
+int note_timeout(int site, int tile, const char *where);
 
 #define NB200_CUDA(call)                                               \
     do {                                                               \

@@ -809,7 +809,7 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
         if (e != cudaSuccess) return fail(note_cuda_error(e, "read result length"));
         FusedCtl h;
         std::memcpy(&h, host_slot, sizeof(h));
-        if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+        if (h.status.error != 0) return fail(note_timeout(h.status.error, h.status.detail, "coo3 merge"));
         if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
         z->nnz = (int32_t)h.total;
         return NB200_OK;
@@ -834,7 +834,7 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
     }
     if (e != cudaSuccess) return note_cuda_error(e, "k_scan_tiles");
     if ((st = read_ctl(h))) return st;
-    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "coo3 merge");
     if (h.total > INT32_MAX) return NB200_E_OVERFLOW;
     z->nnz = (int32_t)h.total;
     if (h.total > capacity) return NB200_E_CAPACITY;
@@ -842,7 +842,7 @@ int coo3_add_run(const nb200_coo3 *a, const nb200_coo3 *b, nb200_coo3 *z, bool a
              : launch_coo3_tile<MODE_FILL>(A, B, pk, cuts, tile_count, nullptr, ctl, Z, num_tiles, stream);
     if (e != cudaSuccess) return note_cuda_error(e, "k_coo3_tile<fill>");
     if ((st = read_ctl(h))) return st;
-    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "coo3 merge");
     return NB200_OK;
 }
 
@@ -903,7 +903,7 @@ int coo3_inner_run(const nb200_coo3 *a, const nb200_coo3 *b, float *z, void *str
     NB200_CUDA(cudaStreamSynchronize(stream));
     FusedCtl h;
     std::memcpy(&h, host_slot, sizeof(h));
-    return h.status.error != 0 ? NB200_E_TIMEOUT : NB200_OK;
+    return h.status.error != 0 ? note_timeout(h.status.error, h.status.detail, "coo3 inner product") : NB200_OK;
 }
 
 }  // namespace nb200

@@ -3,8 +3,9 @@
 // (src/backend/compute.cpp:619-1392 with the runtime-exclusion partition of
 // src/backend/partition.cpp:286-328, 586-811): merge the i lists, under equal i merge the j
 // fibres, under equal (i, j) merge k, otherwise copy the subtree. The result is the unique
-// canonical tree of the union of the coordinate sets, so it is produced here from the flat
-// coordinate merge:
+// canonical tree of the union of the coordinate sets, so it is produced here from flat merges, by
+// one of two routes (two_level_pays chooses; NACHO_B200_CSF_TWO_LEVEL=0 / 1 forces one).
+// Route over expanded coordinates (fibres of about one entry):
 //   1. k_csf_expand    every stored entry gets its (i, j) written out next to its k: one warp
 //                      per 32 (i, j) fibres finds their i by binary search and fills their ranges;
 //   2. coo3_add_run    the sorted-union merge of the two coordinate lists (coo3_merge.cu); k and
@@ -15,7 +16,12 @@
 //                      the merged (i, j) columns: head flags for new i and new (i, j), a packed
 //                      two-counter scan across tiles by bounded look-back, and the scatter of
 //                      i_idx / j_ptr / j_idx / k_ptr.
+// Two-level route (fibres of several entries; described above csf_add_two_level): the fibre lists
+// are merged by the route above, which yields the upper levels and tells which operand holds which
+// fibre; the entries then go through the CSR union with one row per result fibre, so that no
+// per-entry (i, j) is ever written.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "merge_common.cuh"
@@ -187,6 +193,246 @@ __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t 
     }
 }
 
+// The route over expanded coordinates: steps 1-3 of the file comment. `z`'s arrays exist and hold
+// cap_i / cap_j / cap_k entries (cap_k >= n_k(A) + n_k(B)); nothing is freed here on failure.
+int csf_add_expanded(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, int64_t cap_i, int64_t cap_j, int64_t cap_k,
+                     cudaStream_t stream, int slot) {
+    const int64_t total = (int64_t)a->n_k + b->n_k;
+    cudaError_t e;
+    int st;
+    (void)cap_k;
+    // one pool block: expanded (i, j) of A, of B and of the merged list, the merge's own scratch
+    // and the compress pass's control block and tile words
+    const int64_t compress_tiles = std::max<int64_t>((total + NT * CVT - 1) / (NT * CVT), coo3_add_tiles(total));
+    Carver sizes;
+    sizes.take<int32_t>((size_t)a->n_k);
+    sizes.take<int32_t>((size_t)a->n_k);
+    sizes.take<int32_t>((size_t)b->n_k);
+    sizes.take<int32_t>((size_t)b->n_k);
+    sizes.take<int32_t>((size_t)total);
+    sizes.take<int32_t>((size_t)total);
+    sizes.take<uint64_t>((size_t)compress_tiles + 8);
+    const size_t own = sizes.used();
+    Workspace *ws = nullptr;
+    if ((st = acquire_workspace(stream, own + coo3_add_scratch_bytes(total) + 256, &ws, slot))) return (st);
+    Carver carve(ws->dev);
+    int32_t *ai = carve.take<int32_t>((size_t)a->n_k), *aj = carve.take<int32_t>((size_t)a->n_k);
+    int32_t *bi = carve.take<int32_t>((size_t)b->n_k), *bj = carve.take<int32_t>((size_t)b->n_k);
+    int32_t *zi = carve.take<int32_t>((size_t)total), *zj = carve.take<int32_t>((size_t)total);
+    uint64_t *compress_block = carve.take<uint64_t>((size_t)compress_tiles + 8);
+    void *merge_scratch = static_cast<unsigned char *>(ws->dev) + own;
+
+    if (a->n_j > 0) {
+        LaunchScope scope("csf_expand", stream);
+        k_csf_expand<<<(int)(((int64_t)a->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
+    }
+    if (b->n_j > 0) {
+        LaunchScope scope("csf_expand", stream);
+        k_csf_expand<<<(int)(((int64_t)b->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (note_cuda_error(e, "k_csf_expand"));
+
+    nb200_coo3 ca{{a->dims[0], a->dims[1], a->dims[2]}, a->n_k, ai, aj, a->k_idx, a->val};
+    nb200_coo3 cb{{b->dims[0], b->dims[1], b->dims[2]}, b->n_k, bi, bj, b->k_idx, b->val};
+    nb200_coo3 cz{{0, 0, 0}, 0, zi, zj, z->k_idx, z->val};
+    CompressCtl *ctl = reinterpret_cast<CompressCtl *>(compress_block);
+    static_assert(sizeof(CompressCtl) <= 4 * sizeof(uint64_t), "control block must fit its slot");
+    uint64_t *tile_state = compress_block + 4;
+
+    // single-pass route: the merge writes the levels above k itself (no merged i / j columns, no
+    // compress pass); its second look-back runs over `tile_state`, its totals land in ctl
+    e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)coo3_add_tiles(total) + 4), stream);
+    if (e != cudaSuccess) return (note_cuda_error(e, "cudaMemsetAsync"));
+    const CsfLevelsOut levels{z->i_idx, z->j_ptr, z->j_idx, z->k_ptr, (int32_t)std::min<int64_t>(cap_i, INT32_MAX),
+                              (int32_t)std::min<int64_t>(cap_j, INT32_MAX), tile_state, reinterpret_cast<CsfTotals *>(&ctl->n_i)};
+    bool levels_done = false;
+    if ((st = coo3_add_run(&ca, &cb, &cz, false, total, stream, merge_scratch, ws->host, &levels, &levels_done))) return (st);
+    const int32_t nnz = cz.nnz;
+    z->n_k = nnz;
+    if (levels_done) {
+        e = cudaMemcpyAsync(ws->host, ctl, sizeof(CompressCtl), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return (note_cuda_error(e, "read result lengths"));
+        CompressCtl h;
+        std::memcpy(&h, ws->host, sizeof(h));
+        z->n_i = h.n_i;
+        z->n_j = h.n_j;
+        if (h.n_i > cap_i || h.n_j > cap_j) return (NB200_E_CAPACITY);
+        return NB200_OK;
+    }
+
+    const int tiles = (int)(((int64_t)nnz + NT * CVT - 1) / (NT * CVT));
+    e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)tiles + 4), stream);
+    if (e != cudaSuccess) return (note_cuda_error(e, "cudaMemsetAsync"));
+    {
+        LaunchScope scope("csf_compress", stream);
+        k_csf_compress<<<tiles, NT, 0, stream>>>(nnz, zi, zj, (int32_t)std::min<int64_t>(cap_i, INT32_MAX),
+                                                 (int32_t)std::min<int64_t>(cap_j, INT32_MAX), z->i_idx, z->j_ptr, z->j_idx,
+                                                 z->k_ptr, tile_state, ctl);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) return (note_cuda_error(e, "k_csf_compress"));
+    e = cudaMemcpyAsync(ws->host, ctl, sizeof(CompressCtl), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return (note_cuda_error(e, "read result lengths"));
+    CompressCtl h;
+    std::memcpy(&h, ws->host, sizeof(h));
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "csf3 level compress");
+    z->n_i = h.n_i;
+    z->n_j = h.n_j;
+    if (h.n_i > cap_i || h.n_j > cap_j) return (NB200_E_CAPACITY);
+    return NB200_OK;
+}
+
+// ------------------------------------------------------------------ the two-level route ----
+//
+// When the fibres hold several entries each, expanding (i, j) for every entry moves more bytes
+// than the tensor has. The same union then comes from two smaller merges:
+//   1. the fibre lists of A and B -- every (i, j) fibre as one entry of a tensor whose third level
+//      is a single position -- go through the expanded route above with the values 1 (A) and 2 (B):
+//      the result is Z's i_idx / j_ptr / j_idx, and per fibre of Z the sum 1, 2 or 3 says which
+//      operands hold it;
+//   2. an exclusive count of the A flags (and of the B flags) is the fibre of A (of B) that a
+//      fibre of Z corresponds to, or the next one if the operand lacks it: k_ptr[that fibre] is a
+//      row-offset array over Z's fibres in which a missing fibre is an empty row;
+//   3. with those offsets A's and B's (k_idx, val) arrays are CSR matrices with one row per fibre
+//      of Z, and the CSR union (csr_merge.cu) writes Z's k_ptr, k_idx and val in one pass.
+
+__global__ void __launch_bounds__(NT) k_fill_identity(int32_t *__restrict__ p, int32_t n) {
+    const int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x;
+    if (i <= n) p[i] = (int32_t)i;
+}
+
+__global__ void __launch_bounds__(NT) k_fill_float(float *__restrict__ p, int32_t n, float v) {
+    const int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+// flags[u] in {1, 2, 3} -> has_a[u], has_b[u] (n + 1 entries each, the last 0)
+__global__ void __launch_bounds__(NT) k_split_flags(const float *__restrict__ flags, int32_t n, int32_t *__restrict__ has_a,
+                                                   int32_t *__restrict__ has_b) {
+    const int64_t u = (int64_t)blockIdx.x * NT + threadIdx.x;
+    if (u > n) return;
+    const int f = u < n ? (int)ld_nc(flags + u) : 0;
+    has_a[u] = f & 1;
+    has_b[u] = f >> 1;
+}
+
+// ord[u] (fibres of the operand before Z's fibre u) -> k_ptr[ord[u]], in place
+__global__ void __launch_bounds__(NT) k_fibre_offsets(int32_t *__restrict__ ord_a, int32_t *__restrict__ ord_b, int32_t n,
+                                                     const int32_t *__restrict__ a_kptr, const int32_t *__restrict__ b_kptr) {
+    const int64_t u = (int64_t)blockIdx.x * NT + threadIdx.x;
+    if (u > n) return;
+    ord_a[u] = ld_nc(a_kptr + ord_a[u]);
+    ord_b[u] = ld_nc(b_kptr + ord_b[u]);
+}
+
+// The expanded route moves 8 bytes of (i, j) per entry out and back in; the two-level route moves
+// about as much per FIBRE. It pays once fibres hold a few entries on average.
+bool two_level_pays(const nb200_csf3 *a, const nb200_csf3 *b) {
+    if (a->n_j == 0 || b->n_j == 0) return false;
+    if (const char *e = std::getenv("NACHO_B200_CSF_TWO_LEVEL")) return e[0] != '0';  // read per call: tests take both routes
+    return 3 * ((int64_t)a->n_j + b->n_j) <= (int64_t)a->n_k + b->n_k;
+}
+
+int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, int64_t cap_i, int64_t cap_j, int64_t cap_k,
+                      cudaStream_t stream) {
+    const int32_t nja = a->n_j, njb = b->n_j;
+    const int64_t bound_j = (int64_t)nja + njb;
+    if (bound_j > INT32_MAX - 1) return NB200_E_OVERFLOW;
+    const int32_t most = std::max(nja, njb);
+    const int scan_ctas = (int)((bound_j + 1 + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT));
+    Carver sizes;
+    sizes.take<int32_t>((size_t)most + 1);      // identity k_ptr of the fibre tensors
+    sizes.take<int32_t>((size_t)most);          // their k_idx: zeros
+    sizes.take<float>((size_t)nja);             // 1 per fibre of A
+    sizes.take<float>((size_t)njb);             // 2 per fibre of B
+    sizes.take<int32_t>((size_t)bound_j + 1);   // fibre tensor of Z: k_ptr
+    sizes.take<int32_t>((size_t)bound_j);       //                     k_idx
+    sizes.take<float>((size_t)bound_j);         //                     flags
+    sizes.take<int32_t>((size_t)bound_j + 1);   // has_a -> count -> offsets of A over Z's fibres
+    sizes.take<int32_t>((size_t)bound_j + 1);   // the same for B
+    sizes.take<uint64_t>((size_t)scan_ctas + 8);
+    sizes.take<uint64_t>((size_t)scan_ctas + 8);
+    Workspace *ws = nullptr;
+    int st;
+    if ((st = acquire_workspace(stream, sizes.used(), &ws, 3))) return st;
+    Carver carve(ws->dev);
+    int32_t *ident = carve.take<int32_t>((size_t)most + 1);
+    int32_t *zeros = carve.take<int32_t>((size_t)most);
+    float *ones = carve.take<float>((size_t)nja), *twos = carve.take<float>((size_t)njb);
+    int32_t *zf_kptr = carve.take<int32_t>((size_t)bound_j + 1), *zf_kidx = carve.take<int32_t>((size_t)bound_j);
+    float *flags = carve.take<float>((size_t)bound_j);
+    int32_t *off_a = carve.take<int32_t>((size_t)bound_j + 1), *off_b = carve.take<int32_t>((size_t)bound_j + 1);
+    uint64_t *scan_a = carve.take<uint64_t>((size_t)scan_ctas + 8), *scan_b = carve.take<uint64_t>((size_t)scan_ctas + 8);
+    auto grid = [](int64_t n) { return (int)((n + NT - 1) / NT); };
+
+    NB200_CUDA(cudaMemsetAsync(zeros, 0, sizeof(int32_t) * (size_t)most, stream));
+    {
+        LaunchScope scope("csf_fibre_setup", stream);
+        k_fill_identity<<<grid((int64_t)most + 1), NT, 0, stream>>>(ident, most);
+    }
+    {
+        LaunchScope scope("csf_fibre_setup", stream);
+        k_fill_float<<<grid(nja), NT, 0, stream>>>(ones, nja, 1.0f);
+    }
+    {
+        LaunchScope scope("csf_fibre_setup", stream);
+        k_fill_float<<<grid(njb), NT, 0, stream>>>(twos, njb, 2.0f);
+    }
+    NB200_CUDA(cudaGetLastError());
+
+    // ---- 1. union of the fibre lists
+    nb200_csf3 fa = *a, fb = *b, fz = *z;
+    fa.n_k = nja, fa.k_ptr = ident, fa.k_idx = zeros, fa.val = ones;
+    fb.n_k = njb, fb.k_ptr = ident, fb.k_idx = zeros, fb.val = twos;
+    fz.k_ptr = zf_kptr, fz.k_idx = zf_kidx, fz.val = flags;
+    st = csf_add_expanded(&fa, &fb, &fz, cap_i, std::min<int64_t>(cap_j, bound_j), bound_j, stream, 0);
+    z->n_i = fz.n_i;
+    z->n_j = fz.n_j;
+    if (st != NB200_OK) return st;
+    const int32_t nz = fz.n_j;  // fibres of Z
+
+    // ---- 2. offsets of A's and B's entries over Z's fibres
+    NB200_CUDA(cudaMemsetAsync(scan_a, 0, sizeof(uint64_t) * ((size_t)scan_ctas + 8), stream));
+    NB200_CUDA(cudaMemsetAsync(scan_b, 0, sizeof(uint64_t) * ((size_t)scan_ctas + 8), stream));
+    {
+        LaunchScope scope("csf_fibre_flags", stream);
+        k_split_flags<<<grid((int64_t)nz + 1), NT, 0, stream>>>(flags, nz, off_a, off_b);
+    }
+    const int ctas = (int)(((int64_t)nz + 1 + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT));
+    {
+        LaunchScope scope("scan_lookback", stream);
+        k_scan_lookback<<<ctas, SCAN_NT, 0, stream>>>(off_a, nz + 1, scan_a + 4, reinterpret_cast<FusedCtl *>(scan_a));
+    }
+    {
+        LaunchScope scope("scan_lookback", stream);
+        k_scan_lookback<<<ctas, SCAN_NT, 0, stream>>>(off_b, nz + 1, scan_b + 4, reinterpret_cast<FusedCtl *>(scan_b));
+    }
+    {
+        LaunchScope scope("csf_fibre_offsets", stream);
+        k_fibre_offsets<<<grid((int64_t)nz + 1), NT, 0, stream>>>(off_a, off_b, nz, a->k_ptr, b->k_ptr);
+    }
+    NB200_CUDA(cudaGetLastError());
+
+    // ---- 3. the entries: a CSR union with one row per fibre of Z
+    const nb200_csr ma{nz, a->dims[2], a->n_k, off_a, a->k_idx, a->val};
+    const nb200_csr mb{nz, b->dims[2], b->n_k, off_b, b->k_idx, b->val};
+    nb200_csr mz{0, 0, 0, z->k_ptr, z->k_idx, z->val};
+    st = nb200_csr_add_f32_into(&ma, &mb, &mz, cap_k, stream);
+    z->n_k = mz.nnz;
+    if (st != NB200_OK) return st;
+    // a bounded wait of one of the two scans that gave up leaves offsets unscanned: report it
+    FusedCtl h[2];
+    NB200_CUDA(cudaMemcpyAsync(&h[0], scan_a, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaMemcpyAsync(&h[1], scan_b, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaStreamSynchronize(stream));
+    for (const FusedCtl &c : h)
+        if (c.status.error != 0) return note_timeout(c.status.error, c.status.detail, "csf3 fibre offsets");
+    return NB200_OK;
+}
+
 int check_csf3(const nb200_csf3 *t) {
     if (!t || t->n_i < 0 || t->n_j < 0 || t->n_k < 0) return NB200_E_BADARG;
     if (t->n_k > 0 && (!t->i_idx || !t->j_ptr || !t->j_idx || !t->k_ptr || !t->k_idx || !t->val)) return NB200_E_BADARG;
@@ -250,88 +496,8 @@ int csf_add_run(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, bool al
         return NB200_OK;
     }
 
-    // one pool block: expanded (i, j) of A, of B and of the merged list, the merge's own scratch
-    // and the compress pass's control block and tile words
-    const int64_t compress_tiles = std::max<int64_t>((total + NT * CVT - 1) / (NT * CVT), coo3_add_tiles(total));
-    Carver sizes;
-    sizes.take<int32_t>((size_t)a->n_k);
-    sizes.take<int32_t>((size_t)a->n_k);
-    sizes.take<int32_t>((size_t)b->n_k);
-    sizes.take<int32_t>((size_t)b->n_k);
-    sizes.take<int32_t>((size_t)total);
-    sizes.take<int32_t>((size_t)total);
-    sizes.take<uint64_t>((size_t)compress_tiles + 8);
-    const size_t own = sizes.used();
-    Workspace *ws = nullptr;
-    if ((st = acquire_workspace(stream, own + coo3_add_scratch_bytes(total) + 256, &ws))) return fail(st);
-    Carver carve(ws->dev);
-    int32_t *ai = carve.take<int32_t>((size_t)a->n_k), *aj = carve.take<int32_t>((size_t)a->n_k);
-    int32_t *bi = carve.take<int32_t>((size_t)b->n_k), *bj = carve.take<int32_t>((size_t)b->n_k);
-    int32_t *zi = carve.take<int32_t>((size_t)total), *zj = carve.take<int32_t>((size_t)total);
-    uint64_t *compress_block = carve.take<uint64_t>((size_t)compress_tiles + 8);
-    void *merge_scratch = static_cast<unsigned char *>(ws->dev) + own;
-
-    if (a->n_j > 0) {
-        LaunchScope scope("csf_expand", stream);
-        k_csf_expand<<<(int)(((int64_t)a->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
-    }
-    if (b->n_j > 0) {
-        LaunchScope scope("csf_expand", stream);
-        k_csf_expand<<<(int)(((int64_t)b->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
-    }
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csf_expand"));
-
-    nb200_coo3 ca{{a->dims[0], a->dims[1], a->dims[2]}, a->n_k, ai, aj, a->k_idx, a->val};
-    nb200_coo3 cb{{b->dims[0], b->dims[1], b->dims[2]}, b->n_k, bi, bj, b->k_idx, b->val};
-    nb200_coo3 cz{{0, 0, 0}, 0, zi, zj, z->k_idx, z->val};
-    CompressCtl *ctl = reinterpret_cast<CompressCtl *>(compress_block);
-    static_assert(sizeof(CompressCtl) <= 4 * sizeof(uint64_t), "control block must fit its slot");
-    uint64_t *tile_state = compress_block + 4;
-
-    // single-pass route: the merge writes the levels above k itself (no merged i / j columns, no
-    // compress pass); its second look-back runs over `tile_state`, its totals land in ctl
-    e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)coo3_add_tiles(total) + 4), stream);
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
-    const CsfLevelsOut levels{z->i_idx, z->j_ptr, z->j_idx, z->k_ptr, (int32_t)std::min<int64_t>(cap_i, INT32_MAX),
-                              (int32_t)std::min<int64_t>(cap_j, INT32_MAX), tile_state, reinterpret_cast<CsfTotals *>(&ctl->n_i)};
-    bool levels_done = false;
-    if ((st = coo3_add_run(&ca, &cb, &cz, false, total, stream, merge_scratch, ws->host, &levels, &levels_done))) return fail(st);
-    const int32_t nnz = cz.nnz;
-    z->n_k = nnz;
-    if (levels_done) {
-        e = cudaMemcpyAsync(ws->host, ctl, sizeof(CompressCtl), cudaMemcpyDeviceToHost, stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-        if (e != cudaSuccess) return fail(note_cuda_error(e, "read result lengths"));
-        CompressCtl h;
-        std::memcpy(&h, ws->host, sizeof(h));
-        z->n_i = h.n_i;
-        z->n_j = h.n_j;
-        if (h.n_i > cap_i || h.n_j > cap_j) return fail(NB200_E_CAPACITY);
-        return NB200_OK;
-    }
-
-    const int tiles = (int)(((int64_t)nnz + NT * CVT - 1) / (NT * CVT));
-    e = cudaMemsetAsync(compress_block, 0, sizeof(uint64_t) * ((size_t)tiles + 4), stream);
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
-    {
-        LaunchScope scope("csf_compress", stream);
-        k_csf_compress<<<tiles, NT, 0, stream>>>(nnz, zi, zj, (int32_t)std::min<int64_t>(cap_i, INT32_MAX),
-                                                 (int32_t)std::min<int64_t>(cap_j, INT32_MAX), z->i_idx, z->j_ptr, z->j_idx,
-                                                 z->k_ptr, tile_state, ctl);
-        e = cudaGetLastError();
-    }
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csf_compress"));
-    e = cudaMemcpyAsync(ws->host, ctl, sizeof(CompressCtl), cudaMemcpyDeviceToHost, stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "read result lengths"));
-    CompressCtl h;
-    std::memcpy(&h, ws->host, sizeof(h));
-    if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
-    z->n_i = h.n_i;
-    z->n_j = h.n_j;
-    if (h.n_i > cap_i || h.n_j > cap_j) return fail(NB200_E_CAPACITY);
-    return NB200_OK;
+    st = two_level_pays(a, b) ? csf_add_two_level(a, b, z, cap_i, cap_j, cap_k, stream) : csf_add_expanded(a, b, z, cap_i, cap_j, cap_k, stream, 0);
+    return st == NB200_OK ? NB200_OK : fail(st);
 }
 
 // Inner product of two CSF3 tensors (compiler.cpp:141): every entry gets its (i, j) written out

@@ -571,7 +571,7 @@ int csr_add3_run(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb2
         release();
         return csr_add3_chained(a, b, c, z, alloc, capacity, stream_v);
     }
-    if (h.status.error != 0) return release(), NB200_E_TIMEOUT;
+    if (h.status.error != 0) return release(), note_timeout(h.status.error, h.status.detail, "csr add3");
     if (h.total > INT32_MAX) return release(), NB200_E_OVERFLOW;
     *z = out;
     z->nnz = (int32_t)h.total;

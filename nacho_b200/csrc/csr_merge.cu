@@ -851,7 +851,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
             return NB200_OK;
         }
         if ((st = read_ctl(h))) return fail(st);
-        if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+        if (h.status.error != 0) return fail(note_timeout(h.status.error, h.status.detail, "csr merge"));
         if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
         z->nnz = (int32_t)h.total;
         if (alloc && h.total == 0) {  // zero-length arrays are handed over as NULL
@@ -874,7 +874,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_scan_tiles"));
     if ((st = read_ctl(h))) return fail(st);
-    if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+    if (h.status.error != 0) return fail(note_timeout(h.status.error, h.status.detail, "csr merge"));
     if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
     z->nnz = (int32_t)h.total;
     if (alloc) {
@@ -889,7 +889,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     e = launch_tile<OP, MODE_FILL>(A, B, cuts, cbits, tile_count, nullptr, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream);
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fill>"));
     if ((st = read_ctl(h))) return fail(st);
-    if (h.status.error != 0) return fail(NB200_E_TIMEOUT);
+    if (h.status.error != 0) return fail(note_timeout(h.status.error, h.status.detail, "csr merge"));
     return NB200_OK;
 }
 
@@ -1003,7 +1003,7 @@ int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_
     FusedCtl h;  // read back into ordinary host memory: no pinned buffer is taken for this
     NB200_CUDA(cudaMemcpyAsync(&h, ctl, sizeof(h), cudaMemcpyDeviceToHost, stream));
     NB200_CUDA(cudaStreamSynchronize(stream));
-    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "csr merge (no-alloc)");
     if (h.total > INT32_MAX) return NB200_E_OVERFLOW;
     z->nnz = (int32_t)h.total;
     return NB200_OK;

@@ -218,7 +218,7 @@ int dcsr2_run(csr_into_fn op, bool is_union, const nb200_dcsr *a, const nb200_dc
     NB200_CUDA(cudaStreamSynchronize(stream));
     FusedCtl h;
     std::memcpy(&h, s.ws->host, sizeof(h));
-    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "dcsr row compress");
     z->n_i = (int32_t)h.total;
     return NB200_OK;
 }

@@ -69,6 +69,12 @@ int note_cuda_error(cudaError_t e, const char *what) {
     return e == cudaErrorMemoryAllocation ? NB200_E_NOMEM : NB200_E_CUDA;
 }
 
+int note_timeout(int site, int tile, const char *where) {
+    static const char *const names[] = {"?", "look-back over earlier tiles", "bulk copy into shared memory", "tile wider than its key"};
+    std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s gave up at tile %d", where, names[site >= 1 && site <= 3 ? site : 0], tile);
+    return NB200_E_TIMEOUT;
+}
+
 int acquire_workspace(cudaStream_t stream, size_t bytes, Workspace **out, int slot) {
     int dev = 0;
     NB200_CUDA(cudaGetDevice(&dev));

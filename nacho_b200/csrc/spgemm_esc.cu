@@ -891,7 +891,7 @@ int spgemm_symbolic(const nb200_csr *a, const nb200_csr *b, nb200_csr *c, int64_
     NB200_CUDA(cudaStreamSynchronize(stream));
     FusedCtl h;
     std::memcpy(&h, plan.ws->host, sizeof(h));
-    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "spgemm row scan");
     const int64_t nnz = h.total;
     if (nnz > INT32_MAX) return NB200_E_OVERFLOW;
     c->nnz = (int32_t)nnz;

@@ -415,7 +415,7 @@ int sssmm_run(const nb200_csr *a, const nb200_csr *b, const nb200_csr *c, nb200_
     NB200_CUDA(cudaStreamSynchronize(stream));
     FusedCtl h;
     std::memcpy(&h, ws->host, sizeof(h));
-    if (h.status.error != 0) return NB200_E_TIMEOUT;
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "sssmm scan");
     z->nnz = (int32_t)h.total;
     if (h.total > capacity) return NB200_E_CAPACITY;
     if (h.total > 0) {

@@ -221,3 +221,29 @@ print("two-pass ok")
     env = dict(os.environ, NACHO_B200_TWO_PASS="1")
     r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "two-pass ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.parametrize("route", ["0", "1"])
+@pytest.mark.parametrize("dims,n,seed", [((40, 30, 25), 900, 71), ((64, 64, 1 << 12), 400_000, 72),   # fibres of ~100 entries
+                                          ((3, 2000, 1 << 10), 300_000, 73), ((1 << 17, 4, 4), 100_000, 74),   # ~1 entry per fibre
+                                          ((1 << 30, 1 << 30, 1 << 30), 40_000, 75), ((2, 2, 2**31 - 1), 200_000, 76)])
+def test_csf3_both_routes(nacho, oracle, monkeypatch, route, dims, n, seed):
+    """CSF3 add through the route over expanded coordinates (0) and through the two-level route (1:
+    fibre lists merged first, entries through the CSR union with one row per result fibre); both
+    must give the oracle's tree whatever the fibre lengths, also for identical operands (every
+    fibre and entry in both) and for operands without a common fibre."""
+    monkeypatch.setenv("NACHO_B200_CSF_TWO_LEVEL", route)
+    (ca, va), (cb, vb) = _seeded(dims, n, seed)
+    fa, fb = CSF3(dims, *csf3_levels(ca), va), CSF3(dims, *csf3_levels(cb), vb)
+    ga, gb = nacho.to_csf3(ca, va, dims, "cuda"), nacho.to_csf3(cb, vb, dims, "cuda")
+    assert_same(csf3_from_gpu(nacho.gpu_csf_add_f32(ga, gb)), oracle.csf3_add(fa, fb), f"csf3 route {route}")
+    assert_same(csf3_from_gpu(nacho.gpu_csf_add_f32(ga, ga)), oracle.csf3_add(fa, fa), f"csf3 route {route}, identical operands")
+    # disjoint fibres: B moved to other i (first extent permitting)
+    if dims[0] >= 4:
+        half = dims[0] // 2
+        cl, ch = ca[ca[:, 0] < half], cb[cb[:, 0] >= half]
+        vl, vh = va[ca[:, 0] < half], vb[cb[:, 0] >= half]
+        if len(cl) and len(ch):
+            want = oracle.csf3_add(CSF3(dims, *csf3_levels(cl), vl), CSF3(dims, *csf3_levels(ch), vh))
+            got = nacho.gpu_csf_add_f32(nacho.to_csf3(cl, vl, dims, "cuda"), nacho.to_csf3(ch, vh, dims, "cuda"))
+            assert_same(csf3_from_gpu(got), want, f"csf3 route {route}, disjoint slices")
