@@ -193,10 +193,51 @@ __global__ void __launch_bounds__(NT) k_csf_compress(int32_t nnz, const int32_t 
     }
 }
 
+constexpr int FS_VT = 8;  // fibres per thread in k_fibre_slices
+
+// i of every fibre. A CTA takes NT * FS_VT consecutive fibres; they lie in at most that many + 1
+// consecutive stored slices (a stored slice has at least one fibre), so warp 0 finds the slice of the
+// first fibre with a 32-ary search, the CTA copies that window of j_ptr / i_idx to shared memory and
+// every thread finds its fibres' slices there.
+__global__ void __launch_bounds__(NT) k_fibre_slices(int32_t n_i, int32_t n_j, const int32_t *__restrict__ i_idx,
+                                                    const int32_t *__restrict__ j_ptr, int32_t *__restrict__ out_i) {
+    constexpr int SPAN = NT * FS_VT;
+    __shared__ int32_t s_start[SPAN + 1], s_i[SPAN + 1];
+    __shared__ int s_first;
+    const int tid = threadIdx.x;
+    const int64_t q0 = (int64_t)blockIdx.x * SPAN;
+    if (tid < 32) {
+        const int64_t r = warp_last_true(0, (int64_t)n_i - 1, [&](int64_t x) { return ld_nc(j_ptr + x) <= q0; });
+        if (tid == 0) s_first = (int)r;
+    }
+    __syncthreads();
+    const int first = s_first;
+    const int need = (int)min((int64_t)SPAN, (int64_t)n_j - q0);  // fibres of this CTA: slices first .. first + need at most
+    for (int w = tid; w <= need; w += NT) {
+        const bool live = first + w < n_i;
+        s_start[w] = live ? ld_nc(j_ptr + first + w) : INT32_MAX;
+        s_i[w] = live ? ld_nc(i_idx + first + w) : 0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int v = 0; v < FS_VT; ++v) {
+        const int64_t q = q0 + tid + v * NT;
+        if (q >= n_j) return;
+        int lo = 0, hi = need;  // largest w with s_start[w] <= q
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_start[mid] <= q) lo = mid; else hi = mid - 1;
+        }
+        out_i[q] = s_i[lo];
+    }
+}
+
 // The route over expanded coordinates: steps 1-3 of the file comment. `z`'s arrays exist and hold
 // cap_i / cap_j / cap_k entries (cap_k >= n_k(A) + n_k(B)); nothing is freed here on failure.
+// `unit_fibres`: every fibre of the operands holds exactly one entry (n_k == n_j) and their k_ptr
+// arrays are not read: the j column of the entries is j_idx itself and only i is written out.
 int csf_add_expanded(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, int64_t cap_i, int64_t cap_j, int64_t cap_k,
-                     cudaStream_t stream, int slot) {
+                     cudaStream_t stream, int slot, bool unit_fibres = false) {
     const int64_t total = (int64_t)a->n_k + b->n_k;
     cudaError_t e;
     int st;
@@ -222,13 +263,26 @@ int csf_add_expanded(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, in
     uint64_t *compress_block = carve.take<uint64_t>((size_t)compress_tiles + 8);
     void *merge_scratch = static_cast<unsigned char *>(ws->dev) + own;
 
-    if (a->n_j > 0) {
-        LaunchScope scope("csf_expand", stream);
-        k_csf_expand<<<(int)(((int64_t)a->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
-    }
-    if (b->n_j > 0) {
-        LaunchScope scope("csf_expand", stream);
-        k_csf_expand<<<(int)(((int64_t)b->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
+    if (unit_fibres) {
+        aj = a->j_idx;
+        bj = b->j_idx;
+        if (a->n_j > 0) {
+            LaunchScope scope("csf_fibre_slices", stream);
+            k_fibre_slices<<<(int)(((int64_t)a->n_j + NT * FS_VT - 1) / (NT * FS_VT)), NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, ai);
+        }
+        if (b->n_j > 0) {
+            LaunchScope scope("csf_fibre_slices", stream);
+            k_fibre_slices<<<(int)(((int64_t)b->n_j + NT * FS_VT - 1) / (NT * FS_VT)), NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, bi);
+        }
+    } else {
+        if (a->n_j > 0) {
+            LaunchScope scope("csf_expand", stream);
+            k_csf_expand<<<(int)(((int64_t)a->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(a->n_i, a->n_j, a->i_idx, a->j_ptr, a->j_idx, a->k_ptr, ai, aj);
+        }
+        if (b->n_j > 0) {
+            LaunchScope scope("csf_expand", stream);
+            k_csf_expand<<<(int)(((int64_t)b->n_j + 31) / 32 * 32 + NT - 1) / NT, NT, 0, stream>>>(b->n_i, b->n_j, b->i_idx, b->j_ptr, b->j_idx, b->k_ptr, bi, bj);
+        }
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (note_cuda_error(e, "k_csf_expand"));
@@ -299,33 +353,70 @@ int csf_add_expanded(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, in
 //   3. with those offsets A's and B's (k_idx, val) arrays are CSR matrices with one row per fibre
 //      of Z, and the CSR union (csr_merge.cu) writes Z's k_ptr, k_idx and val in one pass.
 
-__global__ void __launch_bounds__(NT) k_fill_identity(int32_t *__restrict__ p, int32_t n) {
-    const int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x;
-    if (i <= n) p[i] = (int32_t)i;
-}
-
 __global__ void __launch_bounds__(NT) k_fill_float(float *__restrict__ p, int32_t n, float v) {
     const int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x;
     if (i < n) p[i] = v;
 }
 
-// flags[u] in {1, 2, 3} -> has_a[u], has_b[u] (n + 1 entries each, the last 0)
-__global__ void __launch_bounds__(NT) k_split_flags(const float *__restrict__ flags, int32_t n, int32_t *__restrict__ has_a,
-                                                   int32_t *__restrict__ has_b) {
-    const int64_t u = (int64_t)blockIdx.x * NT + threadIdx.x;
-    if (u > n) return;
-    const int f = u < n ? (int)ld_nc(flags + u) : 0;
-    has_a[u] = f & 1;
-    has_b[u] = f >> 1;
-}
+constexpr int OVT = 16;  // fibres per thread in the offsets pass
 
-// ord[u] (fibres of the operand before Z's fibre u) -> k_ptr[ord[u]], in place
-__global__ void __launch_bounds__(NT) k_fibre_offsets(int32_t *__restrict__ ord_a, int32_t *__restrict__ ord_b, int32_t n,
-                                                     const int32_t *__restrict__ a_kptr, const int32_t *__restrict__ b_kptr) {
-    const int64_t u = (int64_t)blockIdx.x * NT + threadIdx.x;
-    if (u > n) return;
-    ord_a[u] = ld_nc(a_kptr + ord_a[u]);
-    ord_b[u] = ld_nc(b_kptr + ord_b[u]);
+// flags[u] in {1, 2, 3} for the n fibres of Z: which operand holds fibre u. Writes, for u = 0 .. n,
+// off_a[u] = a_kptr[fibres of A before u] and off_b[u] likewise: one pass, the two running counts
+// packed into one word and carried across tiles by bounded look-back.
+__global__ void __launch_bounds__(NT) k_fibre_offsets(const float *__restrict__ flags, int32_t n, const int32_t *__restrict__ a_kptr,
+                                                     const int32_t *__restrict__ b_kptr, int32_t *__restrict__ off_a,
+                                                     int32_t *__restrict__ off_b, uint64_t *state_raw, FusedCtl *ctl) {
+    __shared__ int scan_tmp[72];
+    __shared__ long long s_base;
+    volatile uint64_t *state = state_raw;
+    const int tid = threadIdx.x, t = blockIdx.x;  // CTAs are dispatched in index order; waits on earlier tiles are bounded
+    const int64_t p0 = ((int64_t)t * NT + tid) * OVT;
+    int f[OVT], mine_a = 0, mine_b = 0;
+    if (p0 + OVT <= n) {  // 16-byte loads: a thread's fibres are consecutive
+#pragma unroll
+        for (int q = 0; q < OVT; q += 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(flags + p0 + q));
+            f[q] = (int)v.x, f[q + 1] = (int)v.y, f[q + 2] = (int)v.z, f[q + 3] = (int)v.w;
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < OVT; ++q) f[q] = p0 + q < n ? (int)ld_nc(flags + p0 + q) : 0;
+    }
+#pragma unroll
+    for (int q = 0; q < OVT; ++q) {
+        mine_a += f[q] & 1;
+        mine_b += f[q] >> 1;
+    }
+    int before_a, before_b, tot_a, tot_b;
+    block_excl_sum2<NT>(mine_a, mine_b, scan_tmp, before_a, before_b, tot_a, tot_b);
+    if (warp_id() == 0) {
+        const int64_t b = lookback_exclusive(state, t, ((int64_t)tot_a << 31) | (int64_t)tot_b, &ctl->status);
+        if (lane_id() == 0) s_base = b;
+    }
+    __syncthreads();
+    const long long base = s_base;
+    if (base < 0) return;
+    int ca = (int)(base >> 31) + before_a, cb = (int)(base & 0x7fffffff) + before_b;
+    int32_t va[OVT], vb[OVT];
+#pragma unroll
+    for (int q = 0; q < OVT; ++q) {
+        const bool live = p0 + q <= n;
+        va[q] = live ? ld_nc(a_kptr + ca) : 0;
+        vb[q] = live ? ld_nc(b_kptr + cb) : 0;
+        ca += f[q] & 1;
+        cb += f[q] >> 1;
+    }
+    if (p0 + OVT <= (int64_t)n + 1) {
+#pragma unroll
+        for (int q = 0; q < OVT; q += 4) {
+            *reinterpret_cast<int4 *>(off_a + p0 + q) = make_int4(va[q], va[q + 1], va[q + 2], va[q + 3]);
+            *reinterpret_cast<int4 *>(off_b + p0 + q) = make_int4(vb[q], vb[q + 1], vb[q + 2], vb[q + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < OVT; ++q)
+            if (p0 + q <= n) off_a[p0 + q] = va[q], off_b[p0 + q] = vb[q];
+    }
 }
 
 // The expanded route moves 8 bytes of (i, j) per entry out and back in; the two-level route moves
@@ -342,37 +433,30 @@ int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
     const int64_t bound_j = (int64_t)nja + njb;
     if (bound_j > INT32_MAX - 1) return NB200_E_OVERFLOW;
     const int32_t most = std::max(nja, njb);
-    const int scan_ctas = (int)((bound_j + 1 + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT));
+    const int tiles_cap = (int)((bound_j + 1 + NT * OVT - 1) / (NT * OVT));
     Carver sizes;
-    sizes.take<int32_t>((size_t)most + 1);      // identity k_ptr of the fibre tensors
-    sizes.take<int32_t>((size_t)most);          // their k_idx: zeros
+    sizes.take<int32_t>((size_t)most);          // k_idx of the fibre tensors: zeros
     sizes.take<float>((size_t)nja);             // 1 per fibre of A
     sizes.take<float>((size_t)njb);             // 2 per fibre of B
     sizes.take<int32_t>((size_t)bound_j + 1);   // fibre tensor of Z: k_ptr
     sizes.take<int32_t>((size_t)bound_j);       //                     k_idx
     sizes.take<float>((size_t)bound_j);         //                     flags
-    sizes.take<int32_t>((size_t)bound_j + 1);   // has_a -> count -> offsets of A over Z's fibres
+    sizes.take<int32_t>((size_t)bound_j + 1);   // offsets of A's entries over Z's fibres
     sizes.take<int32_t>((size_t)bound_j + 1);   // the same for B
-    sizes.take<uint64_t>((size_t)scan_ctas + 8);
-    sizes.take<uint64_t>((size_t)scan_ctas + 8);
+    sizes.take<uint64_t>((size_t)tiles_cap + 8);
     Workspace *ws = nullptr;
     int st;
     if ((st = acquire_workspace(stream, sizes.used(), &ws, 3))) return st;
     Carver carve(ws->dev);
-    int32_t *ident = carve.take<int32_t>((size_t)most + 1);
     int32_t *zeros = carve.take<int32_t>((size_t)most);
     float *ones = carve.take<float>((size_t)nja), *twos = carve.take<float>((size_t)njb);
     int32_t *zf_kptr = carve.take<int32_t>((size_t)bound_j + 1), *zf_kidx = carve.take<int32_t>((size_t)bound_j);
     float *flags = carve.take<float>((size_t)bound_j);
     int32_t *off_a = carve.take<int32_t>((size_t)bound_j + 1), *off_b = carve.take<int32_t>((size_t)bound_j + 1);
-    uint64_t *scan_a = carve.take<uint64_t>((size_t)scan_ctas + 8), *scan_b = carve.take<uint64_t>((size_t)scan_ctas + 8);
+    uint64_t *scan_block = carve.take<uint64_t>((size_t)tiles_cap + 8);
     auto grid = [](int64_t n) { return (int)((n + NT - 1) / NT); };
 
     NB200_CUDA(cudaMemsetAsync(zeros, 0, sizeof(int32_t) * (size_t)most, stream));
-    {
-        LaunchScope scope("csf_fibre_setup", stream);
-        k_fill_identity<<<grid((int64_t)most + 1), NT, 0, stream>>>(ident, most);
-    }
     {
         LaunchScope scope("csf_fibre_setup", stream);
         k_fill_float<<<grid(nja), NT, 0, stream>>>(ones, nja, 1.0f);
@@ -385,34 +469,21 @@ int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
 
     // ---- 1. union of the fibre lists
     nb200_csf3 fa = *a, fb = *b, fz = *z;
-    fa.n_k = nja, fa.k_ptr = ident, fa.k_idx = zeros, fa.val = ones;
-    fb.n_k = njb, fb.k_ptr = ident, fb.k_idx = zeros, fb.val = twos;
+    fa.n_k = nja, fa.k_ptr = nullptr, fa.k_idx = zeros, fa.val = ones;
+    fb.n_k = njb, fb.k_ptr = nullptr, fb.k_idx = zeros, fb.val = twos;
     fz.k_ptr = zf_kptr, fz.k_idx = zf_kidx, fz.val = flags;
-    st = csf_add_expanded(&fa, &fb, &fz, cap_i, std::min<int64_t>(cap_j, bound_j), bound_j, stream, 0);
+    st = csf_add_expanded(&fa, &fb, &fz, cap_i, std::min<int64_t>(cap_j, bound_j), bound_j, stream, 0, true);
     z->n_i = fz.n_i;
     z->n_j = fz.n_j;
     if (st != NB200_OK) return st;
     const int32_t nz = fz.n_j;  // fibres of Z
 
     // ---- 2. offsets of A's and B's entries over Z's fibres
-    NB200_CUDA(cudaMemsetAsync(scan_a, 0, sizeof(uint64_t) * ((size_t)scan_ctas + 8), stream));
-    NB200_CUDA(cudaMemsetAsync(scan_b, 0, sizeof(uint64_t) * ((size_t)scan_ctas + 8), stream));
-    {
-        LaunchScope scope("csf_fibre_flags", stream);
-        k_split_flags<<<grid((int64_t)nz + 1), NT, 0, stream>>>(flags, nz, off_a, off_b);
-    }
-    const int ctas = (int)(((int64_t)nz + 1 + SCAN_NT * SCAN_VT - 1) / (SCAN_NT * SCAN_VT));
-    {
-        LaunchScope scope("scan_lookback", stream);
-        k_scan_lookback<<<ctas, SCAN_NT, 0, stream>>>(off_a, nz + 1, scan_a + 4, reinterpret_cast<FusedCtl *>(scan_a));
-    }
-    {
-        LaunchScope scope("scan_lookback", stream);
-        k_scan_lookback<<<ctas, SCAN_NT, 0, stream>>>(off_b, nz + 1, scan_b + 4, reinterpret_cast<FusedCtl *>(scan_b));
-    }
+    NB200_CUDA(cudaMemsetAsync(scan_block, 0, sizeof(uint64_t) * ((size_t)tiles_cap + 8), stream));
     {
         LaunchScope scope("csf_fibre_offsets", stream);
-        k_fibre_offsets<<<grid((int64_t)nz + 1), NT, 0, stream>>>(off_a, off_b, nz, a->k_ptr, b->k_ptr);
+        k_fibre_offsets<<<(int)(((int64_t)nz + 1 + NT * OVT - 1) / (NT * OVT)), NT, 0, stream>>>(
+            flags, nz, a->k_ptr, b->k_ptr, off_a, off_b, scan_block + 4, reinterpret_cast<FusedCtl *>(scan_block));
     }
     NB200_CUDA(cudaGetLastError());
 
@@ -423,13 +494,11 @@ int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
     st = nb200_csr_add_f32_into(&ma, &mb, &mz, cap_k, stream);
     z->n_k = mz.nnz;
     if (st != NB200_OK) return st;
-    // a bounded wait of one of the two scans that gave up leaves offsets unscanned: report it
-    FusedCtl h[2];
-    NB200_CUDA(cudaMemcpyAsync(&h[0], scan_a, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
-    NB200_CUDA(cudaMemcpyAsync(&h[1], scan_b, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
+    // a look-back of the offsets pass that gave up leaves offsets unwritten: report it
+    FusedCtl h;
+    NB200_CUDA(cudaMemcpyAsync(&h, scan_block, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
     NB200_CUDA(cudaStreamSynchronize(stream));
-    for (const FusedCtl &c : h)
-        if (c.status.error != 0) return note_timeout(c.status.error, c.status.detail, "csf3 fibre offsets");
+    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "csf3 fibre offsets");
     return NB200_OK;
 }
 
