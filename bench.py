@@ -283,7 +283,8 @@ def ref_gpu_baseline(spec, tensors, nbytes, products=None, runs: int = 3):
         tup = [(tuple(int(x) for x in t.shape), t.dim_i_indices, t.dim_j_offsets, t.dim_j_indices, t.dim_k_offsets,
                 t.dim_k_indices, t.values) for t in tensors]
     fn = {"csr_add": ref.csr_add, "csr_mul": ref.csr_mul, "csr_add_3": ref.csr_add_3, "spgemm": ref.spgemm,
-          "coo3d_add": ref.coo3_add, "csf_add": ref.csf3_add}.get(op)
+          "coo3d_add": ref.coo3_add, "csf_add": ref.csf3_add,
+          "sssmm": ref.sssmm if hasattr(ref.lib, "ref_gpu_sssmm") else None}.get(op)
     if fn is None:
         return {"unavailable": f"the reference's {op} GPU kernel is not among the ones built into oracle/_ref"}
     times = []

@@ -62,7 +62,7 @@ class ReferenceGpu:
         P = C.POINTER
         L.ref_gpu_free.argtypes = [C.c_void_p]
         L.ref_gpu_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
-        for name, n, t in (("csr_add", 3, _CSR), ("csr_mul", 3, _CSR), ("csr_add_3", 4, _CSR), ("spgemm", 3, _CSR),
+        for name, n, t in (("csr_add", 3, _CSR), ("csr_mul", 3, _CSR), ("csr_add_3", 4, _CSR), ("spgemm", 3, _CSR), ("sssmm", 4, _CSR),
                            ("coo3d_add", 3, _COO3), ("csf_add", 3, _CSF3)):
             getattr(L, "ref_gpu_" + name).argtypes = [P(t)] * n + [C.c_int, C.c_int]
         self.last_ms = 0.0  # wall-clock of the last driver call, device synchronised on both sides
@@ -126,6 +126,10 @@ class ReferenceGpu:
 
     def spgemm(self, a, b, grid=DEFAULT_GRID, keep=True):
         return self._csr_op("spgemm", (a, b), grid, keep)
+
+    def sssmm(self, a, b, c, grid=DEFAULT_GRID, keep=True):
+        """Masked product sum_j a_ij b_jk c_ik (compiler.cpp:150-153)."""
+        return self._csr_op("sssmm", (a, b, c), grid, keep)
 
     def coo3_add(self, a, b, grid=DEFAULT_GRID, keep=True):
         import torch

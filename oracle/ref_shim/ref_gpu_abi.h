@@ -25,6 +25,7 @@ int ref_gpu_csr_add(const ref_csr *a, const ref_csr *b, ref_csr *z, int num_bloc
 int ref_gpu_csr_mul(const ref_csr *a, const ref_csr *b, ref_csr *z, int num_blocks, int threads_per_block);
 int ref_gpu_csr_add_3(const ref_csr *a, const ref_csr *b, const ref_csr *c, ref_csr *z, int num_blocks, int threads_per_block);
 int ref_gpu_spgemm(const ref_csr *a, const ref_csr *b, ref_csr *z, int num_blocks, int threads_per_block);
+int ref_gpu_sssmm(const ref_csr *a, const ref_csr *b, const ref_csr *c, ref_csr *z, int num_blocks, int threads_per_block);
 int ref_gpu_coo3d_add(const ref_coo3 *a, const ref_coo3 *b, ref_coo3 *z, int num_blocks, int threads_per_block);
 int ref_gpu_csf_add(const ref_csf3 *a, const ref_csf3 *b, ref_csf3 *z, int num_blocks, int threads_per_block);
 

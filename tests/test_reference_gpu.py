@@ -122,6 +122,36 @@ def test_spgemm_laplacian_and_rmat(nacho, ref_gpu, oracle):
     check_spgemm(nacho, ref_gpu, oracle, ta, synth.transpose_csr(ta))
 
 
+def check_sssmm(nacho, ref_gpu, oracle, ta, tb, tc):
+    """Masked product against the reference's own emitted sssmm GPU kernel: same structure (the mask's
+    positions a product reaches), values of both sides within 1e-5 of sum|a b c| of a float64 sum."""
+    a, b, c = dev(ta), dev(tb), dev(tc)
+    if not hasattr(ref_gpu.lib, "ref_gpu_sssmm"):
+        pytest.skip("the checker library was built before the reference's sssmm kernel was added to it")
+    got = nacho.gpu_sssmm_f32(as_csr_gpu(nacho, a), as_csr_gpu(nacho, b), as_csr_gpu(nacho, c))
+    want = ref_gpu.sssmm(a, b, c)
+    same_csr(got, want, exact_values=False)
+    ha, hb, hc = synth_csr(ta), synth_csr(tb), synth_csr(tc)
+    full, v64, abs64, _ = oracle.spgemm(ha, hb, 8, extras=True)
+    key = lambda m: np.repeat(np.arange(m.rows, dtype=np.int64), np.diff(m.row_ptr)) * m.cols + m.col
+    _, i_f, i_c = np.intersect1d(key(full), key(hc), return_indices=True)
+    x64 = v64[i_f] * hc.val[i_c].astype(np.float64)
+    bound = 1e-5 * abs64[i_f] * np.abs(hc.val[i_c]) + 1e-30
+    assert len(x64) == got.values.numel()
+    assert np.all(np.abs(got.values.cpu().numpy().astype(np.float64) - x64) <= bound)
+    assert np.all(np.abs(want[4].cpu().numpy().astype(np.float64) - x64) <= 4 * bound), "the reference itself is off"
+
+
+def test_sssmm_against_the_reference_gpu_kernel(nacho, ref_gpu, oracle):
+    from nacho_b200 import synth
+    check_sssmm(nacho, ref_gpu, oracle, synth.random_csr(500, 400, 0.03, 31), synth.random_csr(400, 300, 0.03, 32),
+                synth.random_csr(500, 300, 0.05, 33))
+    ta = synth.rmat_csr(scale=11, seed=4111)   # A A masked by A, as the reference's sssmm benchmark runs square matrices
+    check_sssmm(nacho, ref_gpu, oracle, ta, ta, ta)
+    lap = synth.laplacian_csr(48)
+    check_sssmm(nacho, ref_gpu, oracle, lap, lap, lap)
+
+
 def test_randomised_shapes_against_the_reference_gpu_kernels(nacho, ref_gpu):
     """Forty seeded draws of shape, density and row skew through all four CSR kernels of both
     sides: index arrays equal, add / multiply values bit-equal, SpGEMM values close (both sides
