@@ -359,6 +359,7 @@ __global__ void __launch_bounds__(NT) k_fill_float(float *__restrict__ p, int32_
 }
 
 constexpr int OVT = 16;  // fibres per thread in the offsets pass
+constexpr int32_t DCSR_FIBRE_ROWS = 1 << 24;  // first extent up to which the fibre lists go through the DCSR union
 
 // flags[u] in {1, 2, 3} for the n fibres of Z: which operand holds fibre u. Writes, for u = 0 .. n,
 // off_a[u] = a_kptr[fibres of A before u] and off_b[u] likewise: one pass, the two running counts
@@ -467,12 +468,26 @@ int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
     }
     NB200_CUDA(cudaGetLastError());
 
-    // ---- 1. union of the fibre lists
-    nb200_csf3 fa = *a, fb = *b, fz = *z;
-    fa.n_k = nja, fa.k_ptr = nullptr, fa.k_idx = zeros, fa.val = ones;
-    fb.n_k = njb, fb.k_ptr = nullptr, fb.k_idx = zeros, fb.val = twos;
-    fz.k_ptr = zf_kptr, fz.k_idx = zf_kidx, fz.val = flags;
-    st = csf_add_expanded(&fa, &fb, &fz, cap_i, std::min<int64_t>(cap_j, bound_j), bound_j, stream, 0, true);
+    // ---- 1. union of the fibre lists. They are DCSR matrices as they lie (slices x j): where the
+    // first extent allows scratch per slice number and the caller's i capacity covers the one-pass
+    // worst case, the DCSR union (CSR merge kernels, formats2d.cu) takes them; otherwise the route
+    // over expanded coordinates does, with every fibre as one entry.
+    const int64_t bound_i = std::min<int64_t>((int64_t)a->n_i + b->n_i, a->dims[0]);
+    nb200_csf3 fz = *z;
+    if (a->dims[0] <= DCSR_FIBRE_ROWS && cap_i >= bound_i) {
+        const nb200_dcsr da{a->dims[0], a->dims[1], a->n_i, nja, a->i_idx, a->j_ptr, a->j_idx, ones};
+        const nb200_dcsr db{b->dims[0], b->dims[1], b->n_i, njb, b->i_idx, b->j_ptr, b->j_idx, twos};
+        nb200_dcsr dz{0, 0, 0, 0, z->i_idx, z->j_ptr, z->j_idx, flags};
+        st = nb200_dcsr_add_f32_into(&da, &db, &dz, cap_i, std::min<int64_t>(cap_j, bound_j), stream);
+        fz.n_i = dz.n_i;
+        fz.n_j = dz.nnz;
+    } else {
+        nb200_csf3 fa = *a, fb = *b;
+        fa.n_k = nja, fa.k_ptr = nullptr, fa.k_idx = zeros, fa.val = ones;
+        fb.n_k = njb, fb.k_ptr = nullptr, fb.k_idx = zeros, fb.val = twos;
+        fz.k_ptr = zf_kptr, fz.k_idx = zf_kidx, fz.val = flags;
+        st = csf_add_expanded(&fa, &fb, &fz, cap_i, std::min<int64_t>(cap_j, bound_j), bound_j, stream, 0, true);
+    }
     z->n_i = fz.n_i;
     z->n_j = fz.n_j;
     if (st != NB200_OK) return st;
