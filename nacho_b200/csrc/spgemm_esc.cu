@@ -149,36 +149,51 @@ __device__ __forceinline__ uint32_t warp_bitonic_sort32(uint32_t key) {
     return key;
 }
 
-// One warp per row with at most 32 products. Lane l holds product l of the row's expansion
-// order; the sort key is (column << 32 | l), so equal columns stay in expansion order.
+#ifndef ESC_SMALL_ROWS
+#define ESC_SMALL_ROWS 4
+#endif
+
+// Rows with at most 32 products, ESC_SMALL_ROWS of them per warp. Lane l holds product l of a row's
+// expansion order; the sort key is (column << 32 | l), so equal columns stay in expansion order.
 // NARROW: B has fewer than 2^27 columns, so (column << 5 | lane) fits 32 bits and the sort
 // moves half as much through the shuffles.
+//
+// A row's work is a chain of five dependent loads (row number, A's offsets, A's columns, B's
+// offsets, B's columns) and little else, so a warp walks the chain for its rows side by side: the
+// loads of one link are issued for all of them before any is used.
 template <bool NUMERIC, bool NARROW>
 __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const int32_t *__restrict__ row_list, int n_rows,
                                                    int32_t *__restrict__ row_count, const int32_t *__restrict__ c_rp,
                                                    int32_t *__restrict__ c_col, float *__restrict__ c_val) {
-    const int w = (blockIdx.x * 256 + threadIdx.x) >> 5;
+    constexpr int R = ESC_SMALL_ROWS;
+    const int w = ((blockIdx.x * 256 + threadIdx.x) >> 5) * R;
     if (w >= n_rows) return;
     const int lane = lane_id();
-    const int32_t i = ld_nc(row_list + w);
-    const int32_t lo = ld_nc(A.rp + i), hi = ld_nc(A.rp + i + 1);
-    uint32_t my_col = 0;
-    float my_val = 0.f;
-    bool have = false;
-    // Expansion, 32 entries of the row at a time (one round unless the row holds entries whose rows
-    // of B are empty): lane l reads entry l and its row of B; the products of the round take the
-    // lanes [base, base + total) in expansion order, each finding its entry among the round's
-    // non-empty ones from the mask of slice starts.
-    int base = 0;
-    for (int32_t chunk = lo; chunk < hi; chunk += 32) {  // uniform across the warp
-        int32_t b_lo = 0, len = 0;
-        float a = 0.f;
-        if (chunk + lane < hi) {
-            const int32_t j = ld_nc(A.col + chunk + lane);
-            b_lo = ld_nc(B.rp + j);
-            len = ld_nc(B.rp + j + 1) - b_lo;
-            if (NUMERIC) a = ld_nc(A.val + chunk + lane);
+    int32_t i[R], lo[R], hi[R], out[R];
+    uint32_t my_col[R];
+    float my_val[R];
+    bool have[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) i[r] = w + r < n_rows ? ld_nc(row_list + w + r) : -1;
+    bool one_round = true;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        lo[r] = hi[r] = out[r] = 0;
+        if (i[r] >= 0) {
+            lo[r] = ld_nc(A.rp + i[r]);
+            hi[r] = ld_nc(A.rp + i[r] + 1);
+            if (NUMERIC) out[r] = ld_nc(c_rp + i[r]);
         }
+        one_round &= hi[r] - lo[r] <= 32;
+        my_col[r] = 0;
+        my_val[r] = 0.f;
+        have[r] = false;
+    }
+    // Expansion, 32 entries of a row at a time (one round unless the row holds entries whose rows of B
+    // are empty): lane l reads entry l and its row of B; the products of the round take the lanes
+    // [base, base + total) in expansion order, each finding its entry among the round's non-empty
+    // ones from the mask of slice starts.
+    auto place = [&](int r, int base, int32_t b_lo, int len, float a) -> int {
         const int incl = warp_incl_sum(len);
         const int start = base + incl - len;                       // first lane of this entry's products
         const unsigned nonempty = __ballot_sync(FULL_MASK, len > 0);
@@ -191,54 +206,93 @@ __global__ void __launch_bounds__(256) k_esc_small(CsrView A, CsrView B, const i
         const int o_start = __shfl_sync(FULL_MASK, start, owner);
         const float o_a = __shfl_sync(FULL_MASK, a, owner);
         if (lane >= base && lane < base + total) {
-            my_col = (uint32_t)ld_nc(B.col + o_lo + (lane - o_start));
-            if (NUMERIC) my_val = o_a * ld_nc(B.val + o_lo + (lane - o_start));
-            have = true;
+            my_col[r] = (uint32_t)ld_nc(B.col + o_lo + (lane - o_start));
+            if (NUMERIC) my_val[r] = o_a * ld_nc(B.val + o_lo + (lane - o_start));
+            have[r] = true;
         }
-        base += total;
-    }
-    if (!NUMERIC) {
-        // distinct columns: a lane counts if it is the first of the lanes that hold its column
-        const unsigned peers = __match_any_sync(FULL_MASK, have ? my_col : 0x80000000u | (uint32_t)lane);
-        const unsigned firsts = __ballot_sync(FULL_MASK, have && lane == __ffs(peers) - 1);
-        if (lane == 0) row_count[i] = __popc(firsts);
-        return;
-    }
-    uint32_t col;
-    int src;
-    bool valid;
-    if (NARROW) {
-        uint32_t key = have ? ((my_col << 5) | (uint32_t)lane) : ~0u;
-        key = warp_bitonic_sort32(key);
-        col = key >> 5;
-        src = (int)(key & 31u);
-        valid = key != ~0u;
+        return total;
+    };
+    if (one_round) {  // uniform: every link of the chain for all rows at once
+        int32_t j[R], b_lo[R], len[R];
+        float a[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            j[r] = lo[r] + lane < hi[r] ? ld_nc(A.col + lo[r] + lane) : -1;
+            a[r] = NUMERIC && j[r] >= 0 ? ld_nc(A.val + lo[r] + lane) : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            b_lo[r] = len[r] = 0;
+            if (j[r] >= 0) {
+                b_lo[r] = ld_nc(B.rp + j[r]);
+                len[r] = ld_nc(B.rp + j[r] + 1) - b_lo[r];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) place(r, 0, b_lo[r], len[r], a[r]);
     } else {
-        uint64_t key = have ? (((uint64_t)my_col << 32) | (uint32_t)lane) : ~0ull;
-        key = warp_bitonic_sort(key);
-        col = (uint32_t)(key >> 32);
-        src = (int)(key & 31u);
-        valid = key != ~0ull;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            int base = 0;
+            for (int32_t chunk = lo[r]; chunk < hi[r]; chunk += 32) {  // uniform across the warp
+                int32_t b_lo = 0, len = 0;
+                float a = 0.f;
+                if (chunk + lane < hi[r]) {
+                    const int32_t j = ld_nc(A.col + chunk + lane);
+                    b_lo = ld_nc(B.rp + j);
+                    len = ld_nc(B.rp + j + 1) - b_lo;
+                    if (NUMERIC) a = ld_nc(A.val + chunk + lane);
+                }
+                base += place(r, base, b_lo, len, a);
+            }
+        }
     }
-    const uint32_t prev_col = __shfl_up_sync(FULL_MASK, col, 1);
-    const bool head = valid && (lane == 0 || prev_col != col);
-    const unsigned heads = __ballot_sync(FULL_MASK, head);
-    float v = __shfl_sync(FULL_MASK, my_val, src);  // value of the product now at this lane
-    float acc = v;
-    // longest run of equal columns in this row (distance from a head to the next head or to
-    // the end of the valid lanes): the summation loop needs no more steps than that
-    const unsigned later = lane < 31 ? (heads >> (lane + 1)) : 0u;
-    const int n_valid = __popc(__ballot_sync(FULL_MASK, valid));
-    const int my_run = head ? (later ? __ffs(later) : n_valid - lane) : 0;
-    const int longest = __reduce_max_sync(FULL_MASK, my_run);
-    for (int t = 1; t < longest; ++t) {  // head lanes add their run in sorted (= expansion) order
-        const float nv = __shfl_down_sync(FULL_MASK, v, t);
-        if (t < my_run) acc += nv;
-    }
-    if (head) {
-        const int pos = ld_nc(c_rp + i) + __popc(heads & ((1u << lane) - 1u));
-        c_col[pos] = (int32_t)col;
-        c_val[pos] = acc;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (i[r] < 0) continue;  // uniform
+        if (!NUMERIC) {
+            // distinct columns: a lane counts if it is the first of the lanes that hold its column
+            const unsigned peers = __match_any_sync(FULL_MASK, have[r] ? my_col[r] : 0x80000000u | (uint32_t)lane);
+            const unsigned firsts = __ballot_sync(FULL_MASK, have[r] && lane == __ffs(peers) - 1);
+            if (lane == 0) row_count[i[r]] = __popc(firsts);
+            continue;
+        }
+        uint32_t col;
+        int src;
+        bool valid;
+        if (NARROW) {
+            uint32_t key = have[r] ? ((my_col[r] << 5) | (uint32_t)lane) : ~0u;
+            key = warp_bitonic_sort32(key);
+            col = key >> 5;
+            src = (int)(key & 31u);
+            valid = key != ~0u;
+        } else {
+            uint64_t key = have[r] ? (((uint64_t)my_col[r] << 32) | (uint32_t)lane) : ~0ull;
+            key = warp_bitonic_sort(key);
+            col = (uint32_t)(key >> 32);
+            src = (int)(key & 31u);
+            valid = key != ~0ull;
+        }
+        const uint32_t prev_col = __shfl_up_sync(FULL_MASK, col, 1);
+        const bool head = valid && (lane == 0 || prev_col != col);
+        const unsigned heads = __ballot_sync(FULL_MASK, head);
+        float v = __shfl_sync(FULL_MASK, my_val[r], src);  // value of the product now at this lane
+        float acc = v;
+        // longest run of equal columns in this row (distance from a head to the next head or to
+        // the end of the valid lanes): the summation loop needs no more steps than that
+        const unsigned later = lane < 31 ? (heads >> (lane + 1)) : 0u;
+        const int n_valid = __popc(__ballot_sync(FULL_MASK, valid));
+        const int my_run = head ? (later ? __ffs(later) : n_valid - lane) : 0;
+        const int longest = __reduce_max_sync(FULL_MASK, my_run);
+        for (int t = 1; t < longest; ++t) {  // head lanes add their run in sorted (= expansion) order
+            const float nv = __shfl_down_sync(FULL_MASK, v, t);
+            if (t < my_run) acc += nv;
+        }
+        if (head) {
+            const int pos = out[r] + __popc(heads & ((1u << lane) - 1u));
+            c_col[pos] = (int32_t)col;
+            c_val[pos] = acc;
+        }
     }
 }
 
@@ -798,11 +852,12 @@ int esc_run_bins(const nb200_csr *a, const nb200_csr *b, const EscPlan &plan, co
     }
     if (plan.host.n_small > 0) {
         LaunchScope scope(NUMERIC ? "esc_small_numeric" : "esc_small_symbolic", stream);
-        const int warps = plan.host.n_small;
+        const int warps = plan.host.n_small;  // rows on the list
+        const int small_warps = (warps + ESC_SMALL_ROWS - 1) / ESC_SMALL_ROWS;
         if (b->cols < (1 << 27))
-            k_esc_small<NUMERIC, true><<<(warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
+            k_esc_small<NUMERIC, true><<<(small_warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
         else
-            k_esc_small<NUMERIC, false><<<(warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
+            k_esc_small<NUMERIC, false><<<(small_warps + 7) / 8, 256, 0, stream>>>(A, B, plan.lists.small_rows, warps, count, c_rp, c_col, c_val);
         NB200_CUDA(cudaGetLastError());
     }
     return NB200_OK;
