@@ -24,6 +24,10 @@ struct CsrOut {
     int32_t *rp;
     int32_t *col;
     float *val;
+    // Asynchronous calls only: three device words {result entries, status, rows} the kernels fill
+    // themselves. The partition kernel writes rows and a status of 0, the last tile the length, and
+    // any tile whose bounded wait gives up (or a length beyond int32) raises the status.
+    long long *result = nullptr;
 };
 
 // Hardware barriers of the tile kernels: 0 = the whole CTA (__syncthreads), 1 = the worker

@@ -56,11 +56,25 @@ struct Cuts {
     int32_t *b;
 };
 
+// Result words of an asynchronous call (CsrOut::result), written from inside the tile kernel.
+__device__ __forceinline__ void publish_length(long long *result, long long total) {
+    if (!result) return;
+    result[0] = total;
+    if (total > INT32_MAX) atomicMax(result + 1, (long long)NB200_E_OVERFLOW);
+}
+__device__ __forceinline__ void publish_timeout(long long *result) {
+    if (result) atomicMax(result + 1, (long long)NB200_E_TIMEOUT);
+}
+
 // ------------------------------------------------------------------------- partition ----
 
 // One warp per cut. Cut t sits at merged position min(t * tile_step, total).
 __global__ void __launch_bounds__(NT) k_csr2_partition(CsrIn A, CsrIn B, int32_t rows, int64_t total,
-                                                       int32_t tile_step, int32_t num_tiles, Cuts cuts) {
+                                                       int32_t tile_step, int32_t num_tiles, Cuts cuts, long long *result) {
+    if (result && blockIdx.x == 0 && threadIdx.x == 0) {  // the tile kernel that follows fills in the rest
+        result[1] = NB200_OK;
+        result[2] = rows;
+    }
     const int t = (blockIdx.x * NT + threadIdx.x) >> 5;
     if (t > num_tiles) return;
     const int32_t a_base = ld_nc(A.rp), b_base = ld_nc(B.rp);
@@ -241,8 +255,14 @@ __device__ __noinline__ void csr2_tile_wide(const CsrIn &A, const CsrIn &B, cons
     WorkerBar::sync();
     if (MODE == MODE_FUSED) {
         base = s_base;
-        if (base < 0) return;  // a bounded wait gave up; the host reports it
-        if (t == num_tiles - 1 && tid == 0) ctl->total = base + total;
+        if (base < 0) {  // a bounded wait gave up; the host reports it
+            if (tid == 0) publish_timeout(Z.result);
+            return;
+        }
+        if (t == num_tiles - 1 && tid == 0) {
+            ctl->total = base + total;
+            publish_length(Z.result, base + total);
+        }
     }
 
     // ---- row offsets. Result row r starts after every result entry of rows < r; inside this
@@ -428,6 +448,7 @@ __device__ __forceinline__ void csr2_tile_blocked(const CsrIn &A, const CsrIn &B
     if (!__syncthreads_and(landed)) {  // the copies did not land in time: report, touch nothing
         if (tid == 0) {
             if (atomicCAS(&ctl->status.error, 0, ERR_COPY_TIMEOUT) == 0) ctl->status.detail = t;
+            publish_timeout(Z.result);
             if (MODE == MODE_FUSED) tile_state[t] = LB_PREFIX;  // successors must not wait on this tile
             mbar_wait_bounded(mbar, 0, MBAR_POLL_LIMIT);        // second bounded wait for copies in flight
         }
@@ -447,7 +468,11 @@ __device__ __forceinline__ void csr2_tile_blocked(const CsrIn &A, const CsrIn &B
         if (lane_id() == 0) {
             if (t > 0) st_relaxed_gpu(tile_state + t, LB_PREFIX | (uint64_t)(bse < 0 ? 0 : bse + total));
             s_base = bse;
-            if (bse >= 0 && t == num_tiles - 1) ctl->total = bse + total;
+            if (bse < 0) publish_timeout(Z.result);
+            if (bse >= 0 && t == num_tiles - 1) {
+                ctl->total = bse + total;
+                publish_length(Z.result, bse + total);
+            }
         }
         __syncthreads();
         return;
@@ -716,16 +741,6 @@ cudaError_t launch_tile(const CsrIn &A, const CsrIn &B, const Cuts &cuts, int cb
     return cudaGetLastError();
 }
 
-// Copies the control block's total and status into device words the caller reads later
-// ({result entries, device status, rows}), so that a call can return without waiting for the GPU.
-// The row count rides along so that the three words are a block's whole contribution to a
-// multi-GPU stitch: they can be handed to an all-gather as they are.
-__global__ void k_publish_result(const FusedCtl *ctl, int64_t rows, int64_t *out) {
-    out[0] = ctl->total;
-    out[1] = ctl->status.error != 0 ? NB200_E_TIMEOUT : (ctl->total > INT32_MAX ? NB200_E_OVERFLOW : NB200_OK);
-    out[2] = rows;
-}
-
 // Shared driver of add and multiply. When `alloc` is set the result arrays are allocated
 // here (one cudaMallocAsync each); otherwise z's arrays are the caller's, `capacity` entries.
 //
@@ -825,7 +840,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
         LaunchScope scope("csr2_partition", stream);
         const int warps = num_tiles + 1;
         const int blocks = (warps * 32 + NT - 1) / NT;
-        k_csr2_partition<<<blocks, NT, 0, stream>>>(A, B, rows, total, TILE_STEP, num_tiles, cuts);
+        k_csr2_partition<<<blocks, NT, 0, stream>>>(A, B, rows, total, TILE_STEP, num_tiles, cuts, reinterpret_cast<long long *>(device_result));
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_partition"));
@@ -841,15 +856,10 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
 
     FusedCtl h;
     if (fused) {
-        e = launch_tile<OP, MODE_FUSED>(A, B, cuts, cbits, nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, num_tiles, stream, knobs);
+        e = launch_tile<OP, MODE_FUSED>(A, B, cuts, cbits, nullptr, tile_state, ctl,
+                                        CsrOut{z->row_ptr, z->col, z->val, reinterpret_cast<long long *>(device_result)}, num_tiles, stream, knobs);
         if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_tile<fused>"));
-        if (device_result) {
-            LaunchScope scope("csr2_publish", stream);
-            k_publish_result<<<1, 1, 0, stream>>>(ctl, rows, device_result);
-            e = cudaGetLastError();
-            if (e != cudaSuccess) return fail(note_cuda_error(e, "k_publish_result"));
-            return NB200_OK;
-        }
+        if (device_result) return NB200_OK;  // length, status and rows arrive in the caller's device words, written by the kernels
         if ((st = read_ctl(h))) return fail(st);
         if (h.status.error != 0) return fail(note_timeout(h.status.error, h.status.detail, "csr merge"));
         if (h.total > INT32_MAX) return fail(NB200_E_OVERFLOW);
@@ -995,7 +1005,7 @@ int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_
 
     const CsrIn A{a->row_ptr, a->col, a->val, a->nnz}, B{b->row_ptr, b->col, b->val, b->nnz};
     const int warps = num_tiles + 1;
-    k_csr2_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts);
+    k_csr2_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts, nullptr);
     NB200_CUDA(cudaGetLastError());
     k_csr2_tile<V_CSR2, OP_UNION, MODE_FUSED><<<num_tiles, NT + 32, csr2_smem_bytes(), stream>>>(
         A, B, cuts, col_bits(a->cols), nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, 0, LOOKBACK_POLL_LIMIT);
