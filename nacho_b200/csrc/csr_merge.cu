@@ -70,11 +70,15 @@ __device__ __forceinline__ void publish_timeout(long long *result) {
 
 // One warp per cut. Cut t sits at merged position min(t * tile_step, total).
 __global__ void __launch_bounds__(NT) k_csr2_partition(CsrIn A, CsrIn B, int32_t rows, int64_t total,
-                                                       int32_t tile_step, int32_t num_tiles, Cuts cuts, long long *result) {
+                                                       int32_t tile_step, int32_t num_tiles, Cuts cuts, long long *result,
+                                                       uint64_t *zero_block, int zero_words) {
     if (result && blockIdx.x == 0 && threadIdx.x == 0) {  // the tile kernel that follows fills in the rest
         result[1] = NB200_OK;
         result[2] = rows;
     }
+    // the control block and the tile words of the kernel that follows start from zero (the grid has at
+    // least 32 threads per tile word, so one word per thread covers them)
+    if (blockIdx.x * NT + threadIdx.x < zero_words) zero_block[blockIdx.x * NT + threadIdx.x] = 0;
     const int t = (blockIdx.x * NT + threadIdx.x) >> 5;
     if (t > num_tiles) return;
     const int32_t a_base = ld_nc(A.rp), b_base = ld_nc(B.rp);
@@ -829,8 +833,7 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
     // the operands' columns.
     static const bool exact_alloc = [] { const char *e = std::getenv("NACHO_B200_EXACT_ALLOC"); return e && e[0] == '1'; }();
     const bool fused = device_result || (alloc ? !exact_alloc : (capacity >= bound && !force_two_pass));
-    cudaError_t e = cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * (fused ? (size_t)num_tiles + 4 : 4), stream);
-    if (e != cudaSuccess) return fail(note_cuda_error(e, "cudaMemsetAsync"));
+    cudaError_t e = cudaSuccess;
     if (fused && alloc && bound > 0) {
         e = cudaMallocAsync(reinterpret_cast<void **>(&z->col), sizeof(int32_t) * (size_t)bound, stream);
         if (e == cudaSuccess) e = cudaMallocAsync(reinterpret_cast<void **>(&z->val), sizeof(float) * (size_t)bound, stream);
@@ -840,7 +843,8 @@ int csr2_run(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, bool alloc, i
         LaunchScope scope("csr2_partition", stream);
         const int warps = num_tiles + 1;
         const int blocks = (warps * 32 + NT - 1) / NT;
-        k_csr2_partition<<<blocks, NT, 0, stream>>>(A, B, rows, total, TILE_STEP, num_tiles, cuts, reinterpret_cast<long long *>(device_result));
+        k_csr2_partition<<<blocks, NT, 0, stream>>>(A, B, rows, total, TILE_STEP, num_tiles, cuts, reinterpret_cast<long long *>(device_result),
+                                                    fused_block, fused ? num_tiles + 4 : 4);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) return fail(note_cuda_error(e, "k_csr2_partition"));
@@ -1000,12 +1004,12 @@ int csr_add_noalloc(const nb200_csr *a, const nb200_csr *b, nb200_csr *z, int64_
     FusedCtl *ctl = reinterpret_cast<FusedCtl *>(fused_block);
     uint64_t *tile_state = fused_block + 4;
     // the array keeps the previous call's contents: the ticket, the status and every tile word
-    // must start at zero
-    NB200_CUDA(cudaMemsetAsync(fused_block, 0, sizeof(uint64_t) * ((size_t)num_tiles + 4), stream));
+    // must start at zero (the partition kernel clears them)
 
     const CsrIn A{a->row_ptr, a->col, a->val, a->nnz}, B{b->row_ptr, b->col, b->val, b->nnz};
     const int warps = num_tiles + 1;
-    k_csr2_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts, nullptr);
+    k_csr2_partition<<<(warps * 32 + NT - 1) / NT, NT, 0, stream>>>(A, B, rows, total, tile_step, num_tiles, cuts, nullptr, fused_block,
+                                                                    num_tiles + 4);
     NB200_CUDA(cudaGetLastError());
     k_csr2_tile<V_CSR2, OP_UNION, MODE_FUSED><<<num_tiles, NT + 32, csr2_smem_bytes(), stream>>>(
         A, B, cuts, col_bits(a->cols), nullptr, tile_state, ctl, CsrOut{z->row_ptr, z->col, z->val}, 0, LOOKBACK_POLL_LIMIT);
