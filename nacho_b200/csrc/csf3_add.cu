@@ -501,6 +501,13 @@ int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
             flags, nz, a->k_ptr, b->k_ptr, off_a, off_b, scan_block + 4, reinterpret_cast<FusedCtl *>(scan_block));
     }
     NB200_CUDA(cudaGetLastError());
+    {   // a look-back of the offsets pass that gave up leaves offsets unwritten: they must not be used
+        NB200_CUDA(cudaMemcpyAsync(ws->host, scan_block, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
+        NB200_CUDA(cudaStreamSynchronize(stream));
+        FusedCtl h;
+        std::memcpy(&h, ws->host, sizeof(h));
+        if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "csf3 fibre offsets");
+    }
 
     // ---- 3. the entries: a CSR union with one row per fibre of Z
     const nb200_csr ma{nz, a->dims[2], a->n_k, off_a, a->k_idx, a->val};
@@ -508,13 +515,7 @@ int csf_add_two_level(const nb200_csf3 *a, const nb200_csf3 *b, nb200_csf3 *z, i
     nb200_csr mz{0, 0, 0, z->k_ptr, z->k_idx, z->val};
     st = nb200_csr_add_f32_into(&ma, &mb, &mz, cap_k, stream);
     z->n_k = mz.nnz;
-    if (st != NB200_OK) return st;
-    // a look-back of the offsets pass that gave up leaves offsets unwritten: report it
-    FusedCtl h;
-    NB200_CUDA(cudaMemcpyAsync(&h, scan_block, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
-    NB200_CUDA(cudaStreamSynchronize(stream));
-    if (h.status.error != 0) return note_timeout(h.status.error, h.status.detail, "csf3 fibre offsets");
-    return NB200_OK;
+    return st;
 }
 
 int check_csf3(const nb200_csf3 *t) {
