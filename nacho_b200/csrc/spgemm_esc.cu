@@ -60,9 +60,104 @@ struct RowLists {
     int32_t *small_rows, *medium_rows, *ranked_rows, *heavy_rows;
 };
 
+// P[p] = products of the first p stored entries of A (p = 0 .. nnz(A), counted from A's first row
+// offset, which need not be 0): B's row lengths summed
+// in one pass, 2048 entries per CTA, CTA totals chained by bounded look-back.
+__global__ void __launch_bounds__(256) k_esc_product_prefix(CsrView A, CsrView B, int32_t nnz_a, unsigned long long *__restrict__ P,
+                                                             uint64_t *state_raw, FusedCtl *ctl) {
+    constexpr int VT = 8;
+    __shared__ unsigned long long warp_sums[9];
+    __shared__ long long s_base;
+    volatile uint64_t *state = state_raw;
+    const int tid = threadIdx.x, t = blockIdx.x;  // CTAs are dispatched in index order; waits on earlier tiles are bounded
+    const int64_t p0 = ((int64_t)t * 256 + tid) * VT;
+    const int32_t *a_col = A.col + ld_nc(A.rp);
+    unsigned len[VT];
+    unsigned long long mine = 0;
+#pragma unroll
+    for (int q = 0; q < VT; ++q) {
+        len[q] = 0;
+        if (p0 + q < nnz_a) {
+            const int32_t j = ld_nc(a_col + p0 + q);
+            len[q] = (unsigned)(ld_nc(B.rp + j + 1) - ld_nc(B.rp + j));
+        }
+        mine += len[q];
+    }
+    unsigned long long incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long up = __shfl_up_sync(FULL_MASK, incl, d);
+        if (lane_id() >= d) incl += up;
+    }
+    if (lane_id() == 31) warp_sums[warp_id()] = incl;
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long run = 0;
+        for (int w = 0; w < 8; ++w) {
+            const unsigned long long c = warp_sums[w];
+            warp_sums[w] = run;
+            run += c;
+        }
+        warp_sums[8] = run;
+    }
+    __syncthreads();
+    if (warp_id() == 0) {
+        const int64_t b = lookback_exclusive(state, t, (int64_t)warp_sums[8], &ctl->status);
+        if (lane_id() == 0) s_base = b;
+    }
+    __syncthreads();
+    if (s_base < 0) return;
+    unsigned long long run = (unsigned long long)s_base + warp_sums[warp_id()] + incl - mine;
+#pragma unroll
+    for (int q = 0; q < VT; ++q) {
+        if (p0 + q <= nnz_a) P[p0 + q] = run;
+        run += len[q];
+    }
+}
+
 // Expand phase 1 (src/backend/compute.cpp:541-611): per-row product counts, and the bins.
-// Rows without products get their count (0) written here.
-__global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, CsrView B, int32_t rows, int32_t *__restrict__ row_count,
+// Rows without products get their count (0) written here. The counts come from the prefix P of
+// B's row lengths over A's entries (k_esc_product_prefix): a hub row costs one subtraction.
+__global__ void __launch_bounds__(256) k_esc_rowwork(CsrView A, const unsigned long long *__restrict__ P, int32_t rows,
+                                                     int32_t *__restrict__ row_count, RowLists lists, EscCtl *ctl) {
+    __shared__ unsigned long long warp_p[8];
+    const int i = blockIdx.x * 256 + threadIdx.x;  // one lane per row: its products are a difference of the prefix
+    unsigned long long p = 0;
+    if (i < rows) {
+        const int32_t base = ld_nc(A.rp);
+        p = ld_nc(P + (ld_nc(A.rp + i + 1) - base)) - ld_nc(P + (ld_nc(A.rp + i) - base));
+    }
+    if (i < rows) {  // lanes of a warp that take the same branch share one atomic
+        if (p == 0) {
+            if (row_count) row_count[i] = 0;
+        } else if (p <= SMALL_P) {
+            lists.small_rows[atomicAdd(&ctl->n_small, 1)] = i;
+        } else if (p <= MEDIUM_P) {
+            lists.medium_rows[atomicAdd(&ctl->n_medium, 1)] = i;
+        } else if (p <= RANKED_P) {
+            lists.ranked_rows[atomicAdd(&ctl->n_ranked, 1)] = i;
+        } else if (p > GIANT_P) {
+            lists.heavy_rows[atomicAdd(&ctl->n_giant, 1)] = i;
+        } else {
+            lists.heavy_rows[rows - 1 - atomicAdd(&ctl->n_heavy, 1)] = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL_MASK, p, o);
+    // one atomic per CTA for the product total
+    if (lane_id() == 0) warp_p[warp_id()] = p;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long sum = 0;
+        for (int v = 0; v < 8; ++v) sum += warp_p[v];
+        if (sum) atomicAdd(&ctl->products, sum);
+    }
+}
+
+// The same with the product counts taken row by row: one lane per row walks its entries (the warp
+// shares the work of its longer rows). For matrices of short rows, where a prefix pass over A's
+// entries costs more than it saves.
+__global__ void __launch_bounds__(256) k_esc_rowwork_walk(CsrView A, CsrView B, int32_t rows, int32_t *__restrict__ row_count,
                                                      RowLists lists, EscCtl *ctl) {
     __shared__ unsigned long long warp_p[8];
     const int i = blockIdx.x * 256 + threadIdx.x;  // one lane per row; the warp shares the work of its longer rows
@@ -749,6 +844,9 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, bool carry_
     sizes.take<uint64_t>((size_t)scan_ctas + 8);
     sizes.take<EscCtl>(1);
     if (with_table) sizes.take<int32_t>(ptr_entries);
+    const int prefix_ctas = (int)(((int64_t)a->nnz + 1 + 2047) / 2048);
+    sizes.take<unsigned long long>((size_t)a->nnz + 1);
+    sizes.take<uint64_t>((size_t)prefix_ctas + 8);
     int st;
     if ((st = acquire_workspace(stream, sizes.used(), &plan->ws))) return st;
     Carver carve(plan->ws->dev);
@@ -762,17 +860,35 @@ int esc_prepare(const nb200_csr *a, const nb200_csr *b, bool counts, bool carry_
     plan->ctl = carve.take<EscCtl>(1);
     plan->n_win = (int)n_win;
     plan->win_ptr = with_table ? carve.take<int32_t>(ptr_entries) : nullptr;
+    unsigned long long *prefix = carve.take<unsigned long long>((size_t)a->nnz + 1);
+    uint64_t *prefix_block = carve.take<uint64_t>((size_t)prefix_ctas + 8);
 
     NB200_CUDA(cudaMemsetAsync(plan->ctl, 0, sizeof(EscCtl), stream));
+    NB200_CUDA(cudaMemsetAsync(prefix_block, 0, sizeof(uint64_t) * ((size_t)prefix_ctas + 8), stream));
     const CsrView A{a->row_ptr, a->col, a->val}, B{b->row_ptr, b->col, b->val};
-    if (rows > 0) {
+    const bool short_rows = (int64_t)a->nnz <= 8 * (int64_t)rows;  // then a lane walks its row faster than a prefix pass pays
+    if (rows > 0 && short_rows) {
         LaunchScope scope("esc_rowwork", stream);
-        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, counts ? plan->row_count : nullptr, plan->lists, plan->ctl);
+        k_esc_rowwork_walk<<<(rows + 255) / 256, 256, 0, stream>>>(A, B, rows, counts ? plan->row_count : nullptr, plan->lists, plan->ctl);
+        NB200_CUDA(cudaGetLastError());
+    } else if (rows > 0) {
+        {
+            LaunchScope scope("esc_product_prefix", stream);
+            k_esc_product_prefix<<<prefix_ctas, 256, 0, stream>>>(A, B, a->nnz, prefix, prefix_block + 4, reinterpret_cast<FusedCtl *>(prefix_block));
+        }
+        LaunchScope scope("esc_rowwork", stream);
+        k_esc_rowwork<<<(rows + 255) / 256, 256, 0, stream>>>(A, prefix, rows, counts ? plan->row_count : nullptr, plan->lists, plan->ctl);
         NB200_CUDA(cudaGetLastError());
     }
     NB200_CUDA(cudaMemcpyAsync(plan->ws->host, plan->ctl, sizeof(EscCtl), cudaMemcpyDeviceToHost, stream));
+    NB200_CUDA(cudaMemcpyAsync(plan->ws->host + 16, prefix_block, sizeof(FusedCtl), cudaMemcpyDeviceToHost, stream));
     NB200_CUDA(cudaStreamSynchronize(stream));
     std::memcpy(&plan->host, plan->ws->host, sizeof(EscCtl));
+    {   // a prefix whose look-back gave up leaves rows with wrong product counts: nothing may be built on them
+        FusedCtl hp;
+        std::memcpy(&hp, plan->ws->host + 16, sizeof(hp));
+        if (hp.status.error != 0) return note_timeout(hp.status.error, hp.status.detail, "spgemm product prefix");
+    }
     if (with_table && plan->host.n_ranked + plan->host.n_giant + plan->host.n_heavy > 0) {
         LaunchScope scope("esc_window_ptr", stream);
         k_esc_window_ptr<<<(unsigned)((ptr_entries + 255) / 256), 256, 0, stream>>>(B, b->rows, plan->n_win, plan->win_ptr);
