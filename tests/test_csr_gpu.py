@@ -239,6 +239,8 @@ def test_bounded_wait_gives_up_and_reports(nacho, oracle):
     assert status == _capi.E_TIMEOUT
     assert time.perf_counter() - t0 < 5.0, "the give-up must come after a short, bounded wait"
     assert "wait" in lib.nb200_strerror(status).decode()
+    said = lib.nb200_last_cuda_error().decode()   # which wait gave up, and at which tile
+    assert "look-back" in said and "tile" in said, said
     # the same context, stream and scratch pool still give exact results
     assert_same(csr_from_gpu(nacho.gpu_csr_add_f32(ga, gb)), oracle.csr_add(synth_csr(ta), synth_csr(tb), 8), "add after a give-up")
 
